@@ -1,0 +1,185 @@
+"""TEST INFRASTRUCTURE ONLY: Python face of the CPU oracle.
+
+`Oracle` loads oracle/liboracle_matmul.so (the plain-C restatement of NiuTensor's
+built-in fp32 CPU matrix multiplication, oracle/matmul_oracle.c). `Reference` loads
+the unmodified NiuTensor CPU library built by `make -C oracle ref` into oracle/_ref/
+(absent on machines where the reference sources are not available).
+
+Only tests, the smoke check and the CPU-baseline legs of the benchmark may import this
+module; the product package never does.
+
+Transposition flags follow the reference enum (source/tensor/XDataType.h:36):
+X_TRANS = 0, X_NOTRANS = 1.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+X_TRANS = 0
+X_NOTRANS = 1
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_F32P = ctypes.POINTER(ctypes.c_float)
+_I32P = ctypes.POINTER(ctypes.c_int)
+
+
+def _fp(x):
+    return x.ctypes.data_as(_F32P)
+
+
+def _as_f32(x):
+    return np.ascontiguousarray(x, dtype=np.float32)
+
+
+def build_oracle():
+    """Compile the C restatement if it is missing or older than its source."""
+    so = os.path.join(_HERE, "liboracle_matmul.so")
+    src = os.path.join(_HERE, "matmul_oracle.c")
+    if not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-s", "-C", _HERE, "oracle"])
+    return so
+
+
+def mm_dims(a_shape, tA, b_shape, tB):
+    """(M, N, K) of op(a) * op(b) from the stored 2-D shapes."""
+    na, ma = a_shape[-2], a_shape[-1]
+    nb, mb = b_shape[-2], b_shape[-1]
+    M, K = (ma, na) if tA == X_TRANS else (na, ma)
+    K2, N = (mb, nb) if tB == X_TRANS else (nb, mb)
+    if K != K2:
+        raise ValueError("unmatched inner dimensions %r %r" % (a_shape, b_shape))
+    return M, N, K
+
+
+class Oracle:
+    """ctypes binding of oracle/matmul_oracle.c."""
+
+    def __init__(self):
+        self.lib = ctypes.CDLL(build_oracle())
+        self.lib.orc_matmul2d_f32.argtypes = [_F32P, ctypes.c_int, _F32P, ctypes.c_int, _F32P] + \
+            [ctypes.c_int] * 6 + [ctypes.c_float] * 2
+        self.lib.orc_matmul_batched_f32.argtypes = [_F32P, ctypes.c_int, _F32P, ctypes.c_int, _F32P] + \
+            [ctypes.c_int] * 7 + [ctypes.c_float] * 2
+        self.lib.orc_matmul_broadcast_f32.argtypes = [_F32P, ctypes.c_int, _F32P, ctypes.c_int, _F32P] + \
+            [ctypes.c_int] * 8 + [ctypes.c_float] * 2
+        self.lib.orc_set_threads.argtypes = [ctypes.c_int]
+
+    def set_threads(self, n):
+        self.lib.orc_set_threads(int(n))
+
+    def matmul2d(self, a, tA, b, tB, alpha=1.0, beta=0.0, c=None):
+        a, b = _as_f32(a), _as_f32(b)
+        M, N, _ = mm_dims(a.shape, tA, b.shape, tB)
+        c = np.zeros((M, N), np.float32) if c is None else _as_f32(c).copy()
+        self.lib.orc_matmul2d_f32(_fp(a), tA, _fp(b), tB, _fp(c), a.shape[0], a.shape[1],
+                                  b.shape[0], b.shape[1], M, N, alpha, beta)
+        return c
+
+    def matmul_batched(self, a, tA, b, tB, alpha=1.0, beta=0.0, c=None):
+        """_MatrixMulBatched: equal leading extents, block i of a meets block i of b."""
+        a, b = _as_f32(a), _as_f32(b)
+        if a.shape[:-2] != b.shape[:-2]:
+            raise ValueError("leading extents differ")
+        M, N, _ = mm_dims(a.shape, tA, b.shape, tB)
+        count = int(np.prod(a.shape[:-2], dtype=np.int64))
+        shape = a.shape[:-2] + (M, N)
+        c = np.zeros(shape, np.float32) if c is None else _as_f32(c).copy().reshape(shape)
+        self.lib.orc_matmul_batched_f32(_fp(a), tA, _fp(b), tB, _fp(c), count,
+                                        a.shape[-2], a.shape[-1], b.shape[-2], b.shape[-1],
+                                        M, N, alpha, beta)
+        return c
+
+    def matmul(self, a, tA, b, tB, alpha=1.0, beta=0.0, c=None):
+        """_MatrixMul: general form; c has shape a.lead + b.lead + (M, N)."""
+        a, b = _as_f32(a), _as_f32(b)
+        M, N, _ = mm_dims(a.shape, tA, b.shape, tB)
+        shape = a.shape[:-2] + b.shape[:-2] + (M, N)
+        c = np.zeros(shape, np.float32) if c is None else _as_f32(c).copy().reshape(shape)
+        P = int(np.prod(a.shape[:-2], dtype=np.int64))
+        Q = int(np.prod(b.shape[:-2], dtype=np.int64))
+        self.lib.orc_matmul_broadcast_f32(_fp(a), tA, _fp(b), tB, _fp(c), P, Q,
+                                          a.shape[-2], a.shape[-1], b.shape[-2], b.shape[-1],
+                                          M, N, alpha, beta)
+        return c
+
+
+def ref_path(kind):
+    return os.path.join(_HERE, "_ref", "libnts_ref_%s.so" % kind)
+
+
+def ref_available(kind="builtin"):
+    return os.path.exists(ref_path(kind))
+
+
+def _preload_openblas_deps():
+    """The OpenBLAS the reference is linked to here ships inside the
+    opencv_python_headless wheel; its libgfortran/libquadmath sit beside it and are not
+    on the loader path, so they are opened first."""
+    import glob
+    import sys
+    dirs = glob.glob(os.path.join(sys.prefix, "lib", "python3*", "site-packages",
+                                  "opencv_python_headless.libs"))
+    for d in dirs:
+        for pat in ("libquadmath-*.so*", "libgfortran-*.so*"):
+            for f in sorted(glob.glob(os.path.join(d, pat))):
+                ctypes.CDLL(f, mode=ctypes.RTLD_GLOBAL)
+
+
+class Reference:
+    """The compiled NiuTensor CPU library behind oracle/ref_driver.cpp.
+
+    kind "builtin": the reference's own scalar loops (correct for all four
+    transposition combinations, single-threaded). kind "openblas": the reference built
+    with USE_BLAS against OpenBLAS; its T/T branch is wrong in the reference itself
+    (source/tensor/core/arithmetic/XTensorBLAS.cpp:64-65), so callers avoid T/T there.
+    """
+    FORM_GENERAL, FORM_BATCHED, FORM_2D = 0, 1, 2
+
+    def __init__(self, kind="builtin"):
+        self.kind = kind
+        if kind == "openblas":
+            _preload_openblas_deps()
+        self.lib = ctypes.CDLL(ref_path(kind))
+        self.lib.ref_matmul_f32.argtypes = [
+            ctypes.c_int,
+            _F32P, ctypes.c_int, _I32P, ctypes.c_int,
+            _F32P, ctypes.c_int, _I32P, ctypes.c_int,
+            _F32P, ctypes.c_int, _I32P,
+            ctypes.c_float, ctypes.c_float]
+        self.lib.ref_set_blas_threads.argtypes = [ctypes.c_int]
+
+    def set_threads(self, n):
+        self.lib.ref_set_blas_threads(int(n))
+
+    def run(self, form, a, tA, b, tB, alpha=1.0, beta=0.0, c=None):
+        a, b = _as_f32(a), _as_f32(b)
+        M, N, _ = mm_dims(a.shape, tA, b.shape, tB)
+        if form == self.FORM_GENERAL:
+            shape = a.shape[:-2] + b.shape[:-2] + (M, N)
+        else:
+            shape = a.shape[:-2] + (M, N)
+        c = np.zeros(shape, np.float32) if c is None else _as_f32(c).copy().reshape(shape)
+        ad = np.asarray(a.shape, np.int32)
+        bd = np.asarray(b.shape, np.int32)
+        cd = np.asarray(c.shape, np.int32)
+        self.lib.ref_matmul_f32(form, _fp(a), a.ndim, ad.ctypes.data_as(_I32P), tA,
+                                _fp(b), b.ndim, bd.ctypes.data_as(_I32P), tB,
+                                _fp(c), c.ndim, cd.ctypes.data_as(_I32P), alpha, beta)
+        return c
+
+
+def round_to_half(x):
+    """IEEE round-to-nearest-even fp32 -> fp16 -> fp32: the values an X_FLOAT16 tensor
+    holds. The reference has no CPU fp16 arithmetic (MatrixMul.cpp:181 "TODO!"), so the
+    fp16 oracle is the fp32 CPU path run on fp16-valued inputs."""
+    return np.asarray(x, np.float32).astype(np.float16).astype(np.float32)
+
+
+def rel_fro(x, ref):
+    """Relative Frobenius error, accumulated in float64."""
+    x = np.asarray(x, np.float64)
+    ref = np.asarray(ref, np.float64)
+    den = np.linalg.norm(ref.ravel())
+    return float(np.linalg.norm((x - ref).ravel()) / (den if den > 0 else 1.0))

@@ -1,0 +1,90 @@
+/*
+ * TEST INFRASTRUCTURE ONLY. Thin C driver around the unmodified NiuTensor CPU
+ * matrix-multiplication operators, compiled together with the NiuTensor sources
+ * (where they lie, never copied) into oracle/_ref/. It wraps caller-owned host
+ * buffers in header-only XTensor objects and calls the reference's own
+ *   nts::_MatrixMul          (source/tensor/core/arithmetic/MatrixMul.cpp:52)
+ *   nts::_MatrixMulBatched   (source/tensor/core/arithmetic/MatrixMulBatched.cpp:49)
+ *   nts::_MatrixMul2D        (source/tensor/core/arithmetic/MatrixMul2D.cpp:46)
+ * Nothing on the product path may link or load this file's output.
+ */
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include "tensor/XTensor.h"
+#include "tensor/XCall.h"
+#include "tensor/core/arithmetic/MatrixMul.h"
+#include "tensor/core/arithmetic/MatrixMul2D.h"
+#include "tensor/core/arithmetic/MatrixMulBatched.h"
+#ifdef USE_BLAS
+#include "tensor/XBLAS.h"
+#endif
+
+using namespace nts;
+
+namespace {
+/* header without storage: negative leading extent (XTensor.cpp:1459-1462) */
+XTensor * View(float * data, int order, const int * dims)
+{
+    int d[8];
+    for (int i = 0; i < order; i++)
+        d[i] = dims[i];
+    d[0] = -d[0];
+    XTensor * t = NewTensorV2(order, d, X_FLOAT, 1.0F, -1, NULL);
+    t->data = data;
+    return t;
+}
+void Drop(XTensor * t)
+{
+    t->data = NULL;
+    delete t;
+}
+}
+
+extern "C" {
+
+/* form: 0 = _MatrixMul (general / broadcast / flatten), 1 = _MatrixMulBatched,
+   2 = _MatrixMul2D. trans flags carry the reference enum: 0 = X_TRANS, 1 = X_NOTRANS. */
+int ref_matmul_f32(int form,
+                   const float * a, int aOrder, const int * aDims, int transA,
+                   const float * b, int bOrder, const int * bDims, int transB,
+                   float * c, int cOrder, const int * cDims,
+                   float alpha, float beta)
+{
+    XTensor * ta = View((float*)a, aOrder, aDims);
+    XTensor * tb = View((float*)b, bOrder, bDims);
+    XTensor * tc = View(c, cOrder, cDims);
+    MATRIX_TRANS_TYPE tA = transA == 0 ? X_TRANS : X_NOTRANS;
+    MATRIX_TRANS_TYPE tB = transB == 0 ? X_TRANS : X_NOTRANS;
+    if (form == 0)
+        _MatrixMul(ta, tA, tb, tB, tc, alpha, beta);
+    else if (form == 1)
+        _MatrixMulBatched(ta, tA, tb, tB, tc, alpha, beta);
+    else
+        _MatrixMul2D(ta, tA, tb, tB, tc, alpha, beta);
+    Drop(ta);
+    Drop(tb);
+    Drop(tc);
+    return 0;
+}
+
+/* 1 when this build routes dense fp32 GEMMs to cblas_sgemm (XTensorBLAS.cpp:39) */
+int ref_uses_blas(void)
+{
+#ifdef USE_BLAS
+    return 1;
+#else
+    return 0;
+#endif
+}
+
+void ref_set_blas_threads(int n)
+{
+#ifdef USE_BLAS
+    openblas_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
+}

@@ -1,0 +1,51 @@
+"""Seeded inputs shared by the fixture generator (make_golden.py, which feeds them to
+the compiled reference) and by the tests (which feed them to the oracle and to the CUDA
+path and compare with the stored reference outputs). numpy's PCG64 stream is stable
+across versions, so the inputs are reproducible from the seed alone."""
+import numpy as np
+
+X_TRANS = 0
+X_NOTRANS = 1
+FORM_GENERAL, FORM_BATCHED, FORM_2D = 0, 1, 2
+
+
+def stored(rng, lead, rows, cols, trans):
+    shp = tuple(lead) + ((cols, rows) if trans == X_TRANS else (rows, cols))
+    return rng.uniform(-1.0, 1.0, shp).astype(np.float32)
+
+
+def seeded_cases():
+    """(key, form, a, tA, b, tB, alpha, beta, c0) for the reference to run."""
+    out = []
+    rng = np.random.default_rng(20240)
+    ab = [(1.0, 0.0), (0.125, 0.0), (1.0, 1.0), (1.0, 0.5), (-0.75, 0.3)]
+    sizes = [(5, 7, 3), (33, 17, 65), (20, 36, 16), (67, 35, 66), (1, 9, 1)]
+    n = 0
+    for tA in (X_TRANS, X_NOTRANS):
+        for tB in (X_TRANS, X_NOTRANS):
+            for (alpha, beta) in ab:
+                M, N, K = sizes[n % len(sizes)]
+                n += 1
+                # 2-D
+                a = stored(rng, (), M, K, tA)
+                b = stored(rng, (), K, N, tB)
+                c0 = rng.normal(size=(M, N)).astype(np.float32)
+                out.append(("2d", FORM_2D, a, tA, b, tB, alpha, beta, c0))
+                # batched, two leading dims
+                a = stored(rng, (2, 2), M, K, tA)
+                b = stored(rng, (2, 2), K, N, tB)
+                c0 = rng.normal(size=(2, 2, M, N)).astype(np.float32)
+                out.append(("batched", FORM_BATCHED, a, tA, b, tB, alpha, beta, c0))
+                # broadcast: every block of a meets every block of b
+                a = stored(rng, (3,), M, K, tA)
+                b = stored(rng, (2,), K, N, tB)
+                c0 = rng.normal(size=(3, 2, M, N)).astype(np.float32)
+                out.append(("broadcast", FORM_GENERAL, a, tA, b, tB, alpha, beta, c0))
+                # a.order > 2, b.order == 2 (the flatten shortcut when tA == X_NOTRANS)
+                a = stored(rng, (2, 2), M, K, tA)
+                b = stored(rng, (), K, N, tB)
+                c0 = rng.normal(size=(2, 2, M, N)).astype(np.float32)
+                out.append(("a3_b2", FORM_GENERAL, a, tA, b, tB, alpha, beta, c0))
+    return out
+
+

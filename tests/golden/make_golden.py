@@ -1,0 +1,90 @@
+"""Regenerates the golden fixtures of this folder. Needs the NiuTensor sources
+(REF, default /root/reference) and the compiled reference CPU library
+(`make -C oracle ref`); the fixtures themselves are committed so the tests run
+without either.
+
+  ref_kat.json     the literal input/answer arrays of the reference's own unit tests
+                   for this path, read as text from source/tensor/test/TMatrixMul.cpp,
+                   TMatrixMul2D.cpp, TMatrixMul2DParallel.cpp, TMatrixMulBatched.cpp
+                   (one entry per `bool TestXxxN()` function; both the `_Op` and the
+                   user-level call of a case share the arrays).
+  ref_seeded.npz   outputs of the reference library itself (built-in fp32 CPU path,
+                   through oracle/ref_driver.cpp) on the seeded inputs that
+                   tests/golden/cases.py regenerates: all four transposition
+                   combinations x alpha/beta pairs x 2-D / batched / broadcast /
+                   flatten forms, ragged sizes included. Only the outputs are stored.
+
+Usage: python tests/golden/make_golden.py
+"""
+import json
+import os
+import re
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+REF = os.environ.get("REF", "/root/reference")
+
+from oracle.oracle import Reference, X_TRANS, X_NOTRANS  # noqa: E402
+from tests.golden.cases import seeded_cases  # noqa: E402
+
+TEST_FILES = ["TMatrixMul.cpp", "TMatrixMul2D.cpp", "TMatrixMul2DParallel.cpp",
+              "TMatrixMulBatched.cpp"]
+FLAG = {"X_TRANS": X_TRANS, "X_NOTRANS": X_NOTRANS}
+
+
+def parse_array(text, name):
+    m = re.search(r"DTYPE\s+%s((?:\[\d+\])+)\s*=\s*(\{.*?\});" % name, text, re.S)
+    dims = [int(x) for x in re.findall(r"\[(\d+)\]", m.group(1))]
+    vals = [float(x.rstrip("Ff")) for x in
+            re.findall(r"-?\d+\.?\d*(?:[eE][-+]?\d+)?[Ff]?", m.group(2))]
+    assert len(vals) == int(np.prod(dims)), (name, dims, len(vals))
+    return dims, vals
+
+
+def parse_file(fn):
+    text = open(os.path.join(REF, "source", "tensor", "test", fn)).read()
+    # split into the bodies of the `bool TestXxxN()` case functions
+    parts = re.split(r"\nbool (Test\w+\d+)\(\)\s*\n\{", text)
+    cases = []
+    for name, body in zip(parts[1::2], parts[2::2]):
+        call = re.search(r"_(MatrixMul\w*)\(\s*s1\s*,\s*(X_\w+)\s*,\s*s2\s*,\s*(X_\w+)\s*,\s*t\s*\)",
+                         body)
+        ad, av = parse_array(body, "sData1")
+        bd, bv = parse_array(body, "sData2")
+        cd, cv = parse_array(body, "answer")
+        line = text[:text.index("bool %s()" % name)].count("\n") + 1
+        cases.append({"source": "source/tensor/test/%s:%d" % (fn, line), "name": name,
+                      "op": "_" + call.group(1), "transA": FLAG[call.group(2)],
+                      "transB": FLAG[call.group(3)], "alpha": 1.0, "beta": 0.0,
+                      "a_shape": ad, "a": av, "b_shape": bd, "b": bv,
+                      "c_shape": cd, "answer": cv, "tolerance": 1e-4})
+    return cases
+
+
+def main():
+    kat = []
+    for fn in TEST_FILES:
+        kat += parse_file(fn)
+    with open(os.path.join(HERE, "ref_kat.json"), "w") as f:
+        json.dump({"generator": "tests/golden/make_golden.py", "cases": kat}, f, indent=1)
+    print("ref_kat.json: %d cases" % len(kat))
+
+    ref = Reference("builtin")
+    arrays = {}
+    meta = []
+    for i, (key, form, a, tA, b, tB, alpha, beta, c0) in enumerate(seeded_cases()):
+        c = ref.run(form, a, tA, b, tB, alpha, beta, c0)
+        arrays["c%d" % i] = c
+        meta.append({"kind": key, "form": form, "transA": tA, "transB": tB,
+                     "alpha": alpha, "beta": beta})
+    arrays["meta"] = np.frombuffer(json.dumps(meta).encode(), dtype=np.uint8)
+    np.savez_compressed(os.path.join(HERE, "ref_seeded.npz"), **arrays)
+    print("ref_seeded.npz: %d cases" % len(meta))
+
+
+if __name__ == "__main__":
+    main()
