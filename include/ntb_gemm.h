@@ -1,0 +1,170 @@
+/*
+ * ntb_gemm.h -- C ABI of the B200 (sm_100a) dense matrix-multiplication library that
+ * stands in for NiuTensor's cuBLAS wrapper layer.
+ *
+ * Every function computes, for row-major packed-or-strided matrices,
+ *
+ *        c = alpha * op(a) * op(b) + beta * c
+ *
+ * with the reference's conventions: `na x ma`, `nb x mb`, `nc x mc` are the STORED
+ * (pre-transposition) rows x cols; transposition flags carry the reference's enum
+ * values (source/tensor/XDataType.h:36: X_TRANS = 0, X_NOTRANS = 1 -- note that 0
+ * means "transposed"); data types carry TENSOR_DATA_TYPE values
+ * (source/tensor/XDataType.h:33). alpha and beta arrive as float even for half
+ * tensors, as DTYPE does in the reference (source/tensor/XGlobal.h:54).
+ *
+ * Supported type triples (a, b, c): (X_FLOAT16, X_FLOAT16, X_FLOAT16),
+ * (X_FLOAT16, X_FLOAT16, X_FLOAT) and (X_FLOAT, X_FLOAT, X_FLOAT). Products are
+ * accumulated in fp32 and alpha/beta are applied in fp32 before the single final
+ * rounding. X_DOUBLE, X_INT and X_INT8 return NTB_ERR_DTYPE.
+ *
+ * Ownership: all matrix pointers are caller-owned device memory on `devID`; the
+ * library never allocates or frees tensor storage. `stream` is a cudaStream_t passed as
+ * void*; NULL means the legacy default stream, which is where the reference issues all
+ * of its work. When beta == 0 the output is never read, so the reference's memset of c
+ * before the call (source/tensor/core/arithmetic/MatrixMul2D.cu:154-155) is not needed.
+ * c must not overlap a or b.
+ *
+ * Errors: every function returns 0 on success or an NTB_ERR_* code; nothing throws or
+ * exits. The C++ operator layer turns a nonzero code into the reference's fatal
+ * ShowNTErrors behaviour. There is no CPU fallback: without a usable CUDA device every
+ * compute entry point returns NTB_ERR_CUDA.
+ *
+ * Threading: re-entrant per device; a per-device context (tensor-map encoder, status
+ * word, staging buffers of the host-buffer entry point) is created lazily under a lock.
+ * The current device of the calling thread is saved and restored around each call
+ * (the reference's ProtectCudaDev/BacktoCudaDev, source/tensor/XDevice.h:233-244).
+ */
+#ifndef NTB_GEMM_H
+#define NTB_GEMM_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* TENSOR_DATA_TYPE (source/tensor/XDataType.h:33) */
+#define NTB_X_INT      0
+#define NTB_X_INT8     1
+#define NTB_X_FLOAT    2
+#define NTB_X_FLOAT16  3
+#define NTB_X_DOUBLE   4
+
+/* MATRIX_TRANS_TYPE (source/tensor/XDataType.h:36) */
+#define NTB_X_TRANS    0
+#define NTB_X_NOTRANS  1
+
+#define NTB_OK              0
+#define NTB_ERR_ARG         1   /* NULL pointer, negative size, bad flag */
+#define NTB_ERR_SHAPE       2   /* inner dimensions or output shape do not match */
+#define NTB_ERR_DTYPE       3   /* unsupported data-type triple */
+#define NTB_ERR_CUDA        4   /* CUDA runtime / driver call failed, or no device */
+#define NTB_ERR_DEVICE_WAIT 5   /* a bounded on-device wait ran out (kernel gave up) */
+#define NTB_ERR_LIMIT       6   /* a size exceeds a documented fixed limit */
+
+/* kernel routes, as reported by ntb_last_route() */
+#define NTB_ROUTE_NONE      0
+#define NTB_ROUTE_TC_F16    1   /* tcgen05 kind::f16, TMA-fed, TMEM accumulators */
+#define NTB_ROUTE_TC_3XTF32 2   /* tcgen05 kind::tf32, three passes on hi/lo split fp32 */
+#define NTB_ROUTE_SIMT      3   /* FFMA kernel for operands TMA cannot address */
+
+/*
+ * Single GEMM. Replaces _CudaBLASMatrixMUL
+ * (source/tensor/core/arithmetic/XTensorBLAS.cu:38-104) and the dense GPU branch of
+ * _CudaMatrixMul2D (source/tensor/core/arithmetic/MatrixMul2D.cu:123-209).
+ * lda/ldb/ldc are row pitches in elements (the reference always has lda = ma etc.;
+ * explicit pitches allow a column shard of a resident matrix to be multiplied in place).
+ */
+int ntb_gemm(int devID, void * stream,
+             const void * a, int transA, const void * b, int transB, void * c,
+             int dtypeAB, int dtypeC,
+             int na, int ma, int nb, int mb, int nc, int mc,
+             long long lda, long long ldb, long long ldc,
+             float alpha, float beta);
+
+/*
+ * `count` GEMMs of one shape whose matrices lie at constant element strides; a stride
+ * of 0 reuses one matrix for every problem. One launch covers all problems.
+ * Replaces _CudaBLASMatrixMULBatchedStrided
+ * (source/tensor/core/arithmetic/XTensorBLAS.cu:181-247), the call behind
+ * _MatrixMulBatchedGPU (source/tensor/core/arithmetic/MatrixMulBatched.cpp:84-138).
+ */
+int ntb_gemm_strided_batched(int devID, void * stream,
+                             const void * a, int transA, const void * b, int transB, void * c,
+                             int dtypeAB, int dtypeC,
+                             int na, int ma, int nb, int mb, int nc, int mc,
+                             long long lda, long long ldb, long long ldc,
+                             long long strideA, long long strideB, long long strideC,
+                             int count, float alpha, float beta);
+
+/*
+ * The general form of _MatrixMul
+ * (source/tensor/core/arithmetic/MatrixMul.cpp:100-146): a holds aBlockNum packed
+ * matrices, b holds bBlockNum; every pair (p, q) is multiplied and written to block
+ * p * bBlockNum + q of c. One launch, base addresses computed on the device from
+ * (p, q) -- there are no pointer tables and no host-to-device copies (the reference
+ * builds three and copies them synchronously, XTensorBLAS.cu:315-347).
+ */
+int ntb_gemm_broadcast(int devID, void * stream,
+                       const void * a, int transA, const void * b, int transB, void * c,
+                       int dtypeAB, int dtypeC,
+                       int na, int ma, int nb, int mb, int nc, int mc,
+                       int aBlockNum, int bBlockNum,
+                       float alpha, float beta);
+
+/*
+ * Uniform-shape list given as HOST arrays of device pointers. Replaces
+ * _CudaBLASMatrixMULList + _CudaBLASMatrixMULBatched
+ * (source/tensor/core/arithmetic/XTensorBLAS.cu:252-387, 109-178). The planner looks
+ * for a constant stride or for the two-level (p, q) pattern of the general form and
+ * issues one launch when it finds either; any other pointer pattern is issued as one
+ * launch per problem on the same stream.
+ */
+int ntb_gemm_list(int devID, void * stream,
+                  const void * const * a, int transA, const void * const * b, int transB,
+                  void * const * c, int dtypeAB, int dtypeC,
+                  int count, int na, int ma, int nb, int mb, int nc, int mc,
+                  float alpha, float beta);
+
+/*
+ * Host-buffer form: a, b and c are HOST memory (pinned or pageable). Copies the
+ * operands (and c when beta != 0) to staging buffers owned by the device context, runs
+ * the strided-batched GEMM, copies c back and synchronises the stream. This is what a
+ * caller holding CPU tensors does through the reference with SetDevice/FlushToDevice
+ * (source/tensor/XTensor.cpp:533-539, 1992-1999) around MatrixMul. Staging buffers grow
+ * on demand and are kept until ntb_release().
+ */
+int ntb_gemm_host(int devID, void * stream,
+                  const void * a, int transA, const void * b, int transB, void * c,
+                  int dtypeAB, int dtypeC,
+                  int na, int ma, int nb, int mb, int nc, int mc,
+                  long long strideA, long long strideB, long long strideC,
+                  int count, float alpha, float beta);
+
+/* Route taken by the calling thread's most recent successful launch (NTB_ROUTE_*). */
+int ntb_last_route(void);
+
+/*
+ * Restricts routing: 0 = automatic (default), NTB_ROUTE_SIMT = always the FFMA kernel,
+ * NTB_ROUTE_TC_F16 / NTB_ROUTE_TC_3XTF32 = fail with NTB_ERR_ARG instead of using the
+ * FFMA kernel when the tensor-core route cannot address the operands. Process-wide.
+ */
+int ntb_set_route(int route);
+
+/*
+ * Synchronises `devID` and reads its status word: NTB_OK, or NTB_ERR_DEVICE_WAIT when a
+ * kernel abandoned a bounded wait since the last call (the word is cleared on read).
+ */
+int ntb_device_status(int devID);
+
+/* Number of kernels this library has launched in the process so far. */
+long long ntb_launch_count(void);
+
+/* Frees the per-device contexts (staging buffers, status words). */
+void ntb_release(void);
+
+const char * ntb_strerror(int code);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

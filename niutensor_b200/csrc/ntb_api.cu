@@ -1,0 +1,435 @@
+/*
+ * extern "C" layer: argument checks with the reference's shape rules, per-device
+ * contexts, routing between the tensor-core and the FFMA kernels, and the host-buffer
+ * entry point. See include/ntb_gemm.h for the contract of every function.
+ */
+#include "ntb_internal.h"
+#include <atomic>
+#include <mutex>
+#include <vector>
+#include <cstdlib>
+#include <cstring>
+
+namespace ntb {
+
+namespace {
+
+constexpr int MAX_DEV = 64;
+std::mutex gLock;
+DeviceCtx * gCtx[MAX_DEV] = { nullptr };
+std::atomic<long long> gLaunches(0);
+std::atomic<int> gForcedRoute(0);
+thread_local int tLastRoute = NTB_ROUTE_NONE;
+
+/* save / restore the calling thread's current device around a call */
+struct DeviceGuard {
+    int prev;
+    bool ok;
+    explicit DeviceGuard(int dev) : prev(-1), ok(false)
+    {
+        if (cudaGetDevice(&prev) != cudaSuccess)
+            return;
+        ok = (prev == dev) || cudaSetDevice(dev) == cudaSuccess;
+        if (!ok)
+            prev = -1;
+    }
+    ~DeviceGuard()
+    {
+        if (prev >= 0) {
+            int cur = -1;
+            if (cudaGetDevice(&cur) == cudaSuccess && cur != prev)
+                cudaSetDevice(prev);
+        }
+    }
+};
+
+/* caller holds the device current */
+DeviceCtx * GetCtx(int dev)
+{
+    if (dev < 0 || dev >= MAX_DEV)
+        return nullptr;
+    std::lock_guard<std::mutex> g(gLock);
+    if (gCtx[dev])
+        return gCtx[dev];
+    DeviceCtx * c = new DeviceCtx();
+    memset(c, 0, sizeof(*c));
+    c->devID = dev;
+    if (cudaDeviceGetAttribute(&c->smCount, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        cudaMalloc((void **)&c->status, sizeof(int)) != cudaSuccess ||
+        cudaMemset(c->status, 0, sizeof(int)) != cudaSuccess) {
+        cudaGetLastError();
+        delete c;
+        return nullptr;
+    }
+    gCtx[dev] = c;
+    return c;
+}
+
+int CheckDtypes(int dtAB, int dtC)
+{
+    if (dtAB == NTB_X_FLOAT16 && (dtC == NTB_X_FLOAT16 || dtC == NTB_X_FLOAT))
+        return NTB_OK;
+    if (dtAB == NTB_X_FLOAT && dtC == NTB_X_FLOAT)
+        return NTB_OK;
+    return NTB_ERR_DTYPE;
+}
+
+/* fills shape fields of a Problem from the stored extents, with the reference's checks
+   (am == bn, an == cn, bm == cm: source/tensor/core/arithmetic/MatrixMul.cpp:79-87) */
+int SetShape(Problem & p, int transA, int transB, int na, int ma, int nb, int mb, int nc, int mc)
+{
+    if ((transA != NTB_X_TRANS && transA != NTB_X_NOTRANS) || (transB != NTB_X_TRANS && transB != NTB_X_NOTRANS))
+        return NTB_ERR_ARG;
+    if (na < 0 || ma < 0 || nb < 0 || mb < 0 || nc < 0 || mc < 0)
+        return NTB_ERR_ARG;
+    const int an = transA == NTB_X_TRANS ? ma : na;
+    const int am = transA == NTB_X_TRANS ? na : ma;
+    const int bn = transB == NTB_X_TRANS ? mb : nb;
+    const int bm = transB == NTB_X_TRANS ? nb : mb;
+    if (am != bn || an != nc || bm != mc)
+        return NTB_ERR_SHAPE;
+    p.M = an; p.N = bm; p.K = am;
+    p.aMN = transA == NTB_X_TRANS;       /* stored K x M: M contiguous */
+    p.bMN = transB == NTB_X_NOTRANS;     /* stored K x N: N contiguous */
+    p.aRows = na; p.aCols = ma; p.bRows = nb; p.bCols = mb;
+    return NTB_OK;
+}
+
+int Dispatch(int devID, cudaStream_t stream, Problem & p)
+{
+    if (p.count == 0 || p.M == 0 || p.N == 0)
+        return NTB_OK;
+    if (!p.a || !p.b || !p.c)
+        return NTB_ERR_ARG;
+    DeviceGuard guard(devID);
+    if (!guard.ok) {
+        cudaGetLastError();
+        return NTB_ERR_CUDA;
+    }
+    DeviceCtx * ctx = GetCtx(devID);
+    if (!ctx)
+        return NTB_ERR_CUDA;
+    const int forced = gForcedRoute.load();
+    const bool tc = forced != NTB_ROUTE_SIMT && TcEligible(p);
+    int rc;
+    if (tc) {
+        rc = LaunchTc(*ctx, p, stream);
+        if (rc == NTB_OK)
+            tLastRoute = p.dtAB == NTB_X_FLOAT16 ? NTB_ROUTE_TC_F16 : NTB_ROUTE_TC_3XTF32;
+    }
+    else {
+        if (forced == NTB_ROUTE_TC_F16 || forced == NTB_ROUTE_TC_3XTF32)
+            return NTB_ERR_ARG;
+        rc = LaunchSimt(*ctx, p, stream);
+        if (rc == NTB_OK)
+            tLastRoute = NTB_ROUTE_SIMT;
+    }
+    return rc;
+}
+
+int GrowStage(DeviceCtx * ctx, int slot, size_t bytes)
+{
+    if (ctx->stageBytes[slot] >= bytes)
+        return NTB_OK;
+    if (ctx->stage[slot])
+        cudaFree(ctx->stage[slot]);
+    ctx->stage[slot] = nullptr;
+    ctx->stageBytes[slot] = 0;
+    if (cudaMalloc(&ctx->stage[slot], bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return NTB_ERR_CUDA;
+    }
+    ctx->stageBytes[slot] = bytes;
+    return NTB_OK;
+}
+
+}
+
+void CountLaunch()
+{
+    gLaunches.fetch_add(1);
+}
+
+EncodeTiledFn GetEncodeTiled()
+{
+    static std::atomic<EncodeTiledFn> cached(nullptr);
+    EncodeTiledFn f = cached.load();
+    if (f)
+        return f;
+    void * sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess || !sym) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    cached.store((EncodeTiledFn)sym);
+    return (EncodeTiledFn)sym;
+}
+
+}
+
+using namespace ntb;
+
+extern "C" {
+
+int ntb_gemm_strided_batched(int devID, void * stream,
+                             const void * a, int transA, const void * b, int transB, void * c,
+                             int dtypeAB, int dtypeC,
+                             int na, int ma, int nb, int mb, int nc, int mc,
+                             long long lda, long long ldb, long long ldc,
+                             long long strideA, long long strideB, long long strideC,
+                             int count, float alpha, float beta)
+{
+    Problem p;
+    memset(&p, 0, sizeof(p));
+    int rc = CheckDtypes(dtypeAB, dtypeC);
+    if (rc != NTB_OK)
+        return rc;
+    rc = SetShape(p, transA, transB, na, ma, nb, mb, nc, mc);
+    if (rc != NTB_OK)
+        return rc;
+    if (count < 0 || lda < ma || ldb < mb || ldc < mc || strideA < 0 || strideB < 0 || strideC < 0)
+        return NTB_ERR_ARG;
+    p.a = a; p.b = b; p.c = c;
+    p.dtAB = dtypeAB; p.dtC = dtypeC;
+    p.lda = lda; p.ldb = ldb; p.ldc = ldc;
+    p.count = count; p.Q = 1;
+    p.sAp = strideA; p.sBp = strideB; p.sCp = strideC;
+    p.alpha = alpha; p.beta = beta;
+    return Dispatch(devID, (cudaStream_t)stream, p);
+}
+
+int ntb_gemm(int devID, void * stream,
+             const void * a, int transA, const void * b, int transB, void * c,
+             int dtypeAB, int dtypeC,
+             int na, int ma, int nb, int mb, int nc, int mc,
+             long long lda, long long ldb, long long ldc,
+             float alpha, float beta)
+{
+    return ntb_gemm_strided_batched(devID, stream, a, transA, b, transB, c, dtypeAB, dtypeC,
+                                    na, ma, nb, mb, nc, mc, lda, ldb, ldc, 0, 0, 0, 1, alpha, beta);
+}
+
+int ntb_gemm_broadcast(int devID, void * stream,
+                       const void * a, int transA, const void * b, int transB, void * c,
+                       int dtypeAB, int dtypeC,
+                       int na, int ma, int nb, int mb, int nc, int mc,
+                       int aBlockNum, int bBlockNum,
+                       float alpha, float beta)
+{
+    Problem p;
+    memset(&p, 0, sizeof(p));
+    int rc = CheckDtypes(dtypeAB, dtypeC);
+    if (rc != NTB_OK)
+        return rc;
+    rc = SetShape(p, transA, transB, na, ma, nb, mb, nc, mc);
+    if (rc != NTB_OK)
+        return rc;
+    if (aBlockNum < 0 || bBlockNum < 0)
+        return NTB_ERR_ARG;
+    if ((long long)aBlockNum * bBlockNum > 2147483647LL)
+        return NTB_ERR_LIMIT;
+    p.a = a; p.b = b; p.c = c;
+    p.dtAB = dtypeAB; p.dtC = dtypeC;
+    p.lda = ma; p.ldb = mb; p.ldc = mc;
+    p.count = aBlockNum * bBlockNum;
+    p.Q = bBlockNum > 0 ? bBlockNum : 1;
+    p.sAp = (long long)na * ma; p.sAq = 0;
+    p.sBp = 0;                  p.sBq = (long long)nb * mb;
+    p.sCq = (long long)nc * mc; p.sCp = p.sCq * p.Q;
+    p.alpha = alpha; p.beta = beta;
+    return Dispatch(devID, (cudaStream_t)stream, p);
+}
+
+int ntb_gemm_list(int devID, void * stream,
+                  const void * const * a, int transA, const void * const * b, int transB,
+                  void * const * c, int dtypeAB, int dtypeC,
+                  int count, int na, int ma, int nb, int mb, int nc, int mc,
+                  float alpha, float beta)
+{
+    if (count < 0)
+        return NTB_ERR_ARG;
+    if (count == 0)
+        return NTB_OK;
+    if (!a || !b || !c)
+        return NTB_ERR_ARG;
+    int rc = CheckDtypes(dtypeAB, dtypeC);
+    if (rc != NTB_OK)
+        return rc;
+    const long long esAB = (long long)ElemSize(dtypeAB), esC = (long long)ElemSize(dtypeC);
+    auto gap = [](const void * x, const void * y) { return (long long)((const char *)x - (const char *)y); };
+
+    if (count == 1)
+        return ntb_gemm(devID, stream, a[0], transA, b[0], transB, c[0], dtypeAB, dtypeC,
+                        na, ma, nb, mb, nc, mc, ma, mb, mc, alpha, beta);
+
+    /* constant byte gaps -> one strided launch */
+    {
+        const long long gA = gap(a[1], a[0]), gB = gap(b[1], b[0]), gC = gap(c[1], c[0]);
+        bool strided = gA >= 0 && gB >= 0 && gC >= 0 && gA % esAB == 0 && gB % esAB == 0 && gC % esC == 0;
+        for (int i = 2; strided && i < count; i++)
+            strided = gap(a[i], a[i - 1]) == gA && gap(b[i], b[i - 1]) == gB && gap(c[i], c[i - 1]) == gC;
+        if (strided)
+            return ntb_gemm_strided_batched(devID, stream, a[0], transA, b[0], transB, c[0], dtypeAB, dtypeC,
+                                            na, ma, nb, mb, nc, mc, ma, mb, mc,
+                                            gA / esAB, gB / esAB, gC / esC, count, alpha, beta);
+    }
+    /* the (p, q) pattern of the general form: a constant over runs of Q problems, b
+       repeating with period Q, c packed */
+    {
+        int Q = 1;
+        while (Q < count && a[Q] == a[0])
+            Q++;
+        if (Q > 1 && Q < count && count % Q == 0) {
+            const int P = count / Q;
+            const long long aBytes = (long long)na * ma * esAB, bBytes = (long long)nb * mb * esAB,
+                            cBytes = (long long)nc * mc * esC;
+            bool match = true;
+            for (int i = 0; match && i < count; i++) {
+                const int pIdx = i / Q, qIdx = i % Q;
+                match = gap(a[i], a[0]) == pIdx * aBytes && gap(b[i], b[0]) == qIdx * bBytes &&
+                        gap(c[i], c[0]) == i * cBytes;
+            }
+            if (match)
+                return ntb_gemm_broadcast(devID, stream, a[0], transA, b[0], transB, c[0], dtypeAB, dtypeC,
+                                          na, ma, nb, mb, nc, mc, P, Q, alpha, beta);
+        }
+    }
+    for (int i = 0; i < count; i++) {
+        rc = ntb_gemm(devID, stream, a[i], transA, b[i], transB, c[i], dtypeAB, dtypeC,
+                      na, ma, nb, mb, nc, mc, ma, mb, mc, alpha, beta);
+        if (rc != NTB_OK)
+            return rc;
+    }
+    return NTB_OK;
+}
+
+int ntb_gemm_host(int devID, void * stream,
+                  const void * a, int transA, const void * b, int transB, void * c,
+                  int dtypeAB, int dtypeC,
+                  int na, int ma, int nb, int mb, int nc, int mc,
+                  long long strideA, long long strideB, long long strideC,
+                  int count, float alpha, float beta)
+{
+    if (!a || !b || !c || count < 0 || na < 0 || ma < 0 || nb < 0 || mb < 0 || nc < 0 || mc < 0)
+        return NTB_ERR_ARG;
+    int rc = CheckDtypes(dtypeAB, dtypeC);
+    if (rc != NTB_OK)
+        return rc;
+    if (count == 0)
+        return NTB_OK;
+    DeviceGuard guard(devID);
+    if (!guard.ok) {
+        cudaGetLastError();
+        return NTB_ERR_CUDA;
+    }
+    DeviceCtx * ctx = GetCtx(devID);
+    if (!ctx)
+        return NTB_ERR_CUDA;
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t esAB = ElemSize(dtypeAB), esC = ElemSize(dtypeC);
+    /* a stride of 0 shares one matrix; otherwise `count` matrices at the given stride */
+    const size_t aBytes = ((size_t)(strideA ? strideA * (count - 1) : 0) + (size_t)na * ma) * esAB;
+    const size_t bBytes = ((size_t)(strideB ? strideB * (count - 1) : 0) + (size_t)nb * mb) * esAB;
+    const size_t cBytes = ((size_t)(strideC ? strideC * (count - 1) : 0) + (size_t)nc * mc) * esC;
+    {
+        std::lock_guard<std::mutex> g(gLock);
+        if (GrowStage(ctx, 0, aBytes) != NTB_OK || GrowStage(ctx, 1, bBytes) != NTB_OK ||
+            GrowStage(ctx, 2, cBytes) != NTB_OK)
+            return NTB_ERR_CUDA;
+    }
+    if (cudaMemcpyAsync(ctx->stage[0], a, aBytes, cudaMemcpyHostToDevice, st) != cudaSuccess ||
+        cudaMemcpyAsync(ctx->stage[1], b, bBytes, cudaMemcpyHostToDevice, st) != cudaSuccess)
+        return NTB_ERR_CUDA;
+    if (beta != 0.f && cudaMemcpyAsync(ctx->stage[2], c, cBytes, cudaMemcpyHostToDevice, st) != cudaSuccess)
+        return NTB_ERR_CUDA;
+    rc = ntb_gemm_strided_batched(devID, stream, ctx->stage[0], transA, ctx->stage[1], transB, ctx->stage[2],
+                                  dtypeAB, dtypeC, na, ma, nb, mb, nc, mc, ma, mb, mc,
+                                  strideA, strideB, strideC, count, alpha, beta);
+    if (rc != NTB_OK)
+        return rc;
+    if (cudaMemcpyAsync(c, ctx->stage[2], cBytes, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+        cudaStreamSynchronize(st) != cudaSuccess) {
+        cudaGetLastError();
+        return NTB_ERR_CUDA;
+    }
+    return NTB_OK;
+}
+
+int ntb_last_route(void)
+{
+    return tLastRoute;
+}
+
+int ntb_set_route(int route)
+{
+    if (route != 0 && route != NTB_ROUTE_SIMT && route != NTB_ROUTE_TC_F16 && route != NTB_ROUTE_TC_3XTF32)
+        return NTB_ERR_ARG;
+    gForcedRoute.store(route);
+    return NTB_OK;
+}
+
+int ntb_device_status(int devID)
+{
+    DeviceGuard guard(devID);
+    if (!guard.ok) {
+        cudaGetLastError();
+        return NTB_ERR_CUDA;
+    }
+    DeviceCtx * ctx = GetCtx(devID);
+    if (!ctx)
+        return NTB_ERR_CUDA;
+    int v = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess ||
+        cudaMemcpy(&v, ctx->status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) {
+        cudaGetLastError();
+        return NTB_ERR_CUDA;
+    }
+    if (v != 0)
+        cudaMemset(ctx->status, 0, sizeof(int));
+    return v;
+}
+
+long long ntb_launch_count(void)
+{
+    return gLaunches.load();
+}
+
+void ntb_release(void)
+{
+    std::lock_guard<std::mutex> g(gLock);
+    for (int d = 0; d < MAX_DEV; d++) {
+        DeviceCtx * c = gCtx[d];
+        if (!c)
+            continue;
+        int prev = -1;
+        cudaGetDevice(&prev);
+        if (cudaSetDevice(d) == cudaSuccess) {
+            for (int s = 0; s < 3; s++)
+                if (c->stage[s])
+                    cudaFree(c->stage[s]);
+            cudaFree(c->status);
+        }
+        if (prev >= 0)
+            cudaSetDevice(prev);
+        delete c;
+        gCtx[d] = nullptr;
+    }
+}
+
+const char * ntb_strerror(int code)
+{
+    switch (code) {
+    case NTB_OK: return "ok";
+    case NTB_ERR_ARG: return "bad argument";
+    case NTB_ERR_SHAPE: return "unmatched tensors in multiplication";
+    case NTB_ERR_DTYPE: return "unsupported data type";
+    case NTB_ERR_CUDA: return "CUDA call failed or no usable device";
+    case NTB_ERR_DEVICE_WAIT: return "a bounded wait on the device ran out";
+    case NTB_ERR_LIMIT: return "size beyond a fixed limit";
+    default: return "unknown error";
+    }
+}
+
+}

@@ -1,0 +1,57 @@
+/* Internal declarations shared by the API layer and the kernel launchers. */
+#ifndef NTB_INTERNAL_H
+#define NTB_INTERNAL_H
+
+#include <cuda_runtime.h>
+#include <cuda.h>
+#include <stdint.h>
+#include "../../include/ntb_gemm.h"
+
+namespace ntb {
+
+/*
+ * One launch: `count` problems of one shape. Problem i splits into (p, q) =
+ * (i / Q, i % Q); operand x of problem i starts at x + p * sXp + q * sXq (elements).
+ *   strided batched: Q = 1, sXp = strideX
+ *   general form   : Q = bBlockNum, A walks p, B walks q, C walks p * Q + q
+ */
+struct Problem {
+    const void * a;
+    const void * b;
+    void * c;
+    int dtAB, dtC;          /* NTB_X_FLOAT / NTB_X_FLOAT16 */
+    int aMN, bMN;           /* operand is MN-major (M resp. N contiguous) instead of K-major */
+    int M, N, K;
+    int aRows, aCols, bRows, bCols;   /* stored extents */
+    long long lda, ldb, ldc;
+    int count, Q;
+    long long sAp, sAq, sBp, sBq, sCp, sCq;
+    float alpha, beta;
+};
+
+struct DeviceCtx {
+    int devID;
+    int smCount;
+    int * status;           /* device word written by a kernel that gave up a wait */
+    void * stage[3];        /* host-buffer entry point: device staging for a, b, c */
+    size_t stageBytes[3];
+};
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn GetEncodeTiled();
+
+/* true when the tcgen05/TMA route can address this problem (alignment, strides) */
+bool TcEligible(const Problem & p);
+int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream);
+int LaunchSimt(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream);
+
+void CountLaunch();
+
+static inline size_t ElemSize(int dt) { return dt == NTB_X_FLOAT16 ? 2 : 4; }
+
+}
+
+#endif

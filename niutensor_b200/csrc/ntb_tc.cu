@@ -1,0 +1,736 @@
+/*
+ * Tensor-core route for sm_100a: a persistent, warp-specialised GEMM built directly on
+ * tcgen05.mma with accumulators in tensor memory (TMEM) and operands brought into
+ * 128-byte-swizzled shared memory by TMA (cp.async.bulk.tensor, no cluster multicast).
+ *
+ *   warp 0      TMA producer: one lane arms full[s] with the stage's byte count and
+ *               issues the A and B boxes of k-block kb into stage s.
+ *   warp 1      owns TMEM (tcgen05.alloc / dealloc); one lane issues the tcgen05.mma
+ *               instructions of a stage and commits them to empty[s]; after the last
+ *               k-block of a tile it commits to tfull[buf].
+ *   warps 2-5   epilogue: tcgen05.ld of the finished accumulator (each warp reads the 32
+ *               TMEM lanes of its sub-partition), alpha/beta, cast, stores to C, then
+ *               release of the accumulator through tempty[buf]. Two accumulators
+ *               alternate, so the epilogue of tile i overlaps the main loop of tile i+1.
+ *   warps 6-9   (fp32 inputs only) split every fp32 operand value x in shared memory
+ *               into hi = tf32(x) and lo = x - hi; the MMA lane then issues three
+ *               kind::tf32 products per k-step, lo*hi + hi*lo + hi*hi, small terms first.
+ *
+ * One CTA per SM walks output tiles tile = blockIdx.x + i * gridDim.x over
+ * (problem, mBlock, nBlock); all problems of a batched / broadcast call are covered by
+ * this one launch, base addresses coming from the problem index.
+ *
+ * Every wait on an mbarrier is bounded: when the limit passes, the waiter raises the
+ * CTA's abort flag, records NTB_ERR_DEVICE_WAIT in the device status word, and every role
+ * leaves its loop; the CTA then lets copies in flight land, frees its TMEM and returns.
+ */
+#include "ntb_internal.h"
+#include <cuda_fp16.h>
+
+namespace ntb {
+
+namespace {
+
+constexpr int BM = 128;             /* rows of an output tile = UMMA M = TMEM lanes */
+constexpr int ROW_BYTES = 128;      /* one swizzle row: 64 halves or 32 floats of K (or MN) */
+constexpr int A_TILE_BYTES = BM * ROW_BYTES;
+constexpr int UMMA_K_BYTES = 32;    /* K extent of one tcgen05.mma: 16 halves / 8 tf32 */
+constexpr int FP32_CHUNK_BLOCKS = 8;  /* fp32 route: 8 k-blocks = 256 of K per TMEM accumulation chain */
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;   /* about two seconds */
+
+struct TcParams {
+    void * c;
+    long long ldc, sCp, sCq;
+    int M, N, K, count, Q;
+    int aSel, bSel;         /* which index walks the operand's batch dimension: 0 none, 1 p, 2 q, 3 i */
+    int aMN, bMN;
+    int tilesM, tilesN;
+    long long totalTiles;
+    int cVec;               /* C rows can be accessed with 16-byte vectors */
+    float alpha, beta;
+    int * status;
+};
+
+/* ---------------------------------------------------------------- PTX wrappers */
+
+__device__ __forceinline__ uint32_t SmemAddr(const void * p)
+{
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void MbarInit(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void MbarExpectTx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void MbarArrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ uint32_t MbarTryWait(uint32_t bar, uint32_t parity)
+{
+    uint32_t done;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done;
+}
+
+/* Bounded wait. Returns false when the CTA is aborting (this waiter ran out of time, or
+   another one did). */
+__device__ __forceinline__ bool MbarWait(uint32_t bar, uint32_t parity, volatile int * abortFlag, int * status)
+{
+    if (MbarTryWait(bar, parity))
+        return true;
+    const long long t0 = clock64();
+    for (uint32_t it = 1; ; ++it) {
+        if (MbarTryWait(bar, parity))
+            return true;
+        if ((it & 255u) == 0) {
+            if (*abortFlag)
+                return false;
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                *abortFlag = 1;
+                atomicExch(status, NTB_ERR_DEVICE_WAIT);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void TmaLoad3D(uint32_t dst, const CUtensorMap * map, uint32_t bar, int c0, int c1, int c2)
+{
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+                 " [%0], [%1, {%3, %4, %5}], [%2];"
+                 :: "r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
+__device__ __forceinline__ void TcFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void TcFenceAfter()  { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void TcCommit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
+}
+
+template <int MODE>
+__device__ __forceinline__ void TcMma(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc, uint32_t iDesc, uint32_t accumulate)
+{
+    if (MODE == 0) {
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                     "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                     :: "r"(dTmem), "l"(aDesc), "l"(bDesc), "r"(iDesc), "r"(accumulate) : "memory");
+    }
+    else {
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                     "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                     :: "r"(dTmem), "l"(aDesc), "l"(bDesc), "r"(iDesc), "r"(accumulate) : "memory");
+    }
+}
+
+/* 32 consecutive fp32 columns of this thread's TMEM lane */
+__device__ __forceinline__ void TmemLoad32(uint32_t taddr, float * v)
+{
+    uint32_t r[32];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; i++)
+        v[i] = __uint_as_float(r[i]);
+}
+
+/*
+ * Shared-memory matrix descriptor of tcgen05.mma: start address, leading and stride byte
+ * offsets in 16-byte units, descriptor version 1, and the swizzle code: 2 = 128-byte
+ * swizzle of 16-byte chunks, 1 = 128-byte swizzle of 32-byte chunks (the only swizzled
+ * layout the tensor core accepts for MN-major 32-bit operands).
+ */
+__device__ __forceinline__ uint64_t SmemDesc(uint32_t addr, uint32_t lboBytes, uint32_t sboBytes, uint32_t layout)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lboBytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sboBytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)layout << 61;
+    return d;
+}
+
+/* Instruction descriptor: fp32 accumulate, operand format, majors, N >> 3, M >> 4. */
+__host__ __device__ constexpr uint32_t InstrDesc(int mode, int aMN, int bMN, int n)
+{
+    return (1u << 4)                                  /* D format: F32 */
+         | ((mode == 0 ? 0u : 2u) << 7)               /* A format: F16 = 0, TF32 = 2 */
+         | ((mode == 0 ? 0u : 2u) << 10)              /* B format */
+         | ((uint32_t)(aMN ? 1 : 0) << 15)
+         | ((uint32_t)(bMN ? 1 : 0) << 16)
+         | ((uint32_t)(n >> 3) << 17)
+         | ((uint32_t)(BM >> 4) << 24);
+}
+
+/* ---------------------------------------------------------------- epilogue helpers */
+
+template <typename OutT> struct Vec16;
+template <> struct Vec16<__half> { static constexpr int N = 8; };
+template <> struct Vec16<float>  { static constexpr int N = 4; };
+
+__device__ __forceinline__ void StoreVec(__half * dst, const float * v)
+{
+    uint4 u;
+    __half2 h0 = __floats2half2_rn(v[0], v[1]);
+    __half2 h1 = __floats2half2_rn(v[2], v[3]);
+    __half2 h2 = __floats2half2_rn(v[4], v[5]);
+    __half2 h3 = __floats2half2_rn(v[6], v[7]);
+    u.x = *(uint32_t *)&h0; u.y = *(uint32_t *)&h1; u.z = *(uint32_t *)&h2; u.w = *(uint32_t *)&h3;
+    *(uint4 *)dst = u;
+}
+__device__ __forceinline__ void StoreVec(float * dst, const float * v)
+{
+    *(float4 *)dst = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void LoadVec(const __half * src, float * v)
+{
+    uint4 u = *(const uint4 *)src;
+    float2 f;
+    f = __half22float2(*(__half2 *)&u.x); v[0] = f.x; v[1] = f.y;
+    f = __half22float2(*(__half2 *)&u.y); v[2] = f.x; v[3] = f.y;
+    f = __half22float2(*(__half2 *)&u.z); v[4] = f.x; v[5] = f.y;
+    f = __half22float2(*(__half2 *)&u.w); v[6] = f.x; v[7] = f.y;
+}
+__device__ __forceinline__ void LoadVec(const float * src, float * v)
+{
+    float4 f = *(const float4 *)src;
+    v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+}
+__device__ __forceinline__ float LoadOne(const __half * p) { return __half2float(*p); }
+__device__ __forceinline__ float LoadOne(const float * p) { return *p; }
+__device__ __forceinline__ void StoreOne(__half * p, float v) { *p = __float2half_rn(v); }
+__device__ __forceinline__ void StoreOne(float * p, float v) { *p = v; }
+
+/* alpha * v (+ beta * old) for 32 consecutive columns of one output row starting at
+   column c0, written with 16-byte vectors where the row allows it, element by element
+   at a ragged edge or for rows that are not 16-byte aligned */
+template <typename OutT>
+__device__ __forceinline__ void StoreRow32(OutT * cRow, int c0, float * v, const TcParams & p)
+{
+    constexpr int VN = Vec16<OutT>::N;
+#pragma unroll
+    for (int g = 0; g < 32 / VN; g++) {
+        const int c = c0 + g * VN;
+        float * vv = v + g * VN;
+        if (p.cVec && c + VN <= p.N) {
+            if (p.beta != 0.f) {
+                float old[VN];
+                LoadVec(cRow + c, old);
+#pragma unroll
+                for (int e = 0; e < VN; e++)
+                    vv[e] = fmaf(p.beta, old[e], p.alpha * vv[e]);
+            }
+            else {
+#pragma unroll
+                for (int e = 0; e < VN; e++)
+                    vv[e] = p.alpha * vv[e];
+            }
+            StoreVec(cRow + c, vv);
+        }
+        else {
+#pragma unroll
+            for (int e = 0; e < VN; e++) {
+                if (c + e < p.N) {
+                    float x = p.alpha * vv[e];
+                    if (p.beta != 0.f)
+                        x = fmaf(p.beta, LoadOne(cRow + c + e), x);
+                    StoreOne(cRow + c + e, x);
+                }
+            }
+        }
+    }
+}
+
+/* ---------------------------------------------------------------- tile walk */
+
+struct TileCoord {
+    int prob, mBlk, nBlk;
+};
+
+/* Tiles of one problem are visited in bands of 8 m-blocks, n fastest inside a band's
+   column, so the CTAs running at the same time share A row panels and B column panels
+   in L2. */
+__device__ __forceinline__ TileCoord DecodeTile(long long t, int tilesM, int tilesN)
+{
+    const int perProb = tilesM * tilesN;
+    TileCoord tc;
+    tc.prob = (int)(t / perProb);
+    int r = (int)(t % perProb);
+    const int GROUP = 8;
+    int band = r / (GROUP * tilesN);
+    int first = band * GROUP;
+    int rows = min(tilesM - first, GROUP);
+    int inBand = r % (GROUP * tilesN);
+    tc.mBlk = first + inBand % rows;
+    tc.nBlk = inBand / rows;
+    return tc;
+}
+
+__device__ __forceinline__ int BatchCoord(int sel, int prob, int Q)
+{
+    return sel == 1 ? prob / Q : sel == 2 ? prob % Q : sel == 3 ? prob : 0;
+}
+
+/* ---------------------------------------------------------------- the kernel */
+
+template <int MODE, int BN, int STAGES, typename OutT>
+__global__ void __launch_bounds__(MODE == 0 ? 192 : 320, 1)
+GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, TcParams p)
+{
+    constexpr int ES = MODE == 0 ? 2 : 4;               /* operand element size */
+    constexpr int EPR = ROW_BYTES / ES;                 /* elements per 128-byte row = K per stage */
+    constexpr int B_TILE_BYTES = BN * ROW_BYTES;
+    constexpr int PLANE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+    constexpr int STAGE_BYTES = PLANE_BYTES * (MODE == 0 ? 1 : 2);   /* fp32: hi plane + lo plane */
+    constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;             /* two accumulators; power of two */
+    constexpr int KSTEPS = ROW_BYTES / UMMA_K_BYTES;                 /* 4 */
+    static_assert(BN == 64 || BN == 128 || BN == 256, "tile width");
+
+    extern __shared__ uint8_t smemRaw[];
+    __shared__ __align__(8) uint64_t barFull[STAGES];
+    __shared__ __align__(8) uint64_t barEmpty[STAGES];
+    __shared__ __align__(8) uint64_t barConv[STAGES];
+    __shared__ __align__(8) uint64_t barTFull[2];
+    __shared__ __align__(8) uint64_t barTEmpty[2];
+    __shared__ uint32_t tmemBaseSlot;
+    __shared__ int abortFlag;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t smemBase = (SmemAddr(smemRaw) + 1023u) & ~1023u;
+    volatile int * abortPtr = &abortFlag;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            MbarInit(SmemAddr(&barFull[s]), 1);
+            MbarInit(SmemAddr(&barEmpty[s]), 1);
+            MbarInit(SmemAddr(&barConv[s]), 128);
+        }
+        for (int b = 0; b < 2; b++) {
+            MbarInit(SmemAddr(&barTFull[b]), 1);
+            MbarInit(SmemAddr(&barTEmpty[b]), 4);
+        }
+        abortFlag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     :: "r"(SmemAddr(&tmemBaseSlot)), "r"((uint32_t)TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    TcFenceBefore();
+    __syncthreads();
+    TcFenceAfter();
+    const uint32_t tmemBase = *(volatile uint32_t *)&tmemBaseSlot;
+
+    const int kBlocks = (p.K + EPR - 1) / EPR;
+    /* k-blocks accumulated in TMEM before the partial sum is handed to the epilogue */
+    const int chunkBlocks = MODE == 0 ? kBlocks : FP32_CHUNK_BLOCKS;
+    const long long firstTile = blockIdx.x;
+    const long long tileStep = gridDim.x;
+
+    if (warp == 0) {
+        /* ------------------------------------------------------------ TMA producer */
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (long long t = firstTile; ok && t < p.totalTiles; t += tileStep) {
+                TileCoord tc = DecodeTile(t, p.tilesM, p.tilesN);
+                const int m0 = tc.mBlk * BM, n0 = tc.nBlk * BN;
+                const int ba = BatchCoord(p.aSel, tc.prob, p.Q);
+                const int bb = BatchCoord(p.bSel, tc.prob, p.Q);
+                for (int kb = 0; kb < kBlocks; kb++) {
+                    ok = MbarWait(SmemAddr(&barEmpty[s]), ph ^ 1u, abortPtr, p.status);
+                    if (!ok)
+                        break;
+                    const uint32_t full = SmemAddr(&barFull[s]);
+                    const uint32_t aDst = smemBase + s * STAGE_BYTES;
+                    const uint32_t bDst = aDst + A_TILE_BYTES;
+                    const int k0 = kb * EPR;
+                    MbarExpectTx(full, PLANE_BYTES);
+                    if (!p.aMN) {
+                        TmaLoad3D(aDst, &tmA, full, k0, m0, ba);
+                    }
+                    else {
+#pragma unroll
+                        for (int j = 0; j < BM / EPR; j++)
+                            TmaLoad3D(aDst + j * EPR * ROW_BYTES, &tmA, full, m0 + j * EPR, k0, ba);
+                    }
+                    if (!p.bMN) {
+                        TmaLoad3D(bDst, &tmB, full, k0, n0, bb);
+                    }
+                    else {
+#pragma unroll
+                        for (int j = 0; j < BN / EPR; j++)
+                            TmaLoad3D(bDst + j * EPR * ROW_BYTES, &tmB, full, n0 + j * EPR, k0, bb);
+                    }
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    }
+    else if (warp == 1) {
+        /* ------------------------------------------------------------ MMA issuer */
+        if (lane == 0) {
+            const uint32_t iDesc = InstrDesc(MODE, p.aMN, p.bMN, BN);
+            /* K-major: rows of 128 B, 8-row groups 1024 B apart, k-step = 32 B along the row.
+               MN-major: boxes of EPR k-rows x 128 B; 64- (or 32-) element MN chunks are
+               EPR*128 B apart (leading offset), 8-k-row groups 1024 B apart (stride offset),
+               k-step = UMMA_K k-rows. */
+            const uint32_t aLbo = p.aMN ? EPR * ROW_BYTES : 16, bLbo = p.bMN ? EPR * ROW_BYTES : 16;
+            const uint32_t mnStep = (UMMA_K_BYTES / ES) * ROW_BYTES;
+            const uint32_t aStep = p.aMN ? mnStep : UMMA_K_BYTES;
+            const uint32_t bStep = p.bMN ? mnStep : UMMA_K_BYTES;
+            /* MN-major fp32 tiles are loaded with the 32-byte-chunk swizzle, whose pattern
+               repeats every 4 k-rows (512 B) instead of every 8 */
+            const uint32_t aLay = (MODE != 0 && p.aMN) ? 1u : 2u, bLay = (MODE != 0 && p.bMN) ? 1u : 2u;
+            const uint32_t aSbo = (MODE != 0 && p.aMN) ? 512u : 1024u, bSbo = (MODE != 0 && p.bMN) ? 512u : 1024u;
+            int s = 0;
+            uint32_t ph = 0;
+            uint32_t it = 0;                      /* accumulator hand-overs so far */
+            bool ok = true;
+            for (long long t = firstTile; ok && t < p.totalTiles; t += tileStep) {
+                for (int kb0 = 0; ok && kb0 < kBlocks; kb0 += chunkBlocks, ++it) {
+                    const uint32_t buf = it & 1u;
+                    ok = MbarWait(SmemAddr(&barTEmpty[buf]), ((it >> 1) & 1u) ^ 1u, abortPtr, p.status);
+                    if (!ok)
+                        break;
+                    TcFenceAfter();
+                    const uint32_t dTmem = tmemBase + buf * BN;
+                    const int kbEnd = min(kBlocks, kb0 + chunkBlocks);
+                    for (int kb = kb0; kb < kbEnd; kb++) {
+                        ok = MbarWait(SmemAddr(MODE == 0 ? &barFull[s] : &barConv[s]), ph, abortPtr, p.status);
+                        if (!ok)
+                            break;
+                        TcFenceAfter();
+                        const uint32_t aHi = smemBase + s * STAGE_BYTES;
+                        const uint32_t bHi = aHi + A_TILE_BYTES;
+#pragma unroll
+                        for (int k = 0; k < KSTEPS; k++) {
+                            const uint64_t aD = SmemDesc(aHi + k * aStep, aLbo, aSbo, aLay);
+                            const uint64_t bD = SmemDesc(bHi + k * bStep, bLbo, bSbo, bLay);
+                            const uint32_t acc = (kb != kb0 || k != 0) ? 1u : 0u;
+                            if (MODE == 0) {
+                                TcMma<MODE>(dTmem, aD, bD, iDesc, acc);
+                            }
+                            else {
+                                const uint64_t aL = SmemDesc(aHi + PLANE_BYTES + k * aStep, aLbo, aSbo, aLay);
+                                const uint64_t bL = SmemDesc(bHi + PLANE_BYTES + k * bStep, bLbo, bSbo, bLay);
+                                TcMma<MODE>(dTmem, aL, bD, iDesc, acc);
+                                TcMma<MODE>(dTmem, aD, bL, iDesc, 1u);
+                                TcMma<MODE>(dTmem, aD, bD, iDesc, 1u);
+                            }
+                        }
+                        TcCommit(SmemAddr(&barEmpty[s]));
+                        if (++s == STAGES) { s = 0; ph ^= 1u; }
+                    }
+                    if (ok)
+                        TcCommit(SmemAddr(&barTFull[buf]));
+                }
+            }
+        }
+    }
+    else if (warp < 6) {
+        /* ------------------------------------------------------------ epilogue */
+        const int sub = warp & 3;                 /* TMEM sub-partition this warp may read */
+        uint32_t it = 0;
+        bool ok = true;
+        for (long long t = firstTile; ok && t < p.totalTiles; t += tileStep) {
+            TileCoord tc = DecodeTile(t, p.tilesM, p.tilesN);
+            const int row = tc.mBlk * BM + sub * 32 + lane;
+            const int n0 = tc.nBlk * BN;
+            const int pp = tc.prob / p.Q, qq = tc.prob % p.Q;
+            OutT * cRow = (OutT *)p.c + pp * p.sCp + qq * p.sCq + (long long)row * p.ldc;
+            const bool rowOk = row < p.M;
+            if (MODE == 0) {
+                /* one accumulator hand-over per tile: load 32 columns, scale, store */
+                const uint32_t buf = it & 1u;
+                ok = MbarWait(SmemAddr(&barTFull[buf]), (it >> 1) & 1u, abortPtr, p.status);
+                if (!ok)
+                    break;
+                TcFenceAfter();
+                const uint32_t tRow = tmemBase + ((uint32_t)(sub * 32) << 16) + buf * BN;
+#pragma unroll 1
+                for (int ch = 0; ch < BN / 32; ch++) {
+                    const int c0 = n0 + ch * 32;
+                    if (c0 >= p.N)
+                        break;                     /* uniform across the warp */
+                    float v[32];
+                    TmemLoad32(tRow + ch * 32, v);
+                    if (rowOk)
+                        StoreRow32(cRow, c0, v, p);
+                }
+                TcFenceBefore();
+                __syncwarp();
+                if (lane == 0)
+                    MbarArrive(SmemAddr(&barTEmpty[buf]));
+                ++it;
+            }
+            else {
+                /* fp32 inputs: the tensor core truncates its fp32 accumulator after every
+                   instruction, an error that grows with the length of the accumulation
+                   chain. K is therefore cut into chunks of chunkBlocks k-blocks; each
+                   chunk's partial sum is handed over here and added, with round-to-nearest
+                   FADDs, to a running sum kept in registers. */
+                constexpr int ACC_N = MODE == 0 ? 32 : BN;
+                float acc[ACC_N];
+                for (int kb0 = 0; ok && kb0 < kBlocks; kb0 += chunkBlocks, ++it) {
+                    const uint32_t buf = it & 1u;
+                    ok = MbarWait(SmemAddr(&barTFull[buf]), (it >> 1) & 1u, abortPtr, p.status);
+                    if (!ok)
+                        break;
+                    TcFenceAfter();
+                    const uint32_t tRow = tmemBase + ((uint32_t)(sub * 32) << 16) + buf * BN;
+#pragma unroll
+                    for (int ch = 0; ch < ACC_N / 32; ch++) {
+                        float v[32];
+                        TmemLoad32(tRow + ch * 32, v);
+                        if (kb0 == 0) {
+#pragma unroll
+                            for (int e = 0; e < 32; e++)
+                                acc[ch * 32 + e] = v[e];
+                        }
+                        else {
+#pragma unroll
+                            for (int e = 0; e < 32; e++)
+                                acc[ch * 32 + e] += v[e];
+                        }
+                    }
+                    TcFenceBefore();
+                    __syncwarp();
+                    if (lane == 0)
+                        MbarArrive(SmemAddr(&barTEmpty[buf]));
+                }
+                if (ok && rowOk) {
+#pragma unroll
+                    for (int ch = 0; ch < ACC_N / 32; ch++) {
+                        const int c0 = n0 + ch * 32;
+                        if (c0 < p.N)
+                            StoreRow32(cRow, c0, acc + ch * 32, p);
+                    }
+                }
+            }
+        }
+    }
+    else if (MODE != 0) {
+        /* ------------------------------------------------------------ fp32 hi/lo split */
+        const int ct = threadIdx.x - 192;         /* 0..127 */
+        int s = 0;
+        uint32_t ph = 0;
+        bool ok = true;
+        for (long long t = firstTile; ok && t < p.totalTiles; t += tileStep) {
+            for (int kb = 0; kb < kBlocks; kb++) {
+                ok = MbarWait(SmemAddr(&barFull[s]), ph, abortPtr, p.status);
+                if (!ok)
+                    break;
+                uint8_t * hi = smemRaw + (smemBase - SmemAddr(smemRaw)) + s * STAGE_BYTES;
+                uint8_t * lo = hi + PLANE_BYTES;
+#pragma unroll 4
+                for (int i = ct; i < PLANE_BYTES / 16; i += 128) {
+                    float4 x = *(float4 *)(hi + i * 16);
+                    float4 h, l;
+                    uint32_t u;
+                    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x.x)); h.x = __uint_as_float(u); l.x = x.x - h.x;
+                    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x.y)); h.y = __uint_as_float(u); l.y = x.y - h.y;
+                    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x.z)); h.z = __uint_as_float(u); l.z = x.z - h.z;
+                    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x.w)); h.w = __uint_as_float(u); l.w = x.w - h.w;
+                    *(float4 *)(hi + i * 16) = h;
+                    *(float4 *)(lo + i * 16) = l;
+                }
+                /* make the generic-proxy stores visible to the tensor core's async-proxy reads */
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                MbarArrive(SmemAddr(&barConv[s]));
+                if (++s == STAGES) { s = 0; ph ^= 1u; }
+            }
+        }
+    }
+
+    /* ---------------------------------------------------------------- teardown */
+    __syncwarp();
+    if (*abortPtr) {
+        /* give copies and MMAs in flight time to land before shared memory and TMEM go away */
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) { }
+    }
+    TcFenceBefore();
+    __syncthreads();
+    TcFenceAfter();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                     :: "r"(tmemBase), "r"((uint32_t)TMEM_COLS) : "memory");
+    }
+}
+
+/* ---------------------------------------------------------------- host side */
+
+/* offset of operand x for problem i is idx * stride with idx in {p, q, i}; find which */
+bool BatchSelector(long long sp, long long sq, int P, int Q, int * sel, long long * stride, int * extent)
+{
+    if (sp == 0 && sq == 0) { *sel = 0; *stride = 0; *extent = 1; return true; }
+    if (sq == 0 || Q == 1)  { *sel = 1; *stride = sp; *extent = P; if (sp == 0) { *sel = 0; *extent = 1; } return true; }
+    if (sp == 0 || P == 1)  { *sel = 2; *stride = sq; *extent = Q; return true; }
+    if (sp == sq * Q)       { *sel = 3; *stride = sq; *extent = P * Q; return true; }
+    return false;
+}
+
+template <int MODE, int BN, int STAGES, typename OutT>
+int LaunchOne(const CUtensorMap & tmA, const CUtensorMap & tmB, const TcParams & tp, int grid, cudaStream_t stream)
+{
+    constexpr int ES = MODE == 0 ? 2 : 4;
+    (void)ES;
+    constexpr int stage = (A_TILE_BYTES + BN * ROW_BYTES) * (MODE == 0 ? 1 : 2);
+    constexpr int smem = stage * STAGES + 1024;
+    auto kern = GemmTcKernel<MODE, BN, STAGES, OutT>;
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return NTB_ERR_CUDA;
+        configured[dev] = true;
+    }
+    kern<<<grid, MODE == 0 ? 192 : 320, smem, stream>>>(tmA, tmB, tp);
+    CountLaunch();
+    return cudaGetLastError() == cudaSuccess ? NTB_OK : NTB_ERR_CUDA;
+}
+
+int EncodeOperand(CUtensorMap * map, int mode, const void * base, int mnMajor, int rows, int cols,
+                  long long ld, long long batchStride, int batchExtent, int tileRows)
+{
+    EncodeTiledFn enc = GetEncodeTiled();
+    if (!enc)
+        return NTB_ERR_CUDA;
+    const int es = mode == 0 ? 2 : 4;
+    const int epr = ROW_BYTES / es;
+    cuuint64_t dims[3] = { (cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batchExtent };
+    cuuint64_t strides[2] = { (cuuint64_t)ld * es,
+                              (cuuint64_t)(batchExtent > 1 ? batchStride : (long long)rows * ld) * es };
+    /* K-major: the stored row is K -> box = 128 bytes of K x tileRows rows.
+       MN-major: the stored row is M (or N) -> box = 128 bytes of MN x one stage of K rows. */
+    cuuint32_t box[3] = { (cuuint32_t)epr, (cuuint32_t)(mnMajor ? epr : tileRows), 1 };
+    cuuint32_t estr[3] = { 1, 1, 1 };
+    CUresult r = enc(map, mode == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                     3, (void *)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     (mode != 0 && mnMajor) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? NTB_OK : NTB_ERR_CUDA;
+}
+
+/* cost model: waves of tiles over the SMs times the tile's width, plus a fixed per-tile cost */
+int PickBN(const Problem & p, int smCount, int mode)
+{
+    const int cand[3] = { 256, 128, 64 };
+    int best = 128;
+    double bestCost = 1e300;
+    for (int i = (mode == 0 ? 0 : 1); i < 3; i++) {
+        int bn = cand[i];
+        long long tiles = (long long)((p.M + BM - 1) / BM) * ((p.N + bn - 1) / bn) * p.count;
+        long long waves = (tiles + smCount - 1) / smCount;
+        double cost = (double)waves * (bn + 24);
+        if (cost < bestCost) { bestCost = cost; best = bn; }
+    }
+    return best;
+}
+
+}
+
+bool TcEligible(const Problem & p)
+{
+    if (p.M <= 0 || p.N <= 0 || p.K <= 0 || p.count <= 0)
+        return false;
+    const bool f16 = p.dtAB == NTB_X_FLOAT16 && (p.dtC == NTB_X_FLOAT16 || p.dtC == NTB_X_FLOAT);
+    const bool f32 = p.dtAB == NTB_X_FLOAT && p.dtC == NTB_X_FLOAT;
+    if (!f16 && !f32)
+        return false;
+    const long long es = ElemSize(p.dtAB);
+    if (((uintptr_t)p.a & 15) || ((uintptr_t)p.b & 15))
+        return false;
+    if ((p.lda * es) % 16 || (p.ldb * es) % 16)
+        return false;
+    if ((p.sAp * es) % 16 || (p.sAq * es) % 16 || (p.sBp * es) % 16 || (p.sBq * es) % 16)
+        return false;
+    if (p.lda < p.aCols || p.ldb < p.bCols)
+        return false;
+    int sel, ext;
+    long long st;
+    const int P = p.count / p.Q;
+    if (!BatchSelector(p.sAp, p.sAq, P, p.Q, &sel, &st, &ext) || st < 0)
+        return false;
+    if (!BatchSelector(p.sBp, p.sBq, P, p.Q, &sel, &st, &ext) || st < 0)
+        return false;
+    return true;
+}
+
+int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream)
+{
+    const int mode = p.dtAB == NTB_X_FLOAT16 ? 0 : 1;
+    const int bn = PickBN(p, ctx.smCount, mode);
+    const int P = p.count / p.Q;
+
+    TcParams tp;
+    tp.c = p.c; tp.ldc = p.ldc; tp.sCp = p.sCp; tp.sCq = p.sCq;
+    tp.M = p.M; tp.N = p.N; tp.K = p.K; tp.count = p.count; tp.Q = p.Q;
+    tp.aMN = p.aMN; tp.bMN = p.bMN;
+    tp.tilesM = (p.M + BM - 1) / BM;
+    tp.tilesN = (p.N + bn - 1) / bn;
+    tp.totalTiles = (long long)tp.tilesM * tp.tilesN * p.count;
+    tp.alpha = p.alpha; tp.beta = p.beta;
+    tp.status = ctx.status;
+    const long long ces = ElemSize(p.dtC);
+    tp.cVec = (((uintptr_t)p.c & 15) == 0) && ((p.ldc * ces) % 16 == 0) &&
+              ((p.sCp * ces) % 16 == 0) && ((p.sCq * ces) % 16 == 0);
+
+    long long stA = 0, stB = 0;
+    int extA = 1, extB = 1;
+    BatchSelector(p.sAp, p.sAq, P, p.Q, &tp.aSel, &stA, &extA);
+    BatchSelector(p.sBp, p.sBq, P, p.Q, &tp.bSel, &stB, &extB);
+
+    CUtensorMap tmA, tmB;
+    int rc = EncodeOperand(&tmA, mode, p.a, p.aMN, p.aRows, p.aCols, p.lda, stA, extA, BM);
+    if (rc != NTB_OK)
+        return rc;
+    rc = EncodeOperand(&tmB, mode, p.b, p.bMN, p.bRows, p.bCols, p.ldb, stB, extB, bn);
+    if (rc != NTB_OK)
+        return rc;
+
+    const int grid = (int)(tp.totalTiles < ctx.smCount ? tp.totalTiles : ctx.smCount);
+    if (mode == 0) {
+        const bool half = p.dtC == NTB_X_FLOAT16;
+        if (bn == 256)
+            return half ? LaunchOne<0, 256, 4, __half>(tmA, tmB, tp, grid, stream)
+                        : LaunchOne<0, 256, 4, float>(tmA, tmB, tp, grid, stream);
+        if (bn == 128)
+            return half ? LaunchOne<0, 128, 6, __half>(tmA, tmB, tp, grid, stream)
+                        : LaunchOne<0, 128, 6, float>(tmA, tmB, tp, grid, stream);
+        return half ? LaunchOne<0, 64, 8, __half>(tmA, tmB, tp, grid, stream)
+                    : LaunchOne<0, 64, 8, float>(tmA, tmB, tp, grid, stream);
+    }
+    if (bn == 128)
+        return LaunchOne<1, 128, 3, float>(tmA, tmB, tp, grid, stream);
+    return LaunchOne<1, 64, 4, float>(tmA, tmB, tp, grid, stream);
+}
+
+}

@@ -1,0 +1,150 @@
+"""Host-side mirror of NiuTensor's matrix-multiplication operators over torch CUDA
+tensors. torch supplies device memory and streams only; every product is computed by the
+library behind include/ntb_gemm.h.
+
+Names, argument meaning and shape rules follow the reference:
+  _MatrixMul         source/tensor/core/arithmetic/MatrixMul.cpp:52-208
+  _MatrixMul2D       source/tensor/core/arithmetic/MatrixMul2D.cpp:46-181
+  _MatrixMulBatched  source/tensor/core/arithmetic/MatrixMulBatched.cpp:49-138
+  MatrixMul          source/tensor/core/arithmetic/MatrixMul.cpp:272-361
+  MatrixMulBatched   source/tensor/core/arithmetic/MatrixMulBatched.cpp:291-390 (= BMMul)
+Transposition flags are the reference's enum values: X_TRANS = 0, X_NOTRANS = 1.
+Where the reference prints an error and terminates, these raise NtError.
+"""
+import torch
+
+from . import capi
+from .capi import X_TRANS, X_NOTRANS, X_FLOAT, X_FLOAT16
+
+
+class NtError(RuntimeError):
+    """The reference's CheckNTErrors / ShowNTErrors (source/tensor/XGlobal.h:78-102)."""
+
+
+def _check(cond, msg):
+    if not cond:
+        raise NtError(msg)
+
+
+def _dtype_code(t):
+    if t.dtype == torch.float32:
+        return X_FLOAT
+    if t.dtype == torch.float16:
+        return X_FLOAT16
+    raise NtError("Unsupported data type!")
+
+
+def _stream(t):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _common_checks(a, b, c):
+    _check(a is not None and b is not None and c is not None, "Empty input tensors!")
+    _check(a.is_cuda and b.is_cuda and c.is_cuda,
+           "this library has no CPU path: tensors must live on a CUDA device")
+    _check(a.device == b.device == c.device, "The code must be run on the same GPU!")
+    _check(a.is_contiguous() and b.is_contiguous() and c.is_contiguous(),
+           "tensors must be dense and packed")
+    _check(a.dtype == b.dtype, "Input tensors should have the same data type!")
+    _dtype_code(a)
+    _check(c.dtype == a.dtype or (a.dtype == torch.float16 and c.dtype == torch.float32),
+           "Input tensors should have the same data type!")
+
+
+def _raise_rc(rc, what):
+    if rc != capi.OK:
+        raise NtError("%s: %s" % (what, capi.strerror(rc)))
+
+
+def _MatrixMul2D(a, transposedA, b, transposedB, c, alpha=1.0, beta=0.0):
+    _common_checks(a, b, c)
+    _check(a.dim() == 2 and b.dim() == 2 and c.dim() == 2, "Input tensors must have a order = 2!")
+    an, am = (a.shape[1], a.shape[0]) if transposedA == X_TRANS else (a.shape[0], a.shape[1])
+    bn, bm = (b.shape[1], b.shape[0]) if transposedB == X_TRANS else (b.shape[0], b.shape[1])
+    _check(am == bn and an == c.shape[0] and bm == c.shape[1], "Unmatched tensors in multiplication!")
+    rc = capi.lib().ntb_gemm(a.device.index, _stream(a), a.data_ptr(), transposedA, b.data_ptr(), transposedB,
+                             c.data_ptr(), _dtype_code(a), _dtype_code(c),
+                             a.shape[0], a.shape[1], b.shape[0], b.shape[1], c.shape[0], c.shape[1],
+                             a.shape[1], b.shape[1], c.shape[1], alpha, beta)
+    _raise_rc(rc, "_MatrixMul2D")
+
+
+def _MatrixMul(a, transposedA, b, transposedB, c, alpha=1.0, beta=0.0):
+    _common_checks(a, b, c)
+    _check(a.dim() >= 2 and b.dim() >= 2 and c.dim() >= 2, "Input tensors must have a order >= 2!")
+    _check(c.dim() == a.dim() + b.dim() - 2, "wrong tensor order")
+    if transposedA == X_NOTRANS and a.dim() > 2 and b.dim() == 2:
+        # the reference folds the leading extents of a and c into rows (MatrixMul.cpp:65-77)
+        _MatrixMul2D(a.view(-1, a.shape[-1]), transposedA, b, transposedB,
+                     c.view(-1, c.shape[-1]), alpha, beta)
+        return
+    na, ma = a.shape[-2], a.shape[-1]
+    nb, mb = b.shape[-2], b.shape[-1]
+    nc, mc = c.shape[-2], c.shape[-1]
+    an, am = (ma, na) if transposedA == X_TRANS else (na, ma)
+    bn, bm = (mb, nb) if transposedB == X_TRANS else (nb, mb)
+    _check(am == bn and an == nc and bm == mc, "Unmatched tensors in multiplication!")
+    a_lead, b_lead = tuple(a.shape[:-2]), tuple(b.shape[:-2])
+    _check(tuple(c.shape[:len(a_lead)]) == a_lead, "Incorrect tensor sizes!")
+    _check(tuple(c.shape[len(a_lead):-2]) == b_lead, "Incorrect tensor sizes!")
+    P = 1
+    for d in a_lead:
+        P *= d
+    Q = 1
+    for d in b_lead:
+        Q *= d
+    rc = capi.lib().ntb_gemm_broadcast(a.device.index, _stream(a), a.data_ptr(), transposedA,
+                                       b.data_ptr(), transposedB, c.data_ptr(),
+                                       _dtype_code(a), _dtype_code(c), na, ma, nb, mb, nc, mc,
+                                       P, Q, alpha, beta)
+    _raise_rc(rc, "_MatrixMul")
+
+
+def _MatrixMulBatched(a, transposedA, b, transposedB, c, alpha=1.0, beta=0.0):
+    _common_checks(a, b, c)
+    _check(a.dim() >= 2 and b.dim() >= 2 and c.dim() >= 2, "Input tensors must have a order >= 2!")
+    _check(a.dim() == b.dim() and a.dim() == c.dim(), "Input tensor and output tensor must have same order!")
+    na, ma = a.shape[-2], a.shape[-1]
+    nb, mb = b.shape[-2], b.shape[-1]
+    nc, mc = c.shape[-2], c.shape[-1]
+    an, am = (ma, na) if transposedA == X_TRANS else (na, ma)
+    bn, bm = (mb, nb) if transposedB == X_TRANS else (nb, mb)
+    _check(am == bn and an == nc and bm == mc, "Unmatched tensors in multiplication!")
+    _check(tuple(a.shape[:-2]) == tuple(b.shape[:-2]) == tuple(c.shape[:-2]), "Incorrect tensor sizes!")
+    count = 1
+    for d in a.shape[:-2]:
+        count *= d
+    rc = capi.lib().ntb_gemm_strided_batched(a.device.index, _stream(a), a.data_ptr(), transposedA,
+                                             b.data_ptr(), transposedB, c.data_ptr(),
+                                             _dtype_code(a), _dtype_code(c), na, ma, nb, mb, nc, mc,
+                                             ma, mb, mc, na * ma, nb * mb, nc * mc, count, alpha, beta)
+    _raise_rc(rc, "_MatrixMulBatched")
+
+
+def MatrixMul(a, transposedA, b, transposedB, alpha=1.0, beta=0.0, c=None):
+    """Allocating form (c is None: result on a's device, shape a.lead + b.lead + [an, bm],
+    MatrixMul.cpp:279-298) or the form writing into the caller's c with alpha and beta
+    (MatrixMul.cpp:317-361; a c of the wrong shape is re-made, CheckMMulShape :210-249)."""
+    an = a.shape[-1] if transposedA == X_TRANS else a.shape[-2]
+    bm = b.shape[-2] if transposedB == X_TRANS else b.shape[-1]
+    shape = tuple(a.shape[:-2]) + tuple(b.shape[:-2]) + (an, bm)
+    if c is None or tuple(c.shape) != shape:
+        c = torch.zeros(shape, dtype=a.dtype, device=a.device)
+    _MatrixMul(a, transposedA, b, transposedB, c, alpha, beta)
+    return c
+
+
+def MMul(a, b, alpha=1.0):
+    """No-transposition shortcut (MatrixMul.cpp:371-459)."""
+    return MatrixMul(a, X_NOTRANS, b, X_NOTRANS, alpha)
+
+
+def MatrixMulBatched(a, transposedA, b, transposedB, alpha=1.0):
+    an = a.shape[-1] if transposedA == X_TRANS else a.shape[-2]
+    bm = b.shape[-2] if transposedB == X_TRANS else b.shape[-1]
+    c = torch.empty(tuple(a.shape[:-2]) + (an, bm), dtype=a.dtype, device=a.device)
+    _MatrixMulBatched(a, transposedA, b, transposedB, c, alpha, 0.0)
+    return c
+
+
+BMMul = MatrixMulBatched

@@ -1,0 +1,84 @@
+"""CPU-side checks of the drop-in boundary: the shared library loads, exports every
+symbol the header declares, validates arguments with the reference's shape rules before
+touching CUDA, and refuses to compute without a device (there is no CPU fallback)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from niutensor_b200 import capi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def header_symbols():
+    text = open(os.path.join(ROOT, "include", "ntb_gemm.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return set(re.findall(r"\b(ntb_\w+)\s*\(", text))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = ctypes.CDLL(capi.LIB_PATH)
+    names = header_symbols()
+    assert names, "no declarations found"
+    for n in names:
+        assert hasattr(lib, n), n
+    assert names == set(capi.PROTOTYPES), names ^ set(capi.PROTOTYPES)
+
+
+def test_argument_checks_run_before_cuda():
+    L = capi.lib()
+    p = 4096  # any non-null address; never dereferenced on these paths
+    f16 = capi.X_FLOAT16
+    # inner dimensions differ: a 4x5, b 6x4
+    assert L.ntb_gemm(0, None, p, 1, p, 1, p, f16, f16, 4, 5, 6, 4, 4, 4, 5, 4, 4, 1.0, 0.0) == capi.ERR_SHAPE
+    # output shape wrong
+    assert L.ntb_gemm(0, None, p, 1, p, 1, p, f16, f16, 4, 5, 5, 4, 4, 3, 5, 4, 3, 1.0, 0.0) == capi.ERR_SHAPE
+    # transposition flag outside the enum
+    assert L.ntb_gemm(0, None, p, 2, p, 1, p, f16, f16, 4, 4, 4, 4, 4, 4, 4, 4, 4, 1.0, 0.0) == capi.ERR_ARG
+    # X_DOUBLE, X_INT are not supported
+    assert L.ntb_gemm(0, None, p, 1, p, 1, p, capi.X_DOUBLE, capi.X_DOUBLE, 4, 4, 4, 4, 4, 4, 4, 4, 4, 1.0, 0.0) == capi.ERR_DTYPE
+    assert L.ntb_gemm(0, None, p, 1, p, 1, p, capi.X_INT, capi.X_INT, 4, 4, 4, 4, 4, 4, 4, 4, 4, 1.0, 0.0) == capi.ERR_DTYPE
+    # fp32 inputs cannot produce a half result
+    assert L.ntb_gemm(0, None, p, 1, p, 1, p, capi.X_FLOAT, f16, 4, 4, 4, 4, 4, 4, 4, 4, 4, 1.0, 0.0) == capi.ERR_DTYPE
+    # pitch smaller than the row
+    assert L.ntb_gemm(0, None, p, 1, p, 1, p, f16, f16, 4, 4, 4, 4, 4, 4, 3, 4, 4, 1.0, 0.0) == capi.ERR_ARG
+    # NULL operand
+    assert L.ntb_gemm(0, None, None, 1, p, 1, p, f16, f16, 4, 4, 4, 4, 4, 4, 4, 4, 4, 1.0, 0.0) == capi.ERR_ARG
+    # empty problems are a no-op, as in the reference's list path (XTensorBLAS.cu:261-262)
+    assert L.ntb_gemm_strided_batched(0, None, p, 1, p, 1, p, f16, f16, 4, 4, 4, 4, 4, 4, 4, 4, 4,
+                                      16, 16, 16, 0, 1.0, 0.0) == capi.OK
+    assert L.ntb_gemm_list(0, None, None, 1, None, 1, None, f16, f16, 0, 4, 4, 4, 4, 4, 4, 1.0, 0.0) == capi.OK
+    assert L.ntb_set_route(7) == capi.ERR_ARG
+    assert capi.strerror(capi.ERR_SHAPE) == "unmatched tensors in multiplication"
+
+
+def test_no_cpu_fallback_without_a_device():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    L = capi.lib()
+    p = 4096
+    rc = L.ntb_gemm(0, None, p, 1, p, 1, p, capi.X_FLOAT16, capi.X_FLOAT16,
+                    4, 4, 4, 4, 4, 4, 4, 4, 4, 1.0, 0.0)
+    assert rc == capi.ERR_CUDA
+
+
+def test_ops_refuse_cpu_tensors():
+    import torch
+    from niutensor_b200 import ops
+    a = torch.zeros(2, 3)
+    b = torch.zeros(3, 2)
+    c = torch.zeros(2, 2)
+    with pytest.raises(ops.NtError):
+        ops._MatrixMul(a, capi.X_NOTRANS, b, capi.X_NOTRANS, c)
+
+
+def test_product_package_does_not_import_the_oracle():
+    pkg = os.path.join(ROOT, "niutensor_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for fn in files:
+            if fn.endswith((".py", ".cu", ".h", ".cpp", ".cuh")):
+                text = open(os.path.join(dirpath, fn)).read()
+                assert "oracle" not in text.lower(), fn

@@ -1,0 +1,385 @@
+"""Parity of the CUDA path with the CPU oracle, through the C ABI.
+
+Tolerances (relative Frobenius error against the reference's fp32 CPU arithmetic):
+fp32 tensors 1e-5, fp16 tensors 2e-3. The reference's own unit-test vectors are checked
+with the reference's comparator and tolerance (1e-4 absolute or relative).
+"""
+import ctypes
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from niutensor_b200 import capi, ops
+from niutensor_b200.capi import X_TRANS, X_NOTRANS
+from oracle.oracle import rel_fro, round_to_half
+from tests.golden.cases import seeded_cases, FORM_GENERAL, FORM_BATCHED, FORM_2D
+from tests.test_oracle import is_float_equal, kat_cases, run_form
+
+pytestmark = pytest.mark.gpu
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+TOL = {torch.float32: 1e-5, torch.float16: 2e-3}
+DEV = "cuda:0"
+
+
+def to_dev(x, dtype):
+    return torch.from_numpy(np.ascontiguousarray(x)).to(DEV).to(dtype)
+
+
+def run_ops(form, a, tA, b, tB, alpha, beta, c):
+    if form in ("_MatrixMul", FORM_GENERAL):
+        ops._MatrixMul(a, tA, b, tB, c, alpha, beta)
+    elif form in ("_MatrixMulBatched", FORM_BATCHED):
+        ops._MatrixMulBatched(a, tA, b, tB, c, alpha, beta)
+    else:
+        ops._MatrixMul2D(a, tA, b, tB, c, alpha, beta)
+
+
+def status_ok():
+    assert capi.lib().ntb_device_status(0) == capi.OK
+
+
+def stored(rng, lead, rows, cols, trans, dist="uniform"):
+    shp = tuple(lead) + ((cols, rows) if trans == X_TRANS else (rows, cols))
+    if dist == "uniform":
+        return rng.uniform(-1.0, 1.0, shp).astype(np.float32)
+    return rng.normal(size=shp).astype(np.float32)
+
+
+# --------------------------------------------------------------- reference fixtures
+
+@pytest.mark.parametrize("case", kat_cases(), ids=lambda c: c["name"])
+def test_reference_unit_test_vectors(case):
+    a = np.asarray(case["a"], np.float32).reshape(case["a_shape"])
+    b = np.asarray(case["b"], np.float32).reshape(case["b_shape"])
+    want = np.asarray(case["answer"], np.float32).reshape(case["c_shape"])
+    op = case["op"] if case["op"] != "_MatrixMul2DParallel" else "_MatrixMul2D"
+    c = torch.zeros(case["c_shape"], device=DEV)
+    run_ops(op, to_dev(a, torch.float32), case["transA"], to_dev(b, torch.float32), case["transB"],
+            1.0, 0.0, c)
+    assert is_float_equal(c.cpu().numpy(), want, case["tolerance"])
+    # the user-level call of the same case
+    if op == "_MatrixMul":
+        u = ops.MatrixMul(to_dev(a, torch.float32), case["transA"], to_dev(b, torch.float32), case["transB"])
+        assert is_float_equal(u.cpu().numpy(), want, case["tolerance"])
+    if op == "_MatrixMulBatched":
+        u = ops.BMMul(to_dev(a, torch.float32), case["transA"], to_dev(b, torch.float32), case["transB"])
+        assert is_float_equal(u.cpu().numpy(), want, case["tolerance"])
+    status_ok()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_stored_reference_outputs(dtype, oracle):
+    z = np.load(os.path.join(GOLD, "ref_seeded.npz"))
+    worst = 0.0
+    for i, (kind, form, a, tA, b, tB, alpha, beta, c0) in enumerate(seeded_cases()):
+        if dtype == torch.float16:
+            # the reference has no fp16 CPU arithmetic: its fp32 path on fp16-valued inputs
+            a, b, c0 = round_to_half(a), round_to_half(b), round_to_half(c0)
+            want = run_form(oracle, form, a, tA, b, tB, alpha, beta, c0)
+        else:
+            want = z["c%d" % i]
+        c = to_dev(c0, dtype)
+        run_ops(form, to_dev(a, dtype), tA, to_dev(b, dtype), tB, alpha, beta, c)
+        err = rel_fro(c.float().cpu().numpy(), want)
+        worst = max(worst, err)
+        assert err <= TOL[dtype], (i, kind, tA, tB, alpha, beta, err)
+    status_ok()
+
+
+# --------------------------------------------------------------- randomized parity
+
+SHAPES_TC = [(128, 128, 64), (256, 384, 192), (136, 200, 72), (64, 520, 264), (384, 72, 40), (8, 8, 8)]
+SHAPES_RAGGED = [(37, 29, 53), (1, 1, 1), (130, 67, 129), (5, 300, 2)]
+AB = [(1.0, 0.0), (0.125, 0.0), (1.0, 1.0), (1.0, 0.5)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("tA", [X_TRANS, X_NOTRANS])
+@pytest.mark.parametrize("tB", [X_TRANS, X_NOTRANS])
+def test_2d_all_transpositions(dtype, tA, tB, oracle):
+    rng = np.random.default_rng(100 + 2 * tA + tB)
+    L = capi.lib()
+    for si, (M, N, K) in enumerate(SHAPES_TC + SHAPES_RAGGED):
+        alpha, beta = AB[si % len(AB)]
+        a = stored(rng, (), M, K, tA)
+        b = stored(rng, (), K, N, tB)
+        c0 = rng.normal(size=(M, N)).astype(np.float32)
+        if dtype == torch.float16:
+            a, b, c0 = round_to_half(a), round_to_half(b), round_to_half(c0)
+        want = oracle.matmul2d(a, tA, b, tB, alpha, beta, c0)
+        c = to_dev(c0, dtype)
+        ops._MatrixMul2D(to_dev(a, dtype), tA, to_dev(b, dtype), tB, c, alpha, beta)
+        route = L.ntb_last_route()
+        es = 2 if dtype == torch.float16 else 4
+        aligned = (a.shape[1] * es) % 16 == 0 and (b.shape[1] * es) % 16 == 0
+        if aligned:
+            assert route == (capi.ROUTE_TC_F16 if dtype == torch.float16 else capi.ROUTE_TC_3XTF32), (M, N, K)
+        else:
+            assert route == capi.ROUTE_SIMT, (M, N, K)
+        err = rel_fro(c.float().cpu().numpy(), want)
+        assert err <= TOL[dtype], (M, N, K, alpha, beta, err, route)
+    status_ok()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_batched_broadcast_and_flatten_forms(dtype, oracle):
+    rng = np.random.default_rng(200)
+    for tA in (X_TRANS, X_NOTRANS):
+        for tB in (X_TRANS, X_NOTRANS):
+            for (M, N, K), (alpha, beta) in zip([(128, 72, 64), (72, 136, 40), (33, 17, 9)], AB[1:]):
+                def prep(*xs):
+                    return [round_to_half(x) if dtype == torch.float16 else x for x in xs]
+                # batched, two leading dims
+                a, b, c0 = prep(stored(rng, (2, 3), M, K, tA), stored(rng, (2, 3), K, N, tB),
+                                rng.normal(size=(2, 3, M, N)).astype(np.float32))
+                c = to_dev(c0, dtype)
+                ops._MatrixMulBatched(to_dev(a, dtype), tA, to_dev(b, dtype), tB, c, alpha, beta)
+                assert rel_fro(c.float().cpu().numpy(), oracle.matmul_batched(a, tA, b, tB, alpha, beta, c0)) <= TOL[dtype]
+                # general form: every block of a meets every block of b
+                a, b, c0 = prep(stored(rng, (3,), M, K, tA), stored(rng, (2, 2), K, N, tB),
+                                rng.normal(size=(3, 2, 2, M, N)).astype(np.float32))
+                c = to_dev(c0, dtype)
+                ops._MatrixMul(to_dev(a, dtype), tA, to_dev(b, dtype), tB, c, alpha, beta)
+                assert rel_fro(c.float().cpu().numpy(), oracle.matmul(a, tA, b, tB, alpha, beta, c0)) <= TOL[dtype]
+                # a of order 3 against a matrix (folded into rows when a is not transposed)
+                a, b, c0 = prep(stored(rng, (4,), M, K, tA), stored(rng, (), K, N, tB),
+                                rng.normal(size=(4, M, N)).astype(np.float32))
+                c = to_dev(c0, dtype)
+                ops._MatrixMul(to_dev(a, dtype), tA, to_dev(b, dtype), tB, c, alpha, beta)
+                assert rel_fro(c.float().cpu().numpy(), oracle.matmul(a, tA, b, tB, alpha, beta, c0)) <= TOL[dtype]
+    status_ok()
+
+
+def test_half_inputs_float_output(oracle):
+    rng = np.random.default_rng(7)
+    a = round_to_half(stored(rng, (), 256, 128, X_NOTRANS))
+    b = round_to_half(stored(rng, (), 128, 192, X_NOTRANS))
+    c = torch.zeros(256, 192, device=DEV, dtype=torch.float32)
+    ops._MatrixMul2D(to_dev(a, torch.float16), X_NOTRANS, to_dev(b, torch.float16), X_NOTRANS, c)
+    # products of halves are exact in fp32; only the accumulation order differs
+    assert rel_fro(c.cpu().numpy(), oracle.matmul2d(a, X_NOTRANS, b, X_NOTRANS)) <= 1e-5
+    status_ok()
+
+
+def test_misaligned_base_pointers_take_the_ffma_route(oracle):
+    """XMem pools hand out pieces back to back, so a tensor may start at any element."""
+    rng = np.random.default_rng(8)
+    L = capi.lib()
+    for dtype in (torch.float16, torch.float32):
+        M, N, K = 64, 72, 40
+        a = stored(rng, (), M, K, X_NOTRANS)
+        b = stored(rng, (), K, N, X_NOTRANS)
+        if dtype == torch.float16:
+            a, b = round_to_half(a), round_to_half(b)
+        abuf = torch.zeros(M * K + 1, device=DEV, dtype=dtype)
+        abuf[1:] = to_dev(a, dtype).reshape(-1)
+        av = abuf[1:].view(M, K)
+        assert av.data_ptr() % 16 != 0
+        c = torch.zeros(M, N, device=DEV, dtype=dtype)
+        ops._MatrixMul2D(av, X_NOTRANS, to_dev(b, dtype), X_NOTRANS, c)
+        assert L.ntb_last_route() == capi.ROUTE_SIMT
+        assert rel_fro(c.float().cpu().numpy(), oracle.matmul2d(a, X_NOTRANS, b, X_NOTRANS)) <= TOL[dtype]
+        # misaligned C only: tensor cores with scalar stores
+        cbuf = torch.zeros(M * N + 1, device=DEV, dtype=dtype)
+        cv = cbuf[1:].view(M, N)
+        ops._MatrixMul2D(to_dev(a, dtype), X_NOTRANS, to_dev(b, dtype), X_NOTRANS, cv)
+        assert L.ntb_last_route() != capi.ROUTE_SIMT
+        assert rel_fro(cv.float().cpu().numpy(), oracle.matmul2d(a, X_NOTRANS, b, X_NOTRANS)) <= TOL[dtype]
+        assert float(cbuf[0]) == 0.0
+    status_ok()
+
+
+def test_forced_ffma_route_matches_tensor_core_route(oracle):
+    rng = np.random.default_rng(9)
+    L = capi.lib()
+    a = stored(rng, (2,), 128, 64, X_TRANS)
+    b = stored(rng, (2,), 64, 136, X_TRANS)
+    want = oracle.matmul_batched(a, X_TRANS, b, X_TRANS, 0.5, 0.0)
+    try:
+        for route in (capi.ROUTE_SIMT, 0):
+            assert L.ntb_set_route(route) == capi.OK
+            c = torch.zeros(2, 128, 136, device=DEV)
+            ops._MatrixMulBatched(to_dev(a, torch.float32), X_TRANS, to_dev(b, torch.float32), X_TRANS, c, 0.5, 0.0)
+            assert (L.ntb_last_route() == capi.ROUTE_SIMT) == (route == capi.ROUTE_SIMT)
+            assert rel_fro(c.cpu().numpy(), want) <= 1e-5
+    finally:
+        L.ntb_set_route(0)
+    status_ok()
+
+
+# --------------------------------------------------------------- semantics corners
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_beta_zero_never_reads_c(dtype):
+    a = torch.randn(128, 64, device=DEV).to(dtype)
+    b = torch.randn(64, 128, device=DEV).to(dtype)
+    for route in (0, capi.ROUTE_SIMT):
+        capi.lib().ntb_set_route(route)
+        try:
+            c = torch.full((128, 128), float("nan"), device=DEV, dtype=dtype)
+            ops._MatrixMul2D(a, X_NOTRANS, b, X_NOTRANS, c, 1.0, 0.0)
+            assert not torch.isnan(c).any()
+        finally:
+            capi.lib().ntb_set_route(0)
+    status_ok()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_pitched_output_leaves_padding_untouched(dtype, oracle):
+    """ldc > mc: a column shard of a wider resident matrix; the gap must stay as it was."""
+    rng = np.random.default_rng(11)
+    L = capi.lib()
+    M, N, K, ldc = 200, 136, 72, 160
+    a = stored(rng, (), M, K, X_NOTRANS)
+    b = stored(rng, (), N, K, X_NOTRANS)       # stored N x K, used transposed
+    if dtype == torch.float16:
+        a, b = round_to_half(a), round_to_half(b)
+    ta, tb = to_dev(a, dtype), to_dev(b, dtype)
+    cbuf = torch.full((M + 2, ldc), 7.0, device=DEV, dtype=dtype)
+    code = capi.X_FLOAT16 if dtype == torch.float16 else capi.X_FLOAT
+    cptr = cbuf.data_ptr() + ldc * cbuf.element_size()      # row 1
+    rc = L.ntb_gemm(0, None, ta.data_ptr(), X_NOTRANS, tb.data_ptr(), X_TRANS, cptr, code, code,
+                    M, K, N, K, M, N, K, K, ldc, 1.0, 0.0)
+    assert rc == capi.OK
+    torch.cuda.synchronize()
+    got = cbuf.float().cpu().numpy()
+    assert rel_fro(got[1:M + 1, :N], oracle.matmul2d(a, X_NOTRANS, b, X_TRANS)) <= TOL[dtype]
+    assert (got[0] == 7.0).all() and (got[M + 1] == 7.0).all() and (got[1:M + 1, N:] == 7.0).all()
+    status_ok()
+
+
+def test_column_shard_of_resident_operand(oracle):
+    """ldb > mb: multiply by columns [n0, n0 + n) of a resident K x N matrix in place."""
+    rng = np.random.default_rng(12)
+    L = capi.lib()
+    M, K, Nfull, n0, n = 128, 64, 512, 256, 128
+    a = round_to_half(stored(rng, (), M, K, X_NOTRANS))
+    b = round_to_half(stored(rng, (), K, Nfull, X_NOTRANS))
+    ta, tb = to_dev(a, torch.float16), to_dev(b, torch.float16)
+    c = torch.zeros(M, n, device=DEV, dtype=torch.float16)
+    rc = L.ntb_gemm(0, None, ta.data_ptr(), X_NOTRANS, tb.data_ptr() + n0 * 2, X_NOTRANS, c.data_ptr(),
+                    capi.X_FLOAT16, capi.X_FLOAT16, M, K, K, n, M, n, K, Nfull, n, 1.0, 0.0)
+    assert rc == capi.OK and L.ntb_last_route() == capi.ROUTE_TC_F16
+    want = oracle.matmul2d(a, X_NOTRANS, np.ascontiguousarray(b[:, n0:n0 + n]), X_NOTRANS)
+    assert rel_fro(c.float().cpu().numpy(), want) <= 2e-3
+    status_ok()
+
+
+def test_k_zero_scales_c_and_empty_batches_are_noops():
+    L = capi.lib()
+    c = torch.ones(8, 8, device=DEV)
+    a = torch.zeros(1, device=DEV)
+    rc = L.ntb_gemm(0, None, a.data_ptr(), X_NOTRANS, a.data_ptr(), X_NOTRANS, c.data_ptr(),
+                    capi.X_FLOAT, capi.X_FLOAT, 8, 0, 0, 8, 8, 8, 0, 8, 8, 1.0, 0.5)
+    assert rc == capi.OK
+    assert torch.equal(c, torch.full((8, 8), 0.5, device=DEV))
+    rc = L.ntb_gemm_strided_batched(0, None, a.data_ptr(), X_NOTRANS, a.data_ptr(), X_NOTRANS, c.data_ptr(),
+                                    capi.X_FLOAT, capi.X_FLOAT, 8, 8, 8, 8, 8, 8, 8, 8, 8, 64, 64, 64, 0, 1.0, 0.0)
+    assert rc == capi.OK
+    assert torch.equal(c, torch.full((8, 8), 0.5, device=DEV))
+    status_ok()
+
+
+def test_shared_operand_stride_zero(oracle):
+    rng = np.random.default_rng(13)
+    L = capi.lib()
+    M, N, K, cnt = 128, 64, 64, 5
+    a = round_to_half(stored(rng, (cnt,), M, K, X_NOTRANS))
+    b = round_to_half(stored(rng, (), K, N, X_NOTRANS))
+    ta, tb = to_dev(a, torch.float16), to_dev(b, torch.float16)
+    c = torch.zeros(cnt, M, N, device=DEV, dtype=torch.float16)
+    rc = L.ntb_gemm_strided_batched(0, None, ta.data_ptr(), X_NOTRANS, tb.data_ptr(), X_NOTRANS, c.data_ptr(),
+                                    capi.X_FLOAT16, capi.X_FLOAT16, M, K, K, N, M, N, K, N, N,
+                                    M * K, 0, M * N, cnt, 1.0, 0.0)
+    assert rc == capi.OK
+    want = oracle.matmul(a, X_NOTRANS, b, X_NOTRANS)
+    assert rel_fro(c.float().cpu().numpy(), want) <= 2e-3
+    status_ok()
+
+
+def test_errors_mirror_the_reference():
+    a = torch.zeros(4, 5, device=DEV)
+    b = torch.zeros(6, 4, device=DEV)
+    c = torch.zeros(4, 4, device=DEV)
+    with pytest.raises(ops.NtError, match="Unmatched tensors"):
+        ops._MatrixMul(a, X_NOTRANS, b, X_NOTRANS, c)
+    with pytest.raises(ops.NtError, match="same data type"):
+        ops._MatrixMul(a, X_NOTRANS, torch.zeros(5, 4, device=DEV, dtype=torch.float16), X_NOTRANS, c)
+    with pytest.raises(ops.NtError, match="wrong tensor order"):
+        ops._MatrixMul(torch.zeros(2, 4, 5, device=DEV), X_NOTRANS, torch.zeros(2, 5, 4, device=DEV), X_NOTRANS,
+                       torch.zeros(2, 4, 4, device=DEV))
+    with pytest.raises(ops.NtError, match="Unsupported data type"):
+        ops._MatrixMul2D(a.double(), X_NOTRANS, torch.zeros(5, 4, device=DEV).double(), X_NOTRANS, c.double())
+    # MatrixMul re-makes a c of the wrong shape (CheckMMulShape)
+    out = ops.MatrixMul(a, X_NOTRANS, torch.zeros(5, 3, device=DEV), X_NOTRANS, c=c)
+    assert tuple(out.shape) == (4, 3)
+
+
+# --------------------------------------------------------------- list planner, host entry
+
+def _ptr_array(ts):
+    arr = (ctypes.c_void_p * len(ts))(*[t.data_ptr() for t in ts])
+    return ctypes.cast(arr, ctypes.POINTER(ctypes.c_void_p)), arr
+
+
+def test_list_planner(oracle):
+    rng = np.random.default_rng(14)
+    L = capi.lib()
+    M, N, K = 128, 64, 64
+    code = capi.X_FLOAT16
+    before = L.ntb_launch_count()
+    # (p, q) pattern of the general form -> one launch
+    a = round_to_half(stored(rng, (3,), M, K, X_NOTRANS))
+    b = round_to_half(stored(rng, (2,), K, N, X_NOTRANS))
+    ta, tb = to_dev(a, torch.float16), to_dev(b, torch.float16)
+    c = torch.zeros(3, 2, M, N, device=DEV, dtype=torch.float16)
+    al = [ta[p] for p in range(3) for q in range(2)]
+    bl = [tb[q] for p in range(3) for q in range(2)]
+    cl = [c[p, q] for p in range(3) for q in range(2)]
+    (ap, k1), (bp, k2), (cp, k3) = _ptr_array(al), _ptr_array(bl), _ptr_array(cl)
+    assert L.ntb_gemm_list(0, None, ap, X_NOTRANS, bp, X_NOTRANS, cp, code, code, 6, M, K, K, N, M, N, 1.0, 0.0) == capi.OK
+    assert L.ntb_launch_count() == before + 1
+    assert rel_fro(c.float().cpu().numpy(), oracle.matmul(a, X_NOTRANS, b, X_NOTRANS)) <= 2e-3
+    # constant stride -> one launch
+    before = L.ntb_launch_count()
+    b6 = round_to_half(stored(rng, (6,), K, N, X_NOTRANS))
+    a6 = round_to_half(stored(rng, (6,), M, K, X_NOTRANS))
+    ta6, tb6 = to_dev(a6, torch.float16), to_dev(b6, torch.float16)
+    c6 = torch.zeros(6, M, N, device=DEV, dtype=torch.float16)
+    (ap, k1), (bp, k2), (cp, k3) = _ptr_array(list(ta6)), _ptr_array(list(tb6)), _ptr_array(list(c6))
+    assert L.ntb_gemm_list(0, None, ap, X_NOTRANS, bp, X_NOTRANS, cp, code, code, 6, M, K, K, N, M, N, 1.0, 0.0) == capi.OK
+    assert L.ntb_launch_count() == before + 1
+    want6 = oracle.matmul_batched(a6, X_NOTRANS, b6, X_NOTRANS)
+    assert rel_fro(c6.float().cpu().numpy(), want6) <= 2e-3
+    # irregular order -> one launch per problem, same results
+    perm = [3, 0, 5, 1, 4, 2]
+    c6b = torch.zeros(6, M, N, device=DEV, dtype=torch.float16)
+    (ap, k1), (bp, k2), (cp, k3) = (_ptr_array([ta6[i] for i in perm]), _ptr_array([tb6[i] for i in perm]),
+                                    _ptr_array([c6b[i] for i in perm]))
+    before = L.ntb_launch_count()
+    assert L.ntb_gemm_list(0, None, ap, X_NOTRANS, bp, X_NOTRANS, cp, code, code, 6, M, K, K, N, M, N, 1.0, 0.0) == capi.OK
+    assert L.ntb_launch_count() == before + 6
+    assert torch.equal(c6b, c6)
+    status_ok()
+
+
+def test_host_buffer_entry(oracle):
+    rng = np.random.default_rng(15)
+    L = capi.lib()
+    M, N, K, cnt = 256, 128, 192, 3
+    for dtype, code, npdt in ((torch.float16, capi.X_FLOAT16, np.float16), (torch.float32, capi.X_FLOAT, np.float32)):
+        a = stored(rng, (cnt,), M, K, X_NOTRANS).astype(npdt)
+        b = stored(rng, (cnt,), N, K, X_NOTRANS).astype(npdt)
+        c0 = rng.normal(size=(cnt, M, N)).astype(npdt)
+        c = c0.copy()
+        rc = L.ntb_gemm_host(0, None, a.ctypes.data, X_NOTRANS, b.ctypes.data, X_TRANS, c.ctypes.data, code, code,
+                             M, K, N, K, M, N, M * K, N * K, M * N, cnt, 1.0, 0.5)
+        assert rc == capi.OK
+        want = oracle.matmul_batched(a.astype(np.float32), X_NOTRANS, b.astype(np.float32), X_TRANS, 1.0, 0.5,
+                                     c0.astype(np.float32))
+        assert rel_fro(c.astype(np.float32), want) <= TOL[dtype]
+    status_ok()
