@@ -153,14 +153,19 @@ class Reference:
     def set_threads(self, n):
         self.lib.ref_set_blas_threads(int(n))
 
-    def run(self, form, a, tA, b, tB, alpha=1.0, beta=0.0, c=None):
+    def run(self, form, a, tA, b, tB, alpha=1.0, beta=0.0, c=None, inplace=False):
+        """c (if given) is copied unless inplace is set, in which case it must be a packed
+        float32 array of the output shape and is overwritten."""
         a, b = _as_f32(a), _as_f32(b)
         M, N, _ = mm_dims(a.shape, tA, b.shape, tB)
         if form == self.FORM_GENERAL:
             shape = a.shape[:-2] + b.shape[:-2] + (M, N)
         else:
             shape = a.shape[:-2] + (M, N)
-        c = np.zeros(shape, np.float32) if c is None else _as_f32(c).copy().reshape(shape)
+        if inplace:
+            assert c is not None and c.dtype == np.float32 and c.flags.c_contiguous and c.shape == shape
+        else:
+            c = np.zeros(shape, np.float32) if c is None else _as_f32(c).copy().reshape(shape)
         ad = np.asarray(a.shape, np.int32)
         bd = np.asarray(b.shape, np.int32)
         cd = np.asarray(c.shape, np.int32)
