@@ -66,6 +66,7 @@ extern "C" {
 #define NTB_ROUTE_TC_F16    1   /* tcgen05 kind::f16, TMA-fed, TMEM accumulators */
 #define NTB_ROUTE_TC_3XTF32 2   /* tcgen05 kind::tf32, three passes on hi/lo split fp32 */
 #define NTB_ROUTE_SIMT      3   /* FFMA kernel for operands TMA cannot address */
+#define NTB_ROUTE_TC_F16_PAIR 4 /* kind::f16 on CTA pairs (cta_group::2), 256 x 256 tiles */
 
 /*
  * Single GEMM. Replaces _CudaBLASMatrixMUL
@@ -146,7 +147,9 @@ int ntb_last_route(void);
 /*
  * Restricts routing: 0 = automatic (default), NTB_ROUTE_SIMT = always the FFMA kernel,
  * NTB_ROUTE_TC_F16 / NTB_ROUTE_TC_3XTF32 = fail with NTB_ERR_ARG instead of using the
- * FFMA kernel when the tensor-core route cannot address the operands. Process-wide.
+ * FFMA kernel when the tensor-core route cannot address the operands (and, for
+ * NTB_ROUTE_TC_F16, never use CTA pairs), NTB_ROUTE_TC_F16_PAIR = likewise, but always
+ * CTA pairs for half operands whatever the problem size. Process-wide.
  */
 int ntb_set_route(int route);
 

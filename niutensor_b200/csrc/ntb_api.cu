@@ -109,16 +109,17 @@ int Dispatch(int devID, cudaStream_t stream, Problem & p)
     DeviceCtx * ctx = GetCtx(devID);
     if (!ctx)
         return NTB_ERR_CUDA;
-    const int forced = gForcedRoute.load();
+    const int forced = ForcedRoute();
     const bool tc = forced != NTB_ROUTE_SIMT && TcEligible(p);
     int rc;
     if (tc) {
-        rc = LaunchTc(*ctx, p, stream);
+        int route = NTB_ROUTE_NONE;
+        rc = LaunchTc(*ctx, p, stream, &route);
         if (rc == NTB_OK)
-            tLastRoute = p.dtAB == NTB_X_FLOAT16 ? NTB_ROUTE_TC_F16 : NTB_ROUTE_TC_3XTF32;
+            tLastRoute = route;
     }
     else {
-        if (forced == NTB_ROUTE_TC_F16 || forced == NTB_ROUTE_TC_3XTF32)
+        if (forced == NTB_ROUTE_TC_F16 || forced == NTB_ROUTE_TC_3XTF32 || forced == NTB_ROUTE_TC_F16_PAIR)
             return NTB_ERR_ARG;
         rc = LaunchSimt(*ctx, p, stream);
         if (rc == NTB_OK)
@@ -148,6 +149,16 @@ int GrowStage(DeviceCtx * ctx, int slot, size_t bytes)
 void CountLaunch()
 {
     gLaunches.fetch_add(1);
+}
+
+int ForcedRoute()
+{
+    const int r = gForcedRoute.load();
+    if (r != 0)
+        return r;
+    /* NTB_ROUTE in the environment gives the default when ntb_set_route() was not used */
+    const char * v = getenv("NTB_ROUTE");
+    return v && *v ? atoi(v) : 0;
 }
 
 EncodeTiledFn GetEncodeTiled()
@@ -364,7 +375,8 @@ int ntb_last_route(void)
 
 int ntb_set_route(int route)
 {
-    if (route != 0 && route != NTB_ROUTE_SIMT && route != NTB_ROUTE_TC_F16 && route != NTB_ROUTE_TC_3XTF32)
+    if (route != 0 && route != NTB_ROUTE_SIMT && route != NTB_ROUTE_TC_F16 && route != NTB_ROUTE_TC_3XTF32 &&
+        route != NTB_ROUTE_TC_F16_PAIR)
         return NTB_ERR_ARG;
     gForcedRoute.store(route);
     return NTB_OK;

@@ -45,10 +45,12 @@ EncodeTiledFn GetEncodeTiled();
 
 /* true when the tcgen05/TMA route can address this problem (alignment, strides) */
 bool TcEligible(const Problem & p);
-int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream);
+/* *route receives the NTB_ROUTE_* code of the kernel launched */
+int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int * route);
 int LaunchSimt(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream);
 
 void CountLaunch();
+int ForcedRoute();           /* value of the last ntb_set_route() */
 
 static inline size_t ElemSize(int dt) { return dt == NTB_X_FLOAT16 ? 2 : 4; }
 

@@ -26,6 +26,7 @@
  */
 #include "ntb_internal.h"
 #include <cuda_fp16.h>
+#include <cstdlib>
 
 namespace ntb {
 
@@ -35,6 +36,9 @@ constexpr int BM = 128;             /* rows of an output tile = UMMA M = TMEM la
 constexpr int ROW_BYTES = 128;      /* one swizzle row: 64 halves or 32 floats of K (or MN) */
 constexpr int A_TILE_BYTES = BM * ROW_BYTES;
 constexpr int UMMA_K_BYTES = 32;    /* K extent of one tcgen05.mma: 16 halves / 8 tf32 */
+/* time of a pair's 256-wide tile relative to a single CTA's 256-wide tile */
+constexpr double PAIR_TILE_COST = 0.75;
+constexpr double PAIR2_TILE_COST = 0.75;  /* per 256 rows of the 512-row pair tile */
 constexpr int FP32_CHUNK_BLOCKS = 8;  /* fp32 route: 8 k-blocks = 256 of K per TMEM accumulation chain */
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;   /* about two seconds */
 
@@ -47,9 +51,22 @@ struct TcParams {
     int tilesM, tilesN;
     long long totalTiles;
     int cVec;               /* C rows can be accessed with 16-byte vectors */
+    int pfDist;             /* producer asks L2 for the boxes of k-block kb + pfDist while loading kb; 0 = off */
+    int group;              /* m-blocks per band of the tile walk */
     float alpha, beta;
     int * status;
 };
+
+/* Optional wait accounting (compile with -DNTB_WAIT_STATS): cycles each role of the
+   CTA-pair kernel spends blocked on its barriers, summed over CTAs.
+   0 producer on empty, 1 MMA on full, 2 MMA on tempty, 3 epilogue warp 2 on tfull,
+   4 kernel cycles of CTA 0's producer lane, 5 CTAs counted */
+#ifdef NTB_WAIT_STATS
+__device__ unsigned long long gWaitStats[8];
+#define NTB_TIMED(slot, expr) do { long long t0_ = clock64(); expr; wstat[slot] += clock64() - t0_; } while (0)
+#else
+#define NTB_TIMED(slot, expr) do { expr; } while (0)
+#endif
 
 /* ---------------------------------------------------------------- PTX wrappers */
 
@@ -73,27 +90,31 @@ __device__ __forceinline__ void MbarArrive(uint32_t bar)
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory");
 }
 
-__device__ __forceinline__ uint32_t MbarTryWait(uint32_t bar, uint32_t parity)
+/* One probe of the barrier. The hardware may park the thread for up to `hintNs`
+   nanoseconds while the phase is incomplete (it is woken when the phase completes), which
+   keeps waiting warps out of the issue slots. */
+__device__ __forceinline__ uint32_t MbarTryWait(uint32_t bar, uint32_t parity, uint32_t hintNs)
 {
     uint32_t done;
     asm volatile("{\n\t.reg .pred p;\n\t"
-                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
                  "selp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+                 : "=r"(done) : "r"(bar), "r"(parity), "r"(hintNs) : "memory");
     return done;
 }
 
 /* Bounded wait. Returns false when the CTA is aborting (this waiter ran out of time, or
    another one did). */
-__device__ __forceinline__ bool MbarWait(uint32_t bar, uint32_t parity, volatile int * abortFlag, int * status)
+__device__ __forceinline__ bool MbarWait(uint32_t bar, uint32_t parity, volatile int * abortFlag, int * status,
+                                         uint32_t hintNs = 200)
 {
-    if (MbarTryWait(bar, parity))
+    if (MbarTryWait(bar, parity, hintNs))
         return true;
     const long long t0 = clock64();
     for (uint32_t it = 1; ; ++it) {
-        if (MbarTryWait(bar, parity))
+        if (MbarTryWait(bar, parity, hintNs))
             return true;
-        if ((it & 255u) == 0) {
+        if ((it & 63u) == 0) {
             if (*abortFlag)
                 return false;
             if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
@@ -105,11 +126,30 @@ __device__ __forceinline__ bool MbarWait(uint32_t bar, uint32_t parity, volatile
     }
 }
 
+/* The same wait for a whole warp: lane 0 polls, the other lanes rest at the warp barrier. */
+__device__ __forceinline__ bool MbarWaitWarp(uint32_t bar, uint32_t parity, volatile int * abortFlag, int * status,
+                                             uint32_t hintNs)
+{
+    uint32_t ok = 1;
+    if ((threadIdx.x & 31) == 0)
+        ok = MbarWait(bar, parity, abortFlag, status, hintNs) ? 1u : 0u;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    return ok != 0;
+}
+
 __device__ __forceinline__ void TmaLoad3D(uint32_t dst, const CUtensorMap * map, uint32_t bar, int c0, int c1, int c2)
 {
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
                  " [%0], [%1, {%3, %4, %5}], [%2];"
                  :: "r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
+/* asks L2 to fetch a box ahead of the load that will need it: by then the load finds its
+   sectors in L2 and completes with L2 latency instead of DRAM latency */
+__device__ __forceinline__ void TmaPrefetch3D(const CUtensorMap * map, int c0, int c1, int c2)
+{
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];"
+                 :: "l"(map), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 
 __device__ __forceinline__ void TcFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -267,16 +307,15 @@ struct TileCoord {
     int prob, mBlk, nBlk;
 };
 
-/* Tiles of one problem are visited in bands of 8 m-blocks, n fastest inside a band's
+/* Tiles of one problem are visited in bands of `GROUP` m-blocks, n fastest inside a band's
    column, so the CTAs running at the same time share A row panels and B column panels
    in L2. */
-__device__ __forceinline__ TileCoord DecodeTile(long long t, int tilesM, int tilesN)
+__device__ __forceinline__ TileCoord DecodeTile(long long t, int tilesM, int tilesN, int GROUP)
 {
     const int perProb = tilesM * tilesN;
     TileCoord tc;
     tc.prob = (int)(t / perProb);
     int r = (int)(t % perProb);
-    const int GROUP = 8;
     int band = r / (GROUP * tilesN);
     int first = band * GROUP;
     int rows = min(tilesM - first, GROUP);
@@ -357,7 +396,7 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             uint32_t ph = 0;
             bool ok = true;
             for (long long t = firstTile; ok && t < p.totalTiles; t += tileStep) {
-                TileCoord tc = DecodeTile(t, p.tilesM, p.tilesN);
+                TileCoord tc = DecodeTile(t, p.tilesM, p.tilesN, p.group);
                 const int m0 = tc.mBlk * BM, n0 = tc.nBlk * BN;
                 const int ba = BatchCoord(p.aSel, tc.prob, p.Q);
                 const int bb = BatchCoord(p.bSel, tc.prob, p.Q);
@@ -385,6 +424,25 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
 #pragma unroll
                         for (int j = 0; j < BN / EPR; j++)
                             TmaLoad3D(bDst + j * EPR * ROW_BYTES, &tmB, full, n0 + j * EPR, k0, bb);
+                    }
+                    if (p.pfDist > 0 && kb + p.pfDist < kBlocks) {
+                        const int kp = k0 + p.pfDist * EPR;
+                        if (!p.aMN) {
+                            TmaPrefetch3D(&tmA, kp, m0, ba);
+                        }
+                        else {
+#pragma unroll
+                            for (int j = 0; j < BM / EPR; j++)
+                                TmaPrefetch3D(&tmA, m0 + j * EPR, kp, ba);
+                        }
+                        if (!p.bMN) {
+                            TmaPrefetch3D(&tmB, kp, n0, bb);
+                        }
+                        else {
+#pragma unroll
+                            for (int j = 0; j < BN / EPR; j++)
+                                TmaPrefetch3D(&tmB, n0 + j * EPR, kp, bb);
+                        }
                     }
                     if (++s == STAGES) { s = 0; ph ^= 1u; }
                 }
@@ -458,7 +516,7 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         uint32_t it = 0;
         bool ok = true;
         for (long long t = firstTile; ok && t < p.totalTiles; t += tileStep) {
-            TileCoord tc = DecodeTile(t, p.tilesM, p.tilesN);
+            TileCoord tc = DecodeTile(t, p.tilesM, p.tilesN, p.group);
             const int row = tc.mBlk * BM + sub * 32 + lane;
             const int n0 = tc.nBlk * BN;
             const int pp = tc.prob / p.Q, qq = tc.prob % p.Q;
@@ -467,7 +525,7 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             if (MODE == 0) {
                 /* one accumulator hand-over per tile: load 32 columns, scale, store */
                 const uint32_t buf = it & 1u;
-                ok = MbarWait(SmemAddr(&barTFull[buf]), (it >> 1) & 1u, abortPtr, p.status);
+                ok = MbarWaitWarp(SmemAddr(&barTFull[buf]), (it >> 1) & 1u, abortPtr, p.status, 2000);
                 if (!ok)
                     break;
                 TcFenceAfter();
@@ -498,7 +556,7 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 float acc[ACC_N];
                 for (int kb0 = 0; ok && kb0 < kBlocks; kb0 += chunkBlocks, ++it) {
                     const uint32_t buf = it & 1u;
-                    ok = MbarWait(SmemAddr(&barTFull[buf]), (it >> 1) & 1u, abortPtr, p.status);
+                    ok = MbarWaitWarp(SmemAddr(&barTFull[buf]), (it >> 1) & 1u, abortPtr, p.status, 2000);
                     if (!ok)
                         break;
                     TcFenceAfter();
@@ -583,6 +641,288 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     }
 }
 
+/* ---------------------------------------------------------------- the CTA-pair kernel */
+
+__device__ __forceinline__ uint32_t ClusterCtaRank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+/* address of the same shared-memory object in the CTA of rank `rank` of this cluster */
+__device__ __forceinline__ uint32_t MapToCta(uint32_t addr, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+
+__device__ __forceinline__ void MbarArriveCluster(uint32_t clusterAddr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(clusterAddr) : "memory");
+}
+
+__device__ __forceinline__ void ClusterSync()
+{
+    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+
+/* TMA load whose completion bytes are counted on a barrier of the pair's leader CTA */
+__device__ __forceinline__ void TmaLoad3DPair(uint32_t dst, const CUtensorMap * map, uint32_t barCluster, int c0, int c1, int c2)
+{
+    asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+                 " [%0], [%1, {%3, %4, %5}], [%2];"
+                 :: "r"(dst), "l"(map), "r"(barCluster), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
+__device__ __forceinline__ void TcMmaPair(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc, uint32_t iDesc, uint32_t accumulate)
+{
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 :: "r"(dTmem), "l"(aDesc), "l"(bDesc), "r"(iDesc), "r"(accumulate) : "memory");
+}
+
+/* arrive, once the MMAs issued so far have finished, on the barrier at this offset in
+   both CTAs of the pair */
+__device__ __forceinline__ void TcCommitPair(uint32_t bar)
+{
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 :: "r"(bar), "h"(mask) : "memory");
+}
+
+/*
+ * fp16 GEMM on pairs of CTAs (a cluster of two SMs, tcgen05 cta_group::2). A pair owns a
+ * (256 * MSUB) x 256 output tile. CTA r of the pair loads, per k-block, MSUB sub-tiles of
+ * 128 rows of A (rows j*256 + r*128.. of the tile) and columns r*128.. of the B tile into
+ * its own shared memory; the leader (rank 0) issues, per k-step, MSUB 256 x 256 x 16 MMAs
+ * that read both CTAs' shared memory, and each CTA's TMEM receives its 128 rows of each
+ * accumulator. Every CTA fetches half as much of B per flop as a lone 128 x 256 CTA
+ * (MSUB = 1), and with MSUB = 2 half as much again: the rate at which an SM can take in
+ * operand tiles, not the tensor pipe, is what bounds the smaller tiles on large products.
+ *
+ * MSUB = 1 keeps two 256-column accumulators, so the epilogue of a tile overlaps the main
+ * loop of the next; MSUB = 2 fills all 512 TMEM columns with one tile and the epilogue runs
+ * between main loops while the producer already refills the pipeline.
+ *
+ * Barriers: full[s] lives in the leader and counts the bytes of both CTAs' loads;
+ * empty[s] and tfull[buf] exist in both CTAs and are signalled together by the leader's
+ * tcgen05.commit; tempty[buf] lives in the leader and collects the eight epilogue warps
+ * of the pair. All waits are local and bounded as in the single-CTA kernel.
+ */
+template <int MSUB, int STAGES, typename OutT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, TcParams p)
+{
+    constexpr int ES = 2;
+    constexpr int EPR = ROW_BYTES / ES;                 /* 64 halves of K per stage */
+    constexpr int BN = 256;                             /* columns of the pair's tile */
+    constexpr int BNH = BN / 2;                         /* columns of B this CTA loads */
+    constexpr int PM = 2 * BM * MSUB;                   /* rows of the pair's tile */
+    constexpr int NBUF = 2 / MSUB;                      /* accumulator sets that fit in TMEM */
+    constexpr int B_TILE_BYTES = BNH * ROW_BYTES;
+    constexpr int STAGE_BYTES = MSUB * A_TILE_BYTES + B_TILE_BYTES;
+    constexpr int TMEM_COLS = 512;
+    constexpr int KSTEPS = ROW_BYTES / UMMA_K_BYTES;
+    static_assert(MSUB == 1 || MSUB == 2, "one or two A sub-tiles per CTA");
+
+    extern __shared__ uint8_t smemRaw[];
+    __shared__ __align__(8) uint64_t barFull[STAGES];
+    __shared__ __align__(8) uint64_t barEmpty[STAGES];
+    __shared__ __align__(8) uint64_t barTFull[2];
+    __shared__ __align__(8) uint64_t barTEmpty[2];
+    __shared__ uint32_t tmemBaseSlot;
+    __shared__ int abortFlag;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = ClusterCtaRank();
+    const uint32_t smemBase = (SmemAddr(smemRaw) + 1023u) & ~1023u;
+    volatile int * abortPtr = &abortFlag;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            MbarInit(SmemAddr(&barFull[s]), 1);
+            MbarInit(SmemAddr(&barEmpty[s]), 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            MbarInit(SmemAddr(&barTFull[b]), 1);
+            MbarInit(SmemAddr(&barTEmpty[b]), 8);
+        }
+        abortFlag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     :: "r"(SmemAddr(&tmemBaseSlot)), "r"((uint32_t)TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    TcFenceBefore();
+    ClusterSync();              /* barriers of both CTAs are initialised before any remote signal */
+    TcFenceAfter();
+    const uint32_t tmemBase = *(volatile uint32_t *)&tmemBaseSlot;
+
+#ifdef NTB_WAIT_STATS
+    long long wstat[4] = {0, 0, 0, 0};
+    const long long kernelT0 = clock64();
+#endif
+    const int kBlocks = (p.K + EPR - 1) / EPR;
+    const long long firstTile = blockIdx.x >> 1;
+    const long long tileStep = gridDim.x >> 1;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (long long t = firstTile; ok && t < p.totalTiles; t += tileStep) {
+                TileCoord tc = DecodeTile(t, p.tilesM, p.tilesN, p.group);
+                const int m0 = tc.mBlk * PM + (int)rank * BM;
+                const int n0 = tc.nBlk * BN + (int)rank * BNH;
+                const int ba = BatchCoord(p.aSel, tc.prob, p.Q);
+                const int bb = BatchCoord(p.bSel, tc.prob, p.Q);
+                for (int kb = 0; kb < kBlocks; kb++) {
+                    NTB_TIMED(0, ok = MbarWait(SmemAddr(&barEmpty[s]), ph ^ 1u, abortPtr, p.status));
+                    if (!ok)
+                        break;
+                    const uint32_t fullLeader = MapToCta(SmemAddr(&barFull[s]), 0);
+                    const uint32_t aDst = smemBase + s * STAGE_BYTES;
+                    const uint32_t bDst = aDst + MSUB * A_TILE_BYTES;
+                    const int k0 = kb * EPR;
+                    if (rank == 0)
+                        MbarExpectTx(SmemAddr(&barFull[s]), 2 * STAGE_BYTES);
+#pragma unroll
+                    for (int sub = 0; sub < MSUB; sub++) {
+                        const int ms = m0 + sub * 2 * BM;
+                        const uint32_t dst = aDst + sub * A_TILE_BYTES;
+                        if (!p.aMN) {
+                            TmaLoad3DPair(dst, &tmA, fullLeader, k0, ms, ba);
+                        }
+                        else {
+#pragma unroll
+                            for (int j = 0; j < BM / EPR; j++)
+                                TmaLoad3DPair(dst + j * EPR * ROW_BYTES, &tmA, fullLeader, ms + j * EPR, k0, ba);
+                        }
+                    }
+                    if (!p.bMN) {
+                        TmaLoad3DPair(bDst, &tmB, fullLeader, k0, n0, bb);
+                    }
+                    else {
+#pragma unroll
+                        for (int j = 0; j < BNH / EPR; j++)
+                            TmaLoad3DPair(bDst + j * EPR * ROW_BYTES, &tmB, fullLeader, n0 + j * EPR, k0, bb);
+                    }
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    }
+    else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            const uint32_t iDesc = (1u << 4) | ((uint32_t)(p.aMN ? 1 : 0) << 15) | ((uint32_t)(p.bMN ? 1 : 0) << 16)
+                                 | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+            const uint32_t aLbo = p.aMN ? EPR * ROW_BYTES : 16, bLbo = p.bMN ? EPR * ROW_BYTES : 16;
+            const uint32_t mnStep = (UMMA_K_BYTES / ES) * ROW_BYTES;
+            const uint32_t aStep = p.aMN ? mnStep : UMMA_K_BYTES;
+            const uint32_t bStep = p.bMN ? mnStep : UMMA_K_BYTES;
+            int s = 0;
+            uint32_t ph = 0;
+            uint32_t it = 0;
+            bool ok = true;
+            for (long long t = firstTile; ok && t < p.totalTiles; t += tileStep, ++it) {
+                const uint32_t buf = it % NBUF;
+                NTB_TIMED(2, ok = MbarWait(SmemAddr(&barTEmpty[buf]), ((it / NBUF) & 1u) ^ 1u, abortPtr, p.status));
+                if (!ok)
+                    break;
+                TcFenceAfter();
+                const uint32_t dTmem = tmemBase + buf * (MSUB * BN);
+                for (int kb = 0; kb < kBlocks; kb++) {
+                    NTB_TIMED(1, ok = MbarWait(SmemAddr(&barFull[s]), ph, abortPtr, p.status));
+                    if (!ok)
+                        break;
+                    TcFenceAfter();
+                    const uint32_t aT = smemBase + s * STAGE_BYTES;
+                    const uint32_t bT = aT + MSUB * A_TILE_BYTES;
+#pragma unroll
+                    for (int k = 0; k < KSTEPS; k++) {
+                        const uint64_t bD = SmemDesc(bT + k * bStep, bLbo, 1024, 2);
+#pragma unroll
+                        for (int sub = 0; sub < MSUB; sub++) {
+                            const uint64_t aD = SmemDesc(aT + sub * A_TILE_BYTES + k * aStep, aLbo, 1024, 2);
+                            TcMmaPair(dTmem + sub * BN, aD, bD, iDesc, (kb | k) != 0 ? 1u : 0u);
+                        }
+                    }
+                    TcCommitPair(SmemAddr(&barEmpty[s]));
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                }
+                if (ok)
+                    TcCommitPair(SmemAddr(&barTFull[buf]));
+            }
+        }
+    }
+    else {
+        const int sub32 = warp & 3;
+        uint32_t it = 0;
+        bool ok = true;
+        for (long long t = firstTile; ok && t < p.totalTiles; t += tileStep, ++it) {
+            TileCoord tc = DecodeTile(t, p.tilesM, p.tilesN, p.group);
+            const int n0 = tc.nBlk * BN;
+            const int pp = tc.prob / p.Q, qq = tc.prob % p.Q;
+            OutT * cBase = (OutT *)p.c + pp * p.sCp + qq * p.sCq;
+            const uint32_t buf = it % NBUF;
+            NTB_TIMED(3, ok = MbarWaitWarp(SmemAddr(&barTFull[buf]), (it / NBUF) & 1u, abortPtr, p.status, 2000));
+            if (!ok)
+                break;
+            TcFenceAfter();
+#pragma unroll 1
+            for (int sub = 0; sub < MSUB; sub++) {
+                const int row = tc.mBlk * PM + sub * 2 * BM + (int)rank * BM + sub32 * 32 + lane;
+                OutT * cRow = cBase + (long long)row * p.ldc;
+                const bool rowOk = row < p.M;
+                const uint32_t tRow = tmemBase + ((uint32_t)(sub32 * 32) << 16) + buf * (MSUB * BN) + sub * BN;
+#pragma unroll 1
+                for (int ch = 0; ch < BN / 32; ch++) {
+                    const int c0 = n0 + ch * 32;
+                    if (c0 >= p.N)
+                        break;
+                    float v[32];
+                    TmemLoad32(tRow + ch * 32, v);
+                    if (rowOk)
+                        StoreRow32(cRow, c0, v, p);
+                }
+            }
+            TcFenceBefore();
+            __syncwarp();
+            if (lane == 0)
+                MbarArriveCluster(MapToCta(SmemAddr(&barTEmpty[buf]), 0));
+        }
+    }
+
+#ifdef NTB_WAIT_STATS
+    if (lane == 0 && (warp <= 2)) {
+        if (warp == 0) { atomicAdd(&gWaitStats[0], (unsigned long long)wstat[0]); atomicAdd(&gWaitStats[5], 1ULL);
+                         if (blockIdx.x == 0) atomicAdd(&gWaitStats[4], (unsigned long long)(clock64() - kernelT0)); }
+        if (warp == 1) { atomicAdd(&gWaitStats[1], (unsigned long long)wstat[1]); atomicAdd(&gWaitStats[2], (unsigned long long)wstat[2]); }
+        if (warp == 2) atomicAdd(&gWaitStats[3], (unsigned long long)wstat[3]);
+    }
+#endif
+    __syncwarp();
+    if (*abortPtr) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) { }
+    }
+    TcFenceBefore();
+    ClusterSync();              /* neither CTA's shared memory or TMEM goes away while the other may still use it */
+    TcFenceAfter();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;"
+                     :: "r"(tmemBase), "r"((uint32_t)TMEM_COLS) : "memory");
+    }
+}
+
 /* ---------------------------------------------------------------- host side */
 
 /* offset of operand x for problem i is idx * stride with idx in {p, q, i}; find which */
@@ -616,6 +956,24 @@ int LaunchOne(const CUtensorMap & tmA, const CUtensorMap & tmB, const TcParams &
     return cudaGetLastError() == cudaSuccess ? NTB_OK : NTB_ERR_CUDA;
 }
 
+template <int MSUB, int STAGES, typename OutT>
+int LaunchPair(const CUtensorMap & tmA, const CUtensorMap & tmB, const TcParams & tp, int pairs, cudaStream_t stream)
+{
+    constexpr int smem = (MSUB * A_TILE_BYTES + 128 * ROW_BYTES) * STAGES + 1024;
+    auto kern = GemmTcPairKernel<MSUB, STAGES, OutT>;
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return NTB_ERR_CUDA;
+        configured[dev] = true;
+    }
+    kern<<<2 * pairs, 192, smem, stream>>>(tmA, tmB, tp);
+    CountLaunch();
+    return cudaGetLastError() == cudaSuccess ? NTB_OK : NTB_ERR_CUDA;
+}
+
 int EncodeOperand(CUtensorMap * map, int mode, const void * base, int mnMajor, int rows, int cols,
                   long long ld, long long batchStride, int batchExtent, int tileRows)
 {
@@ -639,7 +997,17 @@ int EncodeOperand(CUtensorMap * map, int mode, const void * base, int mnMajor, i
     return r == CUDA_SUCCESS ? NTB_OK : NTB_ERR_CUDA;
 }
 
-/* cost model: waves of tiles over the SMs times the tile's width, plus a fixed per-tile cost */
+/* integer tuning knob from the environment, read at every launch */
+int Knob(const char * name, int dflt)
+{
+    const char * v = getenv(name);
+    return v && *v ? atoi(v) : dflt;
+}
+
+/* cost model: waves of tiles over the SMs times the tile's width, plus a fixed per-tile
+   cost. Returns the tile width of the single-CTA kernel, or 0 / -1 for the CTA-pair kernel
+   with 256 x 256 / 512 x 256 tiles, which cost less per flop because each CTA takes in
+   fewer operand bytes per flop. */
 int PickBN(const Problem & p, int smCount, int mode)
 {
     const int cand[3] = { 256, 128, 64 };
@@ -651,6 +1019,16 @@ int PickBN(const Problem & p, int smCount, int mode)
         long long waves = (tiles + smCount - 1) / smCount;
         double cost = (double)waves * (bn + 24);
         if (cost < bestCost) { bestCost = cost; best = bn; }
+    }
+    if (mode == 0 && smCount >= 2) {
+        const long long pairs = smCount / 2;
+        for (int msub = 1; msub <= 2; msub++) {
+            const int pm = 2 * BM * msub;
+            long long tiles = (long long)((p.M + pm - 1) / pm) * ((p.N + 255) / 256) * p.count;
+            long long waves = (tiles + pairs - 1) / pairs;
+            double cost = (double)waves * (256 * msub * (msub == 1 ? PAIR_TILE_COST : PAIR2_TILE_COST) + 24 * msub);
+            if (cost < bestCost) { bestCost = cost; best = msub == 1 ? 0 : -1; }
+        }
     }
     return best;
 }
@@ -684,21 +1062,35 @@ bool TcEligible(const Problem & p)
     return true;
 }
 
-int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream)
+int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int * route)
 {
     const int mode = p.dtAB == NTB_X_FLOAT16 ? 0 : 1;
-    const int bn = PickBN(p, ctx.smCount, mode);
+    int bn = PickBN(p, ctx.smCount, mode);
+    const int forced = ForcedRoute();
+    if (mode == 0 && forced == NTB_ROUTE_TC_F16_PAIR && ctx.smCount >= 2 && bn > 0)
+        bn = Knob("NTB_PAIR_MSUB", 2) == 1 ? 0 : -1;
+    if (bn <= 0 && forced == NTB_ROUTE_TC_F16)
+        bn = 256;
+    const bool pair = bn <= 0;
+    const int msub = bn == -1 ? 2 : 1;
+    if (pair)
+        bn = 256;
+    *route = mode != 0 ? NTB_ROUTE_TC_3XTF32 : pair ? NTB_ROUTE_TC_F16_PAIR : NTB_ROUTE_TC_F16;
     const int P = p.count / p.Q;
 
     TcParams tp;
     tp.c = p.c; tp.ldc = p.ldc; tp.sCp = p.sCp; tp.sCq = p.sCq;
     tp.M = p.M; tp.N = p.N; tp.K = p.K; tp.count = p.count; tp.Q = p.Q;
     tp.aMN = p.aMN; tp.bMN = p.bMN;
-    tp.tilesM = (p.M + BM - 1) / BM;
+    tp.tilesM = pair ? (p.M + 2 * BM * msub - 1) / (2 * BM * msub) : (p.M + BM - 1) / BM;
     tp.tilesN = (p.N + bn - 1) / bn;
     tp.totalTiles = (long long)tp.tilesM * tp.tilesN * p.count;
     tp.alpha = p.alpha; tp.beta = p.beta;
     tp.status = ctx.status;
+    tp.pfDist = Knob("NTB_PREFETCH_DIST", 0);
+    tp.group = Knob("NTB_TILE_GROUP", 8);
+    if (tp.group < 1)
+        tp.group = 1;
     const long long ces = ElemSize(p.dtC);
     tp.cVec = (((uintptr_t)p.c & 15) == 0) && ((p.ldc * ces) % 16 == 0) &&
               ((p.sCp * ces) % 16 == 0) && ((p.sCq * ces) % 16 == 0);
@@ -712,11 +1104,19 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream)
     int rc = EncodeOperand(&tmA, mode, p.a, p.aMN, p.aRows, p.aCols, p.lda, stA, extA, BM);
     if (rc != NTB_OK)
         return rc;
-    rc = EncodeOperand(&tmB, mode, p.b, p.bMN, p.bRows, p.bCols, p.ldb, stB, extB, bn);
+    rc = EncodeOperand(&tmB, mode, p.b, p.bMN, p.bRows, p.bCols, p.ldb, stB, extB, pair ? 128 : bn);
     if (rc != NTB_OK)
         return rc;
 
     const int grid = (int)(tp.totalTiles < ctx.smCount ? tp.totalTiles : ctx.smCount);
+    if (pair) {
+        const int pairs = (int)(tp.totalTiles < ctx.smCount / 2 ? tp.totalTiles : ctx.smCount / 2);
+        if (msub == 2)
+            return p.dtC == NTB_X_FLOAT16 ? LaunchPair<2, 4, __half>(tmA, tmB, tp, pairs, stream)
+                                          : LaunchPair<2, 4, float>(tmA, tmB, tp, pairs, stream);
+        return p.dtC == NTB_X_FLOAT16 ? LaunchPair<1, 6, __half>(tmA, tmB, tp, pairs, stream)
+                                      : LaunchPair<1, 6, float>(tmA, tmB, tp, pairs, stream);
+    }
     if (mode == 0) {
         const bool half = p.dtC == NTB_X_FLOAT16;
         if (bn == 256)
@@ -732,5 +1132,16 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream)
         return LaunchOne<1, 128, 3, float>(tmA, tmB, tp, grid, stream);
     return LaunchOne<1, 64, 4, float>(tmA, tmB, tp, grid, stream);
 }
+
+
+#ifdef NTB_WAIT_STATS
+extern "C" void ntb_debug_wait_stats(unsigned long long * out)
+{
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, gWaitStats, sizeof(unsigned long long) * 8);
+    unsigned long long zero[8] = {0};
+    cudaMemcpyToSymbol(gWaitStats, zero, sizeof(zero));
+}
+#endif
 
 }

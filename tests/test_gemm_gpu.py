@@ -117,7 +117,8 @@ def test_2d_all_transpositions(dtype, tA, tB, oracle):
         es = 2 if dtype == torch.float16 else 4
         aligned = (a.shape[1] * es) % 16 == 0 and (b.shape[1] * es) % 16 == 0
         if aligned:
-            assert route == (capi.ROUTE_TC_F16 if dtype == torch.float16 else capi.ROUTE_TC_3XTF32), (M, N, K)
+            assert route in ((capi.ROUTE_TC_F16, capi.ROUTE_TC_F16_PAIR) if dtype == torch.float16
+                             else (capi.ROUTE_TC_3XTF32,)), (M, N, K)
         else:
             assert route == capi.ROUTE_SIMT, (M, N, K)
         err = rel_fro(c.float().cpu().numpy(), want)
@@ -211,6 +212,38 @@ def test_forced_ffma_route_matches_tensor_core_route(oracle):
     status_ok()
 
 
+@pytest.mark.parametrize("msub", ["1", "2"])
+def test_cta_pair_route(msub, oracle):
+    """The cta_group::2 kernel, forced on shapes the cost model would give to one CTA:
+    ragged edges in M, N and K, every transposition, batches, alpha/beta, fp32 output."""
+    rng = np.random.default_rng(300 + int(msub))
+    L = capi.lib()
+    os.environ["NTB_PAIR_MSUB"] = msub
+    assert L.ntb_set_route(capi.ROUTE_TC_F16_PAIR) == capi.OK
+    try:
+        shapes = [(256, 256, 64), (520, 264, 136), (136, 304, 72), (1024, 512, 320), (8, 8, 8)]
+        n = 0
+        for tA in (X_TRANS, X_NOTRANS):
+            for tB in (X_TRANS, X_NOTRANS):
+                for (M, N, K) in shapes:
+                    alpha, beta = AB[n % len(AB)]
+                    n += 1
+                    cnt = 1 + n % 3
+                    a = round_to_half(stored(rng, (cnt,), M, K, tA))
+                    b = round_to_half(stored(rng, (cnt,), K, N, tB))
+                    c0 = round_to_half(rng.normal(size=(cnt, M, N)).astype(np.float32))
+                    out_dtype = torch.float32 if n % 4 == 0 else torch.float16
+                    c = to_dev(c0, out_dtype)
+                    ops._MatrixMulBatched(to_dev(a, torch.float16), tA, to_dev(b, torch.float16), tB, c, alpha, beta)
+                    assert L.ntb_last_route() == capi.ROUTE_TC_F16_PAIR
+                    err = rel_fro(c.float().cpu().numpy(), oracle.matmul_batched(a, tA, b, tB, alpha, beta, c0))
+                    assert err <= 2e-3, (M, N, K, tA, tB, alpha, beta, err)
+    finally:
+        L.ntb_set_route(0)
+        os.environ.pop("NTB_PAIR_MSUB", None)
+    status_ok()
+
+
 # --------------------------------------------------------------- semantics corners
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
@@ -263,7 +296,7 @@ def test_column_shard_of_resident_operand(oracle):
     c = torch.zeros(M, n, device=DEV, dtype=torch.float16)
     rc = L.ntb_gemm(0, None, ta.data_ptr(), X_NOTRANS, tb.data_ptr() + n0 * 2, X_NOTRANS, c.data_ptr(),
                     capi.X_FLOAT16, capi.X_FLOAT16, M, K, K, n, M, n, K, Nfull, n, 1.0, 0.0)
-    assert rc == capi.OK and L.ntb_last_route() == capi.ROUTE_TC_F16
+    assert rc == capi.OK and L.ntb_last_route() in (capi.ROUTE_TC_F16, capi.ROUTE_TC_F16_PAIR)
     want = oracle.matmul2d(a, X_NOTRANS, np.ascontiguousarray(b[:, n0:n0 + n]), X_NOTRANS)
     assert rel_fro(c.float().cpu().numpy(), want) <= 2e-3
     status_ok()
