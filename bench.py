@@ -42,8 +42,8 @@ FLOPS_PER_RANK = 2.0 * N_DIM * N_DIM * N_DIM
 # algorithmic bytes of one launch: read A, B and C0 once, write C once (fp16)
 BYTES_PER_RANK = 4.0 * N_DIM * N_DIM * 2
 # DRAM traffic of one launch measured by ncu (dram__bytes_read.sum + dram__bytes_write.sum),
-# see profiles/; None until a capture of this kernel and size exists
-NCU_TRAFFIC_BYTES = None
+# profiles/gemm_f16_8192_ncu.md (CTA-pair kernel, this shape)
+NCU_TRAFFIC_BYTES = 1.326e9
 
 
 def load_peaks():

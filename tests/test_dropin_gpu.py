@@ -1,0 +1,63 @@
+"""Drop-in check at link level: the reference's GPU build with its matrix-multiplication
+translation units replaced by niutensor_b200/host/nts_matmul_shim.cpp (built by
+`make -C oracle dropin` into oracle/_ref/, which exists only where the reference sources
+were available at build time). The reference's own unit tests for this path then run on
+the new kernels, and user-level calls the reference has no test for are compared with the
+CPU oracle."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+
+from oracle.oracle import rel_fro, X_NOTRANS, X_TRANS
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LIB = os.path.join(ROOT, "oracle", "_ref", "libnts_dropin.so")
+
+
+@pytest.fixture(scope="module")
+def dropin():
+    if not os.path.exists(LIB):
+        pytest.skip("drop-in check library not built (needs the reference sources)")
+    from niutensor_b200 import capi
+    capi.lib()                                  # libntb_gemm.so first, by its full path
+    lib = ctypes.CDLL(LIB)
+    lib.dropin_run_reference_tests.restype = ctypes.c_int
+    return lib
+
+
+def test_reference_unit_tests_pass_on_the_new_kernels(dropin):
+    mask = dropin.dropin_run_reference_tests()
+    assert mask == 0b1111, "TestMatrixMul / 2D / 2DParallel / Batched bitmask: %s" % bin(mask)
+
+
+def test_user_level_bmmul_on_half_tensors(dropin, oracle):
+    rng = np.random.default_rng(31)
+    batch, length, dk = 6, 128, 64
+    q = rng.normal(size=(batch, length, dk)).astype(np.float16)
+    k = rng.normal(size=(batch, length, dk)).astype(np.float16)
+    s = np.zeros((batch, length, length), np.float16)
+    u16 = ctypes.POINTER(ctypes.c_ushort)
+    rc = dropin.dropin_bmmul_half(0, batch, length, dk, q.ctypes.data_as(u16), k.ctypes.data_as(u16),
+                                  s.ctypes.data_as(u16), ctypes.c_float(0.125))
+    assert rc == 0
+    want = oracle.matmul_batched(q.astype(np.float32), X_NOTRANS, k.astype(np.float32), X_TRANS, 0.125)
+    assert rel_fro(s.astype(np.float32), want) <= 2e-3
+
+
+def test_reference_mulandshift_runs_on_the_shim(dropin, oracle):
+    rng = np.random.default_rng(32)
+    rows, din, dout = 96, 128, 160
+    x = rng.normal(size=(rows, din)).astype(np.float32)
+    w = (rng.normal(size=(din, dout)) / np.sqrt(din)).astype(np.float32)
+    b = rng.normal(size=(dout,)).astype(np.float32)
+    y = np.zeros((rows, dout), np.float32)
+    fp = ctypes.POINTER(ctypes.c_float)
+    rc = dropin.dropin_mulandshift_f32(0, rows, din, dout, x.ctypes.data_as(fp), w.ctypes.data_as(fp),
+                                       b.ctypes.data_as(fp), y.ctypes.data_as(fp))
+    assert rc == 0
+    want = oracle.matmul2d(x, X_NOTRANS, w, X_NOTRANS) + b[None, :]
+    assert rel_fro(y, want) <= 1e-5
