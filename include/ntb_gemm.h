@@ -141,6 +141,26 @@ int ntb_gemm_host(int devID, void * stream,
                   long long strideA, long long strideB, long long strideC,
                   int count, float alpha, float beta);
 
+/*
+ * Host-buffer form of one product that allocates nothing. It has no counterpart in the
+ * reference, whose wrappers borrow scratch from XMem or cudaMalloc (XTensorBLAS.cu:
+ * 329-343); it exists for callers that cannot allocate device memory at call time: a
+ * process whose XMem pools already own the GPU's memory, where a library-side cudaMalloc
+ * may fail, and worker threads sharing a device, which cudaMalloc / cudaFree would stall.
+ * a, b and c are HOST buffers, packed (pitch = columns). All device scratch -- staging for
+ * a, b, c and the status word -- is a fixed array inside the library, so the staged
+ * operands (each rounded up to 256 bytes) must fit in NTB_NOALLOC_MAX_BYTES; a larger
+ * problem returns NTB_ERR_LIMIT. Calls on one device share that array: do not overlap
+ * them. The first call on a device looks up the array's address; make it before any
+ * stream capture begins. The call returns after the result is back in c.
+ */
+#define NTB_NOALLOC_MAX_BYTES (16u << 20)
+int ntb_gemm_host_noalloc(int devID, void * stream,
+                          const void * a, int transA, const void * b, int transB, void * c,
+                          int dtypeAB, int dtypeC,
+                          int na, int ma, int nb, int mb, int nc, int mc,
+                          float alpha, float beta);
+
 /* Route taken by the calling thread's most recent successful launch (NTB_ROUTE_*). */
 int ntb_last_route(void);
 

@@ -13,6 +13,7 @@ X_INT, X_INT8, X_FLOAT, X_FLOAT16, X_DOUBLE = 0, 1, 2, 3, 4
 X_TRANS, X_NOTRANS = 0, 1
 ROUTE_NONE, ROUTE_TC_F16, ROUTE_TC_3XTF32, ROUTE_SIMT, ROUTE_TC_F16_PAIR = 0, 1, 2, 3, 4
 OK, ERR_ARG, ERR_SHAPE, ERR_DTYPE, ERR_CUDA, ERR_DEVICE_WAIT, ERR_LIMIT = range(7)
+NOALLOC_MAX_BYTES = 16 << 20
 
 _vp = ctypes.c_void_p
 _i = ctypes.c_int
@@ -27,6 +28,7 @@ PROTOTYPES = {
     "ntb_gemm_list": (_i, [_i, _vp, ctypes.POINTER(_vp), _i, ctypes.POINTER(_vp), _i, ctypes.POINTER(_vp),
                            _i, _i, _i] + [_i] * 6 + [_f, _f]),
     "ntb_gemm_host": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _i, _i] + [_i] * 6 + [_ll] * 3 + [_i, _f, _f]),
+    "ntb_gemm_host_noalloc": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _i, _i] + [_i] * 6 + [_f, _f]),
     "ntb_last_route": (_i, []),
     "ntb_set_route": (_i, [_i]),
     "ntb_device_status": (_i, [_i]),

@@ -1,0 +1,163 @@
+/*
+ * ntb_gemm_host_noalloc: the host-buffer product for callers that must not allocate.
+ *
+ * Who needs it: a NiuTensor process normally hands all of a GPU's free memory to its XMem
+ * pools at start-up, so a later cudaMalloc inside a library can simply fail; and trainer
+ * worker threads that share a device cannot afford cudaMalloc / cudaFree either, because
+ * both stall every stream of the device while they run. The regular host-buffer entry
+ * point (ntb_gemm_host) grows its staging buffers with cudaMalloc, and every other entry
+ * point creates its device context (a cudaMalloc'ed status word) on first use. This one
+ * touches no allocator at all: its device-side scratch -- the status word the kernels
+ * write when a bounded wait runs out, plus the staging space for a, b and c -- is the
+ * fixed array below, which every GPU that loads this library holds until the process
+ * exits.
+ *
+ * Limit: the staged a, b and c (each rounded up to 256 bytes) must fit in
+ * NTB_NOALLOC_MAX_BYTES; larger problems are refused with NTB_ERR_LIMIT.
+ *
+ * Sharing: all calls on a device use the same array, and it keeps what the previous call
+ * left in it. Each call clears the status word before it launches; nothing else needs to
+ * start at zero, because the staging areas are fully overwritten by the copies (c only when
+ * beta != 0, and it is never read otherwise). Two calls that overlap on one GPU -- from two
+ * threads, or on two streams -- race on the array; callers serialise them.
+ *
+ * Set-up: the first call on a device resolves the array's device address (with that device
+ * current) and caches it; make that first call before starting any stream capture.
+ */
+#include "ntb_internal.h"
+#include <mutex>
+#include <cstring>
+
+namespace ntb {
+
+namespace {
+
+constexpr size_t HEADER_BYTES = 256;          /* status word, padded so staging stays 256-aligned */
+
+/* In host code this name is only a handle for the runtime's symbol calls, not an address a
+   kernel could use; the device address comes from cudaGetSymbolAddress in SetUp(). */
+static __device__ __align__(256) unsigned char gNoAllocScratch[HEADER_BYTES + NTB_NOALLOC_MAX_BYTES];
+
+constexpr int MAX_DEV = 64;
+std::mutex gSetUpLock;
+unsigned char * gScratchAddr[MAX_DEV] = { nullptr };
+int gSmCount[MAX_DEV] = { 0 };
+
+size_t RoundUp256(size_t n)
+{
+    return (n + 255) & ~(size_t)255;
+}
+
+/* once per device, with that device current */
+int SetUp(int dev, unsigned char ** out, int * smCount)
+{
+    std::lock_guard<std::mutex> g(gSetUpLock);
+    if (!gScratchAddr[dev]) {
+        unsigned char * ptr = nullptr;
+        if (cudaGetSymbolAddress((void **)&ptr, gNoAllocScratch) != cudaSuccess || !ptr ||
+            cudaDeviceGetAttribute(&gSmCount[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+            cudaGetLastError();
+            return NTB_ERR_CUDA;
+        }
+        gScratchAddr[dev] = ptr;
+    }
+    *out = gScratchAddr[dev];
+    *smCount = gSmCount[dev];
+    return NTB_OK;
+}
+
+}
+
+}
+
+using namespace ntb;
+
+extern "C" int ntb_gemm_host_noalloc(int devID, void * stream,
+                                     const void * a, int transA, const void * b, int transB, void * c,
+                                     int dtypeAB, int dtypeC,
+                                     int na, int ma, int nb, int mb, int nc, int mc,
+                                     float alpha, float beta)
+{
+    if (!a || !b || !c || devID < 0 || devID >= MAX_DEV)
+        return NTB_ERR_ARG;
+    if ((transA != NTB_X_TRANS && transA != NTB_X_NOTRANS) || (transB != NTB_X_TRANS && transB != NTB_X_NOTRANS))
+        return NTB_ERR_ARG;
+    if (na < 0 || ma < 0 || nb < 0 || mb < 0 || nc < 0 || mc < 0)
+        return NTB_ERR_ARG;
+    const bool f16 = dtypeAB == NTB_X_FLOAT16 && (dtypeC == NTB_X_FLOAT16 || dtypeC == NTB_X_FLOAT);
+    const bool f32 = dtypeAB == NTB_X_FLOAT && dtypeC == NTB_X_FLOAT;
+    if (!f16 && !f32)
+        return NTB_ERR_DTYPE;
+    const int an = transA == NTB_X_TRANS ? ma : na, am = transA == NTB_X_TRANS ? na : ma;
+    const int bn = transB == NTB_X_TRANS ? mb : nb, bm = transB == NTB_X_TRANS ? nb : mb;
+    if (am != bn || an != nc || bm != mc)
+        return NTB_ERR_SHAPE;
+    if (nc == 0 || mc == 0)
+        return NTB_OK;
+
+    const size_t aBytes = (size_t)na * ma * ElemSize(dtypeAB);
+    const size_t bBytes = (size_t)nb * mb * ElemSize(dtypeAB);
+    const size_t cBytes = (size_t)nc * mc * ElemSize(dtypeC);
+    if (RoundUp256(aBytes) + RoundUp256(bBytes) + RoundUp256(cBytes) > (size_t)NTB_NOALLOC_MAX_BYTES)
+        return NTB_ERR_LIMIT;      /* the fixed scratch array cannot hold this problem */
+
+    int prev = -1;
+    if (cudaGetDevice(&prev) != cudaSuccess || (prev != devID && cudaSetDevice(devID) != cudaSuccess)) {
+        cudaGetLastError();
+        return NTB_ERR_CUDA;
+    }
+    int rc = NTB_OK;
+    int hostStatus = 0;
+    do {
+        unsigned char * scratch = nullptr;
+        DeviceCtx ctx;
+        memset(&ctx, 0, sizeof(ctx));
+        ctx.devID = devID;
+        rc = SetUp(devID, &scratch, &ctx.smCount);
+        if (rc != NTB_OK)
+            break;
+        ctx.status = (int *)scratch;
+        unsigned char * dA = scratch + HEADER_BYTES;
+        unsigned char * dB = dA + RoundUp256(aBytes);
+        unsigned char * dC = dB + RoundUp256(bBytes);
+        cudaStream_t st = (cudaStream_t)stream;
+
+        rc = NTB_ERR_CUDA;
+        /* the array still holds the previous call's status word: clear it */
+        if (cudaMemsetAsync(scratch, 0, HEADER_BYTES, st) != cudaSuccess)
+            break;
+        if (aBytes && cudaMemcpyAsync(dA, a, aBytes, cudaMemcpyHostToDevice, st) != cudaSuccess)
+            break;
+        if (bBytes && cudaMemcpyAsync(dB, b, bBytes, cudaMemcpyHostToDevice, st) != cudaSuccess)
+            break;
+        if (beta != 0.f && cudaMemcpyAsync(dC, c, cBytes, cudaMemcpyHostToDevice, st) != cudaSuccess)
+            break;
+
+        Problem p;
+        memset(&p, 0, sizeof(p));
+        p.a = dA; p.b = dB; p.c = dC;
+        p.dtAB = dtypeAB; p.dtC = dtypeC;
+        p.aMN = transA == NTB_X_TRANS;
+        p.bMN = transB == NTB_X_NOTRANS;
+        p.M = an; p.N = bm; p.K = am;
+        p.aRows = na; p.aCols = ma; p.bRows = nb; p.bCols = mb;
+        p.lda = ma; p.ldb = mb; p.ldc = mc;
+        p.count = 1; p.Q = 1;
+        p.alpha = alpha; p.beta = beta;
+        int route = NTB_ROUTE_NONE;
+        rc = TcEligible(p) ? LaunchTc(ctx, p, st, &route) : LaunchSimt(ctx, p, st);
+        if (rc != NTB_OK)
+            break;
+        rc = NTB_ERR_CUDA;
+        if (cudaMemcpyAsync(c, dC, cBytes, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+            cudaMemcpyAsync(&hostStatus, scratch, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+            cudaStreamSynchronize(st) != cudaSuccess)
+            break;
+        rc = hostStatus == 0 ? NTB_OK : NTB_ERR_DEVICE_WAIT;
+    } while (0);
+    if (rc == NTB_ERR_CUDA)
+        cudaGetLastError();
+    if (prev >= 0 && prev != devID)
+        cudaSetDevice(prev);
+    return rc;
+}
