@@ -260,6 +260,21 @@ def main_ours(args):
     tflops = FLOPS_PER_RANK * world / (ms_per_step * 1e-3) / 1e12
     per_gpu_tflops = tflops / world
 
+    # optional: what a caller who wants the whole C on every rank pays on top (not in `value`)
+    gather_ms = None
+    if world > 1:
+        from niutensor_b200 import shard
+        shard.gather_columns(c, N_DIM * world)
+        barrier()
+        e0.record()
+        for _ in range(3):
+            shard.gather_columns(c, N_DIM * world)
+        e1.record()
+        barrier()
+        g = torch.tensor([e0.elapsed_time(e1) / 3], device=dev, dtype=torch.float64)
+        dist.all_reduce(g, op=dist.ReduceOp.MAX)
+        gather_ms = float(g.item())
+
     if args.kernel_only:
         if rank == 0:
             print(json.dumps({"metric": "MatrixMul TFLOP/s", "value": tflops, "unit": "TFLOP/s",
@@ -321,6 +336,11 @@ def main_ours(args):
             "gpu_launches": int(launches),
             "clocks": clocks,
         }
+        if gather_ms is not None:
+            line["allgather_of_c"] = {"ms": gather_ms, "bytes_received_per_gpu": (world - 1) * mat_bytes,
+                                      "gb_per_s_per_gpu": (world - 1) * mat_bytes / (gather_ms * 1e-3) / 1e9,
+                                      "note": "NCCL all_gather + local re-interleave; only for callers that "
+                                              "need the full C on every rank; not part of value"}
         if world == 1:
             try:
                 line["cpu_baseline"] = {k: v for k, v in time_cpu(2, 1).items() if k != "ms_per_step"}

@@ -1,0 +1,87 @@
+"""Sharding one matrix product across the ranks of a process group (one process per GPU).
+
+Output tiles of a product are independent, so the path shards with no exchange:
+
+* 2-D products shard the columns of C: A is replicated, rank r owns the columns
+  [n0, n1) of op(B) -- rows of the stored B when transposedB == X_TRANS (the output layer:
+  rows of the vocabulary matrix), columns of the stored B otherwise -- and produces
+  C[:, n0:n1].
+* batched products (BMMul) shard the leading (batch) extent.
+
+A collective is needed only when a caller wants the whole C on every rank:
+`gather_columns` / `gather_batch` (all_gather over the group's backend -- NCCL over NVLink
+on GPUs, gloo in CPU tests -- plus the local re-interleave, because column shards of a
+row-major matrix are not contiguous).
+"""
+import torch
+import torch.distributed as dist
+
+from .capi import X_TRANS, X_NOTRANS
+
+
+def split_range(total, world, rank, multiple=1):
+    """[lo, hi) of `total` units for `rank`: contiguous, balanced in units of `multiple`
+    (the last rank takes the ragged remainder)."""
+    if world < 1 or not (0 <= rank < world):
+        raise ValueError("bad rank %d of %d" % (rank, world))
+    blocks = (total + multiple - 1) // multiple
+    lo = (blocks * rank // world) * multiple
+    hi = (blocks * (rank + 1) // world) * multiple
+    return min(lo, total), min(hi, total)
+
+
+def column_shard(n_cols, world, rank):
+    """Columns of C owned by `rank`; multiples of 8 keep fp16 row segments 16-byte aligned,
+    which the TMA-fed kernels need when the shard is addressed inside a resident matrix."""
+    return split_range(n_cols, world, rank, 8)
+
+
+def local_b(b_full, transposedB, world, rank):
+    """The part of a full stored B that `rank` multiplies by (a view, no copy)."""
+    if transposedB == X_TRANS:
+        lo, hi = column_shard(b_full.shape[-2], world, rank)
+        return b_full[..., lo:hi, :]
+    lo, hi = column_shard(b_full.shape[-1], world, rank)
+    return b_full[..., :, lo:hi]
+
+
+def matmul_column_shard(a, transposedA, b_local, transposedB, alpha=1.0, beta=0.0, c_local=None):
+    """This rank's columns of C = alpha * op(a) * op(b) + beta * C from its packed shard of B."""
+    from . import ops
+    if not b_local.is_contiguous():
+        b_local = b_local.contiguous()
+    return ops.MatrixMul(a, transposedA, b_local, transposedB, alpha, beta, c=c_local)
+
+
+def gather_columns(c_local, n_cols, group=None):
+    """All ranks receive the full [..., M, n_cols] matrix from the per-rank column shards."""
+    world = dist.get_world_size(group)
+    widths = [column_shard(n_cols, world, r) for r in range(world)]
+    wmax = max(hi - lo for lo, hi in widths)
+    lead = tuple(c_local.shape[:-1])
+    # equal-sized pieces for all_gather: pad the narrower shards
+    piece = torch.zeros(lead + (wmax,), dtype=c_local.dtype, device=c_local.device)
+    piece[..., :c_local.shape[-1]] = c_local
+    pieces = [torch.empty_like(piece) for _ in range(world)]
+    dist.all_gather(pieces, piece, group=group)
+    full = torch.empty(lead + (n_cols,), dtype=c_local.dtype, device=c_local.device)
+    for r, (lo, hi) in enumerate(widths):
+        full[..., lo:hi] = pieces[r][..., :hi - lo]
+    return full
+
+
+def batch_shard(count, world, rank):
+    return split_range(count, world, rank, 1)
+
+
+def gather_batch(c_local, count, group=None):
+    """All ranks receive all `count` result matrices from per-rank batch shards."""
+    world = dist.get_world_size(group)
+    sizes = [batch_shard(count, world, r) for r in range(world)]
+    bmax = max(hi - lo for lo, hi in sizes)
+    tail = tuple(c_local.shape[1:])
+    piece = torch.zeros((bmax,) + tail, dtype=c_local.dtype, device=c_local.device)
+    piece[:c_local.shape[0]] = c_local
+    pieces = [torch.empty_like(piece) for _ in range(world)]
+    dist.all_gather(pieces, piece, group=group)
+    return torch.cat([pieces[r][:hi - lo] for r, (lo, hi) in enumerate(sizes)], dim=0)
