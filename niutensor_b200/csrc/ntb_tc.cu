@@ -39,6 +39,11 @@ constexpr int UMMA_K_BYTES = 32;    /* K extent of one tcgen05.mma: 16 halves / 
 /* time of a pair's 256-wide tile relative to a single CTA's 256-wide tile */
 constexpr double PAIR_TILE_COST = 0.75;
 constexpr double PAIR2_TILE_COST = 0.75;  /* per 256 rows of the 512-row pair tile */
+/* fp32 route: threads that split operands into hi/lo planes (warps 6 and up) */
+#ifndef NTB_CONV_THREADS
+#define NTB_CONV_THREADS 128
+#endif
+constexpr int CONV_THREADS = NTB_CONV_THREADS;
 constexpr int FP32_CHUNK_BLOCKS = 8;  /* fp32 route: 8 k-blocks = 256 of K per TMEM accumulation chain */
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;   /* about two seconds */
 
@@ -51,6 +56,8 @@ struct TcParams {
     int tilesM, tilesN;
     long long totalTiles;
     int cVec;               /* C rows can be accessed with 16-byte vectors */
+    int cTma;               /* C is written with TMA stores from swizzled staging boxes */
+    int cSel;               /* index that walks C's batch dimension in its tensor map (as aSel) */
     int pfDist;             /* producer asks L2 for the boxes of k-block kb + pfDist while loading kb; 0 = off */
     int group;              /* m-blocks per band of the tile walk */
     float alpha, beta;
@@ -193,6 +200,25 @@ __device__ __forceinline__ void TmemLoad32(uint32_t taddr, float * v)
         v[i] = __uint_as_float(r[i]);
 }
 
+/* the reverse: 32 values into 32 consecutive columns of this thread's TMEM lane */
+__device__ __forceinline__ void TmemStore32(uint32_t taddr, const float * v)
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+                 "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+                 :: "r"(taddr),
+                    "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+                    "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+                    "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+                    "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+                    "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+                    "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+                    "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+                    "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+                 : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 /*
  * Shared-memory matrix descriptor of tcgen05.mma: start address, leading and stride byte
  * offsets in 16-byte units, descriptor version 1, and the swizzle code: 2 = 128-byte
@@ -261,45 +287,147 @@ __device__ __forceinline__ float LoadOne(const float * p) { return *p; }
 __device__ __forceinline__ void StoreOne(__half * p, float v) { *p = __float2half_rn(v); }
 __device__ __forceinline__ void StoreOne(float * p, float v) { *p = v; }
 
-/* alpha * v (+ beta * old) for 32 consecutive columns of one output row starting at
-   column c0, written with 16-byte vectors where the row allows it, element by element
-   at a ragged edge or for rows that are not 16-byte aligned */
+/* v <- alpha * v (+ beta * old C) for 32 consecutive columns of one output row starting
+   at column c0; old values are read with 16-byte vectors where the row allows it */
 template <typename OutT>
-__device__ __forceinline__ void StoreRow32(OutT * cRow, int c0, float * v, const TcParams & p)
+__device__ __forceinline__ void ScaleRow32(const OutT * cRow, int c0, bool rowOk, float * v, const TcParams & p)
 {
     constexpr int VN = Vec16<OutT>::N;
+    if (p.beta == 0.f || !rowOk) {
+#pragma unroll
+        for (int e = 0; e < 32; e++)
+            v[e] = p.alpha * v[e];
+        return;
+    }
 #pragma unroll
     for (int g = 0; g < 32 / VN; g++) {
         const int c = c0 + g * VN;
         float * vv = v + g * VN;
         if (p.cVec && c + VN <= p.N) {
-            if (p.beta != 0.f) {
-                float old[VN];
-                LoadVec(cRow + c, old);
+            float old[VN];
+            LoadVec(cRow + c, old);
 #pragma unroll
-                for (int e = 0; e < VN; e++)
-                    vv[e] = fmaf(p.beta, old[e], p.alpha * vv[e]);
-            }
-            else {
-#pragma unroll
-                for (int e = 0; e < VN; e++)
-                    vv[e] = p.alpha * vv[e];
-            }
-            StoreVec(cRow + c, vv);
+            for (int e = 0; e < VN; e++)
+                vv[e] = fmaf(p.beta, old[e], p.alpha * vv[e]);
         }
         else {
 #pragma unroll
             for (int e = 0; e < VN; e++) {
-                if (c + e < p.N) {
-                    float x = p.alpha * vv[e];
-                    if (p.beta != 0.f)
-                        x = fmaf(p.beta, LoadOne(cRow + c + e), x);
-                    StoreOne(cRow + c + e, x);
-                }
+                float x = p.alpha * vv[e];
+                if (c + e < p.N)
+                    x = fmaf(p.beta, LoadOne(cRow + c + e), x);
+                vv[e] = x;
             }
         }
     }
 }
+
+/* final values of 32 consecutive columns of one row, straight from registers: 16-byte
+   vectors where the row allows it, element by element at a ragged edge or for rows that
+   are not 16-byte aligned */
+template <typename OutT>
+__device__ __forceinline__ void StoreRow32Direct(OutT * cRow, int c0, const float * v, const TcParams & p)
+{
+    constexpr int VN = Vec16<OutT>::N;
+#pragma unroll
+    for (int g = 0; g < 32 / VN; g++) {
+        const int c = c0 + g * VN;
+        const float * vv = v + g * VN;
+        if (p.cVec && c + VN <= p.N) {
+            StoreVec(cRow + c, vv);
+        }
+        else {
+#pragma unroll
+            for (int e = 0; e < VN; e++)
+                if (c + e < p.N)
+                    StoreOne(cRow + c + e, vv[e]);
+        }
+    }
+}
+
+/*
+ * Per-warp writer of output tiles. When C allows it (16-byte aligned base and pitches)
+ * the 32 rows x 128 bytes a warp produces are staged in shared memory in the 128-byte
+ * swizzled layout (conflict-free for one-row-per-lane writes) and sent to HBM by one TMA
+ * store per box: full 128-byte lines, asynchronous, clipped by TMA at the ragged edges of
+ * C. Two boxes per warp alternate; before a box is refilled the warp waits until the store
+ * that last used it has read it. Otherwise values go out with direct stores.
+ */
+constexpr int EPI_BOX_BYTES = 32 * ROW_BYTES;               /* 32 rows x 128 B */
+constexpr int EPI_BYTES = 4 * 2 * EPI_BOX_BYTES;            /* four epilogue warps, two boxes each */
+
+template <typename OutT>
+struct TileWriter {
+    static constexpr int BOX_COLS = ROW_BYTES / (int)sizeof(OutT);   /* 64 halves / 32 floats */
+    static constexpr int CHUNKS = 32 * (int)sizeof(OutT) / 16;      /* 16-byte chunks per 32 columns */
+    uint32_t stage;          /* shared-memory address of this warp's two boxes */
+    uint32_t boxes;          /* boxes handed to TMA so far */
+    const CUtensorMap * map;
+
+    __device__ __forceinline__ void Init(uint32_t epiBase, int sub, const CUtensorMap * m)
+    {
+        stage = epiBase + sub * 2 * EPI_BOX_BYTES;
+        boxes = 0;
+        map = m;
+    }
+
+    /* v: raw accumulators of columns c0 .. c0+31 of this lane's row (row = row0 + lane) */
+    __device__ __forceinline__ void Put32(const TcParams & p, OutT * cRow, bool rowOk, int row0, int c0,
+                                          int batch, float * v, int lane)
+    {
+        ScaleRow32(cRow, c0, rowOk, v, p);
+        if (!p.cTma) {
+            if (rowOk)
+                StoreRow32Direct(cRow, c0, v, p);
+            return;
+        }
+        const int colInBox = c0 % BOX_COLS;
+        const uint32_t box = stage + (boxes & 1u) * EPI_BOX_BYTES;
+        if (colInBox == 0) {
+            /* the store that used this box two boxes ago must have read it */
+            if (lane == 0 && boxes >= 2)
+                asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            __syncwarp();
+        }
+        const uint32_t rowAddr = box + lane * ROW_BYTES;
+        const int firstChunk = colInBox * (int)sizeof(OutT) / 16;
+#pragma unroll
+        for (int j = 0; j < CHUNKS; j++) {
+            const uint32_t dst = rowAddr + (uint32_t)(((firstChunk + j) ^ (lane & 7)) << 4);
+            uint32_t w0, w1, w2, w3;
+            if (sizeof(OutT) == 2) {
+                __half2 h0 = __floats2half2_rn(v[j * 8 + 0], v[j * 8 + 1]);
+                __half2 h1 = __floats2half2_rn(v[j * 8 + 2], v[j * 8 + 3]);
+                __half2 h2 = __floats2half2_rn(v[j * 8 + 4], v[j * 8 + 5]);
+                __half2 h3 = __floats2half2_rn(v[j * 8 + 6], v[j * 8 + 7]);
+                w0 = *(uint32_t *)&h0; w1 = *(uint32_t *)&h1; w2 = *(uint32_t *)&h2; w3 = *(uint32_t *)&h3;
+            }
+            else {
+                w0 = __float_as_uint(v[j * 4 + 0]); w1 = __float_as_uint(v[j * 4 + 1]);
+                w2 = __float_as_uint(v[j * 4 + 2]); w3 = __float_as_uint(v[j * 4 + 3]);
+            }
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" :: "r"(dst), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+        }
+        if (colInBox + 32 == BOX_COLS || c0 + 32 >= p.N) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0 && row0 < p.M) {
+                asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
+                             :: "l"(map), "r"(c0 - colInBox), "r"(row0), "r"(batch), "r"(box) : "memory");
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+            boxes++;
+        }
+    }
+
+    /* all of this warp's stores have completed */
+    __device__ __forceinline__ void Finish(int lane)
+    {
+        if (lane == 0)
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        __syncwarp();
+    }
+};
 
 /* ---------------------------------------------------------------- tile walk */
 
@@ -333,15 +461,18 @@ __device__ __forceinline__ int BatchCoord(int sel, int prob, int Q)
 /* ---------------------------------------------------------------- the kernel */
 
 template <int MODE, int BN, int STAGES, typename OutT>
-__global__ void __launch_bounds__(MODE == 0 ? 192 : 320, 1)
-GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, TcParams p)
+__global__ void __launch_bounds__(MODE == 0 ? 192 : 192 + CONV_THREADS, 1)
+GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+             const __grid_constant__ CUtensorMap tmC, TcParams p)
 {
     constexpr int ES = MODE == 0 ? 2 : 4;               /* operand element size */
     constexpr int EPR = ROW_BYTES / ES;                 /* elements per 128-byte row = K per stage */
     constexpr int B_TILE_BYTES = BN * ROW_BYTES;
     constexpr int PLANE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
     constexpr int STAGE_BYTES = PLANE_BYTES * (MODE == 0 ? 1 : 2);   /* fp32: hi plane + lo plane */
-    constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;             /* two accumulators; power of two */
+    /* two accumulators, plus (fp32 route) one running sum; a power of two */
+    constexpr int TMEM_NEED = (MODE == 0 ? 2 : 3) * BN;
+    constexpr int TMEM_COLS = TMEM_NEED <= 128 ? 128 : TMEM_NEED <= 256 ? 256 : 512;
     constexpr int KSTEPS = ROW_BYTES / UMMA_K_BYTES;                 /* 4 */
     static_assert(BN == 64 || BN == 128 || BN == 256, "tile width");
 
@@ -363,7 +494,7 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         for (int s = 0; s < STAGES; s++) {
             MbarInit(SmemAddr(&barFull[s]), 1);
             MbarInit(SmemAddr(&barEmpty[s]), 1);
-            MbarInit(SmemAddr(&barConv[s]), 128);
+            MbarInit(SmemAddr(&barConv[s]), CONV_THREADS);
         }
         for (int b = 0; b < 2; b++) {
             MbarInit(SmemAddr(&barTFull[b]), 1);
@@ -515,11 +646,15 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         const int sub = warp & 3;                 /* TMEM sub-partition this warp may read */
         uint32_t it = 0;
         bool ok = true;
+        TileWriter<OutT> writer;
+        writer.Init(smemBase + STAGES * STAGE_BYTES, sub, &tmC);
         for (long long t = firstTile; ok && t < p.totalTiles; t += tileStep) {
             TileCoord tc = DecodeTile(t, p.tilesM, p.tilesN, p.group);
-            const int row = tc.mBlk * BM + sub * 32 + lane;
+            const int row0 = tc.mBlk * BM + sub * 32;
+            const int row = row0 + lane;
             const int n0 = tc.nBlk * BN;
             const int pp = tc.prob / p.Q, qq = tc.prob % p.Q;
+            const int bc = BatchCoord(p.cSel, tc.prob, p.Q);
             OutT * cRow = (OutT *)p.c + pp * p.sCp + qq * p.sCq + (long long)row * p.ldc;
             const bool rowOk = row < p.M;
             if (MODE == 0) {
@@ -537,8 +672,7 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                         break;                     /* uniform across the warp */
                     float v[32];
                     TmemLoad32(tRow + ch * 32, v);
-                    if (rowOk)
-                        StoreRow32(cRow, c0, v, p);
+                    writer.Put32(p, cRow, rowOk, row0, c0, bc, v, lane);
                 }
                 TcFenceBefore();
                 __syncwarp();
@@ -551,9 +685,9 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                    instruction, an error that grows with the length of the accumulation
                    chain. K is therefore cut into chunks of chunkBlocks k-blocks; each
                    chunk's partial sum is handed over here and added, with round-to-nearest
-                   FADDs, to a running sum kept in registers. */
-                constexpr int ACC_N = MODE == 0 ? 32 : BN;
-                float acc[ACC_N];
+                   FADDs, to a running sum kept in a third TMEM region (the sum of a
+                   128-column row does not fit the registers a ten-warp CTA leaves a thread). */
+                const uint32_t tRun = tmemBase + ((uint32_t)(sub * 32) << 16) + 2 * BN;   /* running sum */
                 for (int kb0 = 0; ok && kb0 < kBlocks; kb0 += chunkBlocks, ++it) {
                     const uint32_t buf = it & 1u;
                     ok = MbarWaitWarp(SmemAddr(&barTFull[buf]), (it >> 1) & 1u, abortPtr, p.status, 2000);
@@ -561,19 +695,25 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                         break;
                     TcFenceAfter();
                     const uint32_t tRow = tmemBase + ((uint32_t)(sub * 32) << 16) + buf * BN;
-#pragma unroll
-                    for (int ch = 0; ch < ACC_N / 32; ch++) {
+                    const bool first = kb0 == 0, last = kb0 + chunkBlocks >= kBlocks;
+#pragma unroll 1
+                    for (int ch = 0; ch < BN / 32; ch++) {
                         float v[32];
                         TmemLoad32(tRow + ch * 32, v);
-                        if (kb0 == 0) {
+                        if (!first) {
+                            float r[32];
+                            TmemLoad32(tRun + ch * 32, r);
 #pragma unroll
                             for (int e = 0; e < 32; e++)
-                                acc[ch * 32 + e] = v[e];
+                                v[e] += r[e];
+                        }
+                        if (!last) {
+                            TmemStore32(tRun + ch * 32, v);
                         }
                         else {
-#pragma unroll
-                            for (int e = 0; e < 32; e++)
-                                acc[ch * 32 + e] += v[e];
+                            const int c0 = n0 + ch * 32;
+                            if (c0 < p.N)
+                                writer.Put32(p, cRow, rowOk, row0, c0, bc, v, lane);
                         }
                     }
                     TcFenceBefore();
@@ -581,20 +721,13 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                     if (lane == 0)
                         MbarArrive(SmemAddr(&barTEmpty[buf]));
                 }
-                if (ok && rowOk) {
-#pragma unroll
-                    for (int ch = 0; ch < ACC_N / 32; ch++) {
-                        const int c0 = n0 + ch * 32;
-                        if (c0 < p.N)
-                            StoreRow32(cRow, c0, acc + ch * 32, p);
-                    }
-                }
             }
         }
+        writer.Finish(lane);
     }
     else if (MODE != 0) {
         /* ------------------------------------------------------------ fp32 hi/lo split */
-        const int ct = threadIdx.x - 192;         /* 0..127 */
+        const int ct = threadIdx.x - 192;         /* 0 .. CONV_THREADS-1 */
         int s = 0;
         uint32_t ph = 0;
         bool ok = true;
@@ -606,7 +739,7 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 uint8_t * hi = smemRaw + (smemBase - SmemAddr(smemRaw)) + s * STAGE_BYTES;
                 uint8_t * lo = hi + PLANE_BYTES;
 #pragma unroll 4
-                for (int i = ct; i < PLANE_BYTES / 16; i += 128) {
+                for (int i = ct; i < PLANE_BYTES / 16; i += CONV_THREADS) {
                     float4 x = *(float4 *)(hi + i * 16);
                     float4 h, l;
                     uint32_t u;
@@ -714,7 +847,8 @@ __device__ __forceinline__ void TcCommitPair(uint32_t bar)
  */
 template <int MSUB, int STAGES, typename OutT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
-GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, TcParams p)
+GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, TcParams p)
 {
     constexpr int ES = 2;
     constexpr int EPR = ROW_BYTES / ES;                 /* 64 halves of K per stage */
@@ -867,10 +1001,13 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int sub32 = warp & 3;
         uint32_t it = 0;
         bool ok = true;
+        TileWriter<OutT> writer;
+        writer.Init(smemBase + STAGES * STAGE_BYTES, sub32, &tmC);
         for (long long t = firstTile; ok && t < p.totalTiles; t += tileStep, ++it) {
             TileCoord tc = DecodeTile(t, p.tilesM, p.tilesN, p.group);
             const int n0 = tc.nBlk * BN;
             const int pp = tc.prob / p.Q, qq = tc.prob % p.Q;
+            const int bc = BatchCoord(p.cSel, tc.prob, p.Q);
             OutT * cBase = (OutT *)p.c + pp * p.sCp + qq * p.sCq;
             const uint32_t buf = it % NBUF;
             NTB_TIMED(3, ok = MbarWaitWarp(SmemAddr(&barTFull[buf]), (it / NBUF) & 1u, abortPtr, p.status, 2000));
@@ -879,7 +1016,8 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             TcFenceAfter();
 #pragma unroll 1
             for (int sub = 0; sub < MSUB; sub++) {
-                const int row = tc.mBlk * PM + sub * 2 * BM + (int)rank * BM + sub32 * 32 + lane;
+                const int row0 = tc.mBlk * PM + sub * 2 * BM + (int)rank * BM + sub32 * 32;
+                const int row = row0 + lane;
                 OutT * cRow = cBase + (long long)row * p.ldc;
                 const bool rowOk = row < p.M;
                 const uint32_t tRow = tmemBase + ((uint32_t)(sub32 * 32) << 16) + buf * (MSUB * BN) + sub * BN;
@@ -890,8 +1028,7 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         break;
                     float v[32];
                     TmemLoad32(tRow + ch * 32, v);
-                    if (rowOk)
-                        StoreRow32(cRow, c0, v, p);
+                    writer.Put32(p, cRow, rowOk, row0, c0, bc, v, lane);
                 }
             }
             TcFenceBefore();
@@ -899,6 +1036,7 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (lane == 0)
                 MbarArriveCluster(MapToCta(SmemAddr(&barTEmpty[buf]), 0));
         }
+        writer.Finish(lane);
     }
 
 #ifdef NTB_WAIT_STATS
@@ -936,12 +1074,13 @@ bool BatchSelector(long long sp, long long sq, int P, int Q, int * sel, long lon
 }
 
 template <int MODE, int BN, int STAGES, typename OutT>
-int LaunchOne(const CUtensorMap & tmA, const CUtensorMap & tmB, const TcParams & tp, int grid, cudaStream_t stream)
+int LaunchOne(const CUtensorMap & tmA, const CUtensorMap & tmB, const CUtensorMap & tmC, const TcParams & tp, int grid,
+              cudaStream_t stream)
 {
     constexpr int ES = MODE == 0 ? 2 : 4;
     (void)ES;
     constexpr int stage = (A_TILE_BYTES + BN * ROW_BYTES) * (MODE == 0 ? 1 : 2);
-    constexpr int smem = stage * STAGES + 1024;
+    constexpr int smem = stage * STAGES + EPI_BYTES + 1024;
     auto kern = GemmTcKernel<MODE, BN, STAGES, OutT>;
     static bool configured[64] = {false};
     int dev = 0;
@@ -951,15 +1090,16 @@ int LaunchOne(const CUtensorMap & tmA, const CUtensorMap & tmB, const TcParams &
             return NTB_ERR_CUDA;
         configured[dev] = true;
     }
-    kern<<<grid, MODE == 0 ? 192 : 320, smem, stream>>>(tmA, tmB, tp);
+    kern<<<grid, MODE == 0 ? 192 : 192 + CONV_THREADS, smem, stream>>>(tmA, tmB, tmC, tp);
     CountLaunch();
     return cudaGetLastError() == cudaSuccess ? NTB_OK : NTB_ERR_CUDA;
 }
 
 template <int MSUB, int STAGES, typename OutT>
-int LaunchPair(const CUtensorMap & tmA, const CUtensorMap & tmB, const TcParams & tp, int pairs, cudaStream_t stream)
+int LaunchPair(const CUtensorMap & tmA, const CUtensorMap & tmB, const CUtensorMap & tmC, const TcParams & tp, int pairs,
+               cudaStream_t stream)
 {
-    constexpr int smem = (MSUB * A_TILE_BYTES + 128 * ROW_BYTES) * STAGES + 1024;
+    constexpr int smem = (MSUB * A_TILE_BYTES + 128 * ROW_BYTES) * STAGES + EPI_BYTES + 1024;
     auto kern = GemmTcPairKernel<MSUB, STAGES, OutT>;
     static bool configured[64] = {false};
     int dev = 0;
@@ -969,7 +1109,7 @@ int LaunchPair(const CUtensorMap & tmA, const CUtensorMap & tmB, const TcParams 
             return NTB_ERR_CUDA;
         configured[dev] = true;
     }
-    kern<<<2 * pairs, 192, smem, stream>>>(tmA, tmB, tp);
+    kern<<<2 * pairs, 192, smem, stream>>>(tmA, tmB, tmC, tp);
     CountLaunch();
     return cudaGetLastError() == cudaSuccess ? NTB_OK : NTB_ERR_CUDA;
 }
@@ -993,6 +1133,26 @@ int EncodeOperand(CUtensorMap * map, int mode, const void * base, int mnMajor, i
                      3, (void *)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      (mode != 0 && mnMajor) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? NTB_OK : NTB_ERR_CUDA;
+}
+
+/* tensor map of C for the epilogue's stores: boxes of 32 rows x 128 bytes, 128-byte swizzle */
+int EncodeOutput(CUtensorMap * map, int dtC, void * base, int rows, int cols, long long ld,
+                 long long batchStride, int batchExtent)
+{
+    EncodeTiledFn enc = GetEncodeTiled();
+    if (!enc)
+        return NTB_ERR_CUDA;
+    const int es = dtC == NTB_X_FLOAT16 ? 2 : 4;
+    cuuint64_t dims[3] = { (cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batchExtent };
+    cuuint64_t strides[2] = { (cuuint64_t)ld * es,
+                              (cuuint64_t)(batchExtent > 1 ? batchStride : (long long)rows * ld) * es };
+    cuuint32_t box[3] = { (cuuint32_t)(ROW_BYTES / es), 32, 1 };
+    cuuint32_t estr[3] = { 1, 1, 1 };
+    CUresult r = enc(map, dtC == NTB_X_FLOAT16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                     3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? NTB_OK : NTB_ERR_CUDA;
 }
@@ -1108,29 +1268,43 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
     if (rc != NTB_OK)
         return rc;
 
+    /* C through TMA stores when its base, pitch and batch strides are 16-byte aligned and
+       its batch offset is one index times one stride; otherwise direct stores */
+    CUtensorMap tmC = tmA;
+    long long stC = 0;
+    int extC = 1;
+    tp.cSel = 0;
+    tp.cTma = tp.cVec && Knob("NTB_TMA_STORE", 1) != 0 && p.ldc >= p.N &&
+              BatchSelector(p.sCp, p.sCq, P, p.Q, &tp.cSel, &stC, &extC) && stC >= 0;
+    if (tp.cTma) {
+        rc = EncodeOutput(&tmC, p.dtC, p.c, p.M, p.N, p.ldc, stC, extC);
+        if (rc != NTB_OK)
+            return rc;
+    }
+
     const int grid = (int)(tp.totalTiles < ctx.smCount ? tp.totalTiles : ctx.smCount);
     if (pair) {
         const int pairs = (int)(tp.totalTiles < ctx.smCount / 2 ? tp.totalTiles : ctx.smCount / 2);
         if (msub == 2)
-            return p.dtC == NTB_X_FLOAT16 ? LaunchPair<2, 4, __half>(tmA, tmB, tp, pairs, stream)
-                                          : LaunchPair<2, 4, float>(tmA, tmB, tp, pairs, stream);
-        return p.dtC == NTB_X_FLOAT16 ? LaunchPair<1, 6, __half>(tmA, tmB, tp, pairs, stream)
-                                      : LaunchPair<1, 6, float>(tmA, tmB, tp, pairs, stream);
+            return p.dtC == NTB_X_FLOAT16 ? LaunchPair<2, 4, __half>(tmA, tmB, tmC, tp, pairs, stream)
+                                          : LaunchPair<2, 4, float>(tmA, tmB, tmC, tp, pairs, stream);
+        return p.dtC == NTB_X_FLOAT16 ? LaunchPair<1, 6, __half>(tmA, tmB, tmC, tp, pairs, stream)
+                                      : LaunchPair<1, 6, float>(tmA, tmB, tmC, tp, pairs, stream);
     }
     if (mode == 0) {
         const bool half = p.dtC == NTB_X_FLOAT16;
         if (bn == 256)
-            return half ? LaunchOne<0, 256, 4, __half>(tmA, tmB, tp, grid, stream)
-                        : LaunchOne<0, 256, 4, float>(tmA, tmB, tp, grid, stream);
+            return half ? LaunchOne<0, 256, 4, __half>(tmA, tmB, tmC, tp, grid, stream)
+                        : LaunchOne<0, 256, 4, float>(tmA, tmB, tmC, tp, grid, stream);
         if (bn == 128)
-            return half ? LaunchOne<0, 128, 6, __half>(tmA, tmB, tp, grid, stream)
-                        : LaunchOne<0, 128, 6, float>(tmA, tmB, tp, grid, stream);
-        return half ? LaunchOne<0, 64, 8, __half>(tmA, tmB, tp, grid, stream)
-                    : LaunchOne<0, 64, 8, float>(tmA, tmB, tp, grid, stream);
+            return half ? LaunchOne<0, 128, 6, __half>(tmA, tmB, tmC, tp, grid, stream)
+                        : LaunchOne<0, 128, 6, float>(tmA, tmB, tmC, tp, grid, stream);
+        return half ? LaunchOne<0, 64, 8, __half>(tmA, tmB, tmC, tp, grid, stream)
+                    : LaunchOne<0, 64, 8, float>(tmA, tmB, tmC, tp, grid, stream);
     }
     if (bn == 128)
-        return LaunchOne<1, 128, 3, float>(tmA, tmB, tp, grid, stream);
-    return LaunchOne<1, 64, 4, float>(tmA, tmB, tp, grid, stream);
+        return LaunchOne<1, 128, 3, float>(tmA, tmB, tmC, tp, grid, stream);
+    return LaunchOne<1, 64, 4, float>(tmA, tmB, tmC, tp, grid, stream);
 }
 
 
