@@ -27,6 +27,7 @@
 #include "ntb_internal.h"
 #include <cuda_fp16.h>
 #include <cstdlib>
+#include <cmath>
 
 namespace ntb {
 
@@ -36,9 +37,6 @@ constexpr int BM = 128;             /* rows of an output tile = UMMA M = TMEM la
 constexpr int ROW_BYTES = 128;      /* one swizzle row: 64 halves or 32 floats of K (or MN) */
 constexpr int A_TILE_BYTES = BM * ROW_BYTES;
 constexpr int UMMA_K_BYTES = 32;    /* K extent of one tcgen05.mma: 16 halves / 8 tf32 */
-/* time of a pair's 256-wide tile relative to a single CTA's 256-wide tile */
-constexpr double PAIR_TILE_COST = 0.75;
-constexpr double PAIR2_TILE_COST = 0.75;  /* per 256 rows of the 512-row pair tile */
 /* fp32 route: threads that split operands into hi/lo planes (warps 6 and up) */
 #ifndef NTB_CONV_THREADS
 #define NTB_CONV_THREADS 128
@@ -514,6 +512,10 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     TcFenceAfter();
     const uint32_t tmemBase = *(volatile uint32_t *)&tmemBaseSlot;
 
+#ifdef NTB_WAIT_STATS
+    long long wstat[4] = {0, 0, 0, 0};
+    const long long kernelT0 = clock64();
+#endif
     const int kBlocks = (p.K + EPR - 1) / EPR;
     /* k-blocks accumulated in TMEM before the partial sum is handed to the epilogue */
     const int chunkBlocks = MODE == 0 ? kBlocks : FP32_CHUNK_BLOCKS;
@@ -532,7 +534,7 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 const int ba = BatchCoord(p.aSel, tc.prob, p.Q);
                 const int bb = BatchCoord(p.bSel, tc.prob, p.Q);
                 for (int kb = 0; kb < kBlocks; kb++) {
-                    ok = MbarWait(SmemAddr(&barEmpty[s]), ph ^ 1u, abortPtr, p.status);
+                    NTB_TIMED(0, ok = MbarWait(SmemAddr(&barEmpty[s]), ph ^ 1u, abortPtr, p.status));
                     if (!ok)
                         break;
                     const uint32_t full = SmemAddr(&barFull[s]);
@@ -603,14 +605,14 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             for (long long t = firstTile; ok && t < p.totalTiles; t += tileStep) {
                 for (int kb0 = 0; ok && kb0 < kBlocks; kb0 += chunkBlocks, ++it) {
                     const uint32_t buf = it & 1u;
-                    ok = MbarWait(SmemAddr(&barTEmpty[buf]), ((it >> 1) & 1u) ^ 1u, abortPtr, p.status);
+                    NTB_TIMED(2, ok = MbarWait(SmemAddr(&barTEmpty[buf]), ((it >> 1) & 1u) ^ 1u, abortPtr, p.status));
                     if (!ok)
                         break;
                     TcFenceAfter();
                     const uint32_t dTmem = tmemBase + buf * BN;
                     const int kbEnd = min(kBlocks, kb0 + chunkBlocks);
                     for (int kb = kb0; kb < kbEnd; kb++) {
-                        ok = MbarWait(SmemAddr(MODE == 0 ? &barFull[s] : &barConv[s]), ph, abortPtr, p.status);
+                        NTB_TIMED(1, ok = MbarWait(SmemAddr(MODE == 0 ? &barFull[s] : &barConv[s]), ph, abortPtr, p.status));
                         if (!ok)
                             break;
                         TcFenceAfter();
@@ -759,6 +761,13 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     }
 
     /* ---------------------------------------------------------------- teardown */
+#ifdef NTB_WAIT_STATS
+    if (lane == 0 && warp <= 1) {
+        if (warp == 0) { atomicAdd(&gWaitStats[0], (unsigned long long)wstat[0]); atomicAdd(&gWaitStats[5], 1ULL);
+                         if (blockIdx.x == 0) atomicAdd(&gWaitStats[4], (unsigned long long)(clock64() - kernelT0)); }
+        if (warp == 1) { atomicAdd(&gWaitStats[1], (unsigned long long)wstat[1]); atomicAdd(&gWaitStats[2], (unsigned long long)wstat[2]); }
+    }
+#endif
     __syncwarp();
     if (*abortPtr) {
         /* give copies and MMAs in flight time to land before shared memory and TMEM go away */
@@ -1164,29 +1173,42 @@ int Knob(const char * name, int dflt)
     return v && *v ? atoi(v) : dflt;
 }
 
-/* cost model: waves of tiles over the SMs times the tile's width, plus a fixed per-tile
-   cost. Returns the tile width of the single-CTA kernel, or 0 / -1 for the CTA-pair kernel
-   with 256 x 256 / 512 x 256 tiles, which cost less per flop because each CTA takes in
-   fewer operand bytes per flop. */
+/*
+ * Cost model for the tile shape, in SM clocks per CTA: waves x (k-blocks x clocks per
+ * k-block + epilogue and hand-over cost of one tile). A k-block costs the larger of its MMA
+ * time and the time its operand bytes take to arrive (an SM takes in about 57 bytes per
+ * clock here, measured on the large product). Returns the tile width of the single-CTA
+ * kernel, or 0 / -1 for the CTA-pair kernel with 256 x 256 / 512 x 256 tiles. Constants
+ * were fitted to timings of the benchmark configurations on a B200.
+ */
 int PickBN(const Problem & p, int smCount, int mode)
 {
-    const int cand[3] = { 256, 128, 64 };
+    const double ingest = 57.0;                       /* bytes per clock per SM */
+    const int es = mode == 0 ? 2 : 4;
+    const int kElems = ROW_BYTES / es;
+    const double kBlocks = (double)((p.K + kElems - 1) / kElems);
+    const double mmaPerCol = mode == 0 ? 2.0 : 6.0;   /* clocks per k-block per output column (3 passes at half rate for fp32) */
     int best = 128;
     double bestCost = 1e300;
+    const int cand[3] = { 256, 128, 64 };
     for (int i = (mode == 0 ? 0 : 1); i < 3; i++) {
-        int bn = cand[i];
-        long long tiles = (long long)((p.M + BM - 1) / BM) * ((p.N + bn - 1) / bn) * p.count;
-        long long waves = (tiles + smCount - 1) / smCount;
-        double cost = (double)waves * (bn + 24);
+        const int bn = cand[i];
+        const long long tiles = (long long)((p.M + BM - 1) / BM) * ((p.N + bn - 1) / bn) * p.count;
+        const long long waves = (tiles + smCount - 1) / smCount;
+        const double perK = fmax(mmaPerCol * bn, (double)(BM + bn) * ROW_BYTES / ingest);
+        const double cost = (double)waves * (kBlocks * perK + 1500.0 + 4.0 * bn);
         if (cost < bestCost) { bestCost = cost; best = bn; }
     }
     if (mode == 0 && smCount >= 2) {
         const long long pairs = smCount / 2;
         for (int msub = 1; msub <= 2; msub++) {
             const int pm = 2 * BM * msub;
-            long long tiles = (long long)((p.M + pm - 1) / pm) * ((p.N + 255) / 256) * p.count;
-            long long waves = (tiles + pairs - 1) / pairs;
-            double cost = (double)waves * (256 * msub * (msub == 1 ? PAIR_TILE_COST : PAIR2_TILE_COST) + 24 * msub);
+            const long long tiles = (long long)((p.M + pm - 1) / pm) * ((p.N + 255) / 256) * p.count;
+            const long long waves = (tiles + pairs - 1) / pairs;
+            const double perK = fmax(512.0 * msub, (double)(msub * BM + 128) * ROW_BYTES / ingest);
+            /* the second accumulator set of the 512-row tile is not double-buffered: its
+               epilogue is exposed; pairs also pay for cluster start-up and hand-shakes */
+            const double cost = (double)waves * (kBlocks * perK + 2524.0 * msub + (msub == 2 ? 6000.0 : 0.0)) + 2000.0;
             if (cost < bestCost) { bestCost = cost; best = msub == 1 ? 0 : -1; }
         }
     }
@@ -1227,6 +1249,9 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
     const int mode = p.dtAB == NTB_X_FLOAT16 ? 0 : 1;
     int bn = PickBN(p, ctx.smCount, mode);
     const int forced = ForcedRoute();
+    const int knobBN = Knob("NTB_BN", 0);           /* tuning: force the single-CTA tile width */
+    if (knobBN == 64 || knobBN == 128 || (knobBN == 256 && mode == 0))
+        bn = knobBN;
     if (mode == 0 && forced == NTB_ROUTE_TC_F16_PAIR && ctx.smCount >= 2 && bn > 0)
         bn = Knob("NTB_PAIR_MSUB", 2) == 1 ? 0 : -1;
     if (bn <= 0 && forced == NTB_ROUTE_TC_F16)
