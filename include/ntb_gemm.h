@@ -83,6 +83,29 @@ int ntb_gemm(int devID, void * stream,
              float alpha, float beta);
 
 /*
+ * Single GEMM with a fused row-vector bias and optional activation:
+ *
+ *        c = act(alpha * op(a) * op(b) + beta * c + bias)
+ *
+ * bias holds mc values of c's data type (NULL: none) and is added to every row; act is
+ * NTB_ACT_NONE or NTB_ACT_RECTIFY (max(x, 0), source/tensor/function/Rectify.cpp).
+ * Replaces the two-pass MulAndShift of the reference -- _MatrixMul into a scratch tensor,
+ * then _SumDim re-reading and re-writing it (source/tensor/core/arithmetic/
+ * MulAndShift.cpp:66-88, SumDim.cu:43-103) -- and, with NTB_ACT_RECTIFY, the Rectify pass
+ * that follows it in the feed-forward layer (source/sample/transformer/submodel/FFN.cpp:
+ * 90-101). The sum is formed in fp32 and rounded once. A leading-dimension fold of a
+ * (rows = product of its leading extents) is the caller's business, as in ntb_gemm.
+ */
+#define NTB_ACT_NONE    0
+#define NTB_ACT_RECTIFY 1
+int ntb_gemm_bias_act(int devID, void * stream,
+                      const void * a, int transA, const void * b, int transB, const void * bias, void * c,
+                      int dtypeAB, int dtypeC,
+                      int na, int ma, int nb, int mb, int nc, int mc,
+                      long long lda, long long ldb, long long ldc,
+                      float alpha, float beta, int act);
+
+/*
  * `count` GEMMs of one shape whose matrices lie at constant element strides; a stride
  * of 0 reuses one matrix for every problem. One launch covers all problems.
  * Replaces _CudaBLASMatrixMULBatchedStrided

@@ -14,6 +14,7 @@ X_TRANS, X_NOTRANS = 0, 1
 ROUTE_NONE, ROUTE_TC_F16, ROUTE_TC_3XTF32, ROUTE_SIMT, ROUTE_TC_F16_PAIR = 0, 1, 2, 3, 4
 OK, ERR_ARG, ERR_SHAPE, ERR_DTYPE, ERR_CUDA, ERR_DEVICE_WAIT, ERR_LIMIT = range(7)
 NOALLOC_MAX_BYTES = 16 << 20
+ACT_NONE, ACT_RECTIFY = 0, 1
 
 _vp = ctypes.c_void_p
 _i = ctypes.c_int
@@ -23,6 +24,7 @@ _f = ctypes.c_float
 #: every symbol include/ntb_gemm.h declares, with its argument types
 PROTOTYPES = {
     "ntb_gemm": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _i, _i] + [_i] * 6 + [_ll] * 3 + [_f, _f]),
+    "ntb_gemm_bias_act": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i] + [_i] * 6 + [_ll] * 3 + [_f, _f, _i]),
     "ntb_gemm_strided_batched": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _i, _i] + [_i] * 6 + [_ll] * 6 + [_i, _f, _f]),
     "ntb_gemm_broadcast": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _i, _i] + [_i] * 6 + [_i, _i, _f, _f]),
     "ntb_gemm_list": (_i, [_i, _vp, ctypes.POINTER(_vp), _i, ctypes.POINTER(_vp), _i, ctypes.POINTER(_vp),

@@ -211,6 +211,32 @@ int ntb_gemm_strided_batched(int devID, void * stream,
     return Dispatch(devID, (cudaStream_t)stream, p);
 }
 
+int ntb_gemm_bias_act(int devID, void * stream,
+                      const void * a, int transA, const void * b, int transB, const void * bias, void * c,
+                      int dtypeAB, int dtypeC,
+                      int na, int ma, int nb, int mb, int nc, int mc,
+                      long long lda, long long ldb, long long ldc,
+                      float alpha, float beta, int act)
+{
+    Problem p;
+    memset(&p, 0, sizeof(p));
+    int rc = CheckDtypes(dtypeAB, dtypeC);
+    if (rc != NTB_OK)
+        return rc;
+    rc = SetShape(p, transA, transB, na, ma, nb, mb, nc, mc);
+    if (rc != NTB_OK)
+        return rc;
+    if (lda < ma || ldb < mb || ldc < mc || (act != NTB_ACT_NONE && act != NTB_ACT_RECTIFY))
+        return NTB_ERR_ARG;
+    p.a = a; p.b = b; p.c = c;
+    p.dtAB = dtypeAB; p.dtC = dtypeC;
+    p.lda = lda; p.ldb = ldb; p.ldc = ldc;
+    p.count = 1; p.Q = 1;
+    p.alpha = alpha; p.beta = beta;
+    p.bias = bias; p.act = act;
+    return Dispatch(devID, (cudaStream_t)stream, p);
+}
+
 int ntb_gemm(int devID, void * stream,
              const void * a, int transA, const void * b, int transB, void * c,
              int dtypeAB, int dtypeC,

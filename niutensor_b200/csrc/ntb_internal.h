@@ -27,6 +27,8 @@ struct Problem {
     int count, Q;
     long long sAp, sAq, sBp, sBq, sCp, sCq;
     float alpha, beta;
+    const void * bias;      /* optional row vector of N values (type of c) added to every row of every problem */
+    int act;                /* NTB_ACT_NONE / NTB_ACT_RECTIFY, applied last */
 };
 
 struct DeviceCtx {

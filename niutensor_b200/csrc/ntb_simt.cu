@@ -24,6 +24,8 @@ struct SimtParams {
     int M, N, K, count, Q, tilesM, tilesN;
     int aMN, bMN;
     float alpha, beta;
+    const void * bias;
+    int act;
 };
 
 template <typename T> __device__ __forceinline__ float ToF(T x);
@@ -120,6 +122,10 @@ __global__ void __launch_bounds__(NTHREADS) GemmSimtKernel(SimtParams p)
             float v = p.alpha * acc[i][j];
             if (p.beta != 0.f)
                 v = fmaf(p.beta, ToF<TOut>(*dst), v);
+            if (p.bias != nullptr)
+                v += ToF<TOut>(((const TOut *)p.bias)[gn]);
+            if (p.act == NTB_ACT_RECTIFY)
+                v = fmaxf(v, 0.f);
             *dst = FromF<TOut>(v);
         }
     }
@@ -141,6 +147,7 @@ int LaunchSimt(const DeviceCtx & ctx, const Problem & pr, cudaStream_t stream)
     p.tilesN = (pr.N + TN - 1) / TN;
     p.aMN = pr.aMN; p.bMN = pr.bMN;
     p.alpha = pr.alpha; p.beta = pr.beta;
+    p.bias = pr.bias; p.act = pr.act;
     long long tiles = (long long)p.tilesM * p.tilesN * pr.count;
     if (tiles <= 0)
         return NTB_OK;

@@ -59,6 +59,8 @@ struct TcParams {
     int pfDist;             /* producer asks L2 for the boxes of k-block kb + pfDist while loading kb; 0 = off */
     int group;              /* m-blocks per band of the tile walk */
     float alpha, beta;
+    const void * bias;      /* N values of C's type added to every output row, or NULL */
+    int act;                /* 1: max(x, 0) applied last */
     int * status;
 };
 
@@ -285,8 +287,9 @@ __device__ __forceinline__ float LoadOne(const float * p) { return *p; }
 __device__ __forceinline__ void StoreOne(__half * p, float v) { *p = __float2half_rn(v); }
 __device__ __forceinline__ void StoreOne(float * p, float v) { *p = v; }
 
-/* v <- alpha * v (+ beta * old C) for 32 consecutive columns of one output row starting
-   at column c0; old values are read with 16-byte vectors where the row allows it */
+/* v <- act(alpha * v (+ beta * old C) (+ bias)) for 32 consecutive columns of one output
+   row starting at column c0; old values and the bias are read with 16-byte vectors where
+   alignment allows it */
 template <typename OutT>
 __device__ __forceinline__ void ScaleRow32(const OutT * cRow, int c0, bool rowOk, float * v, const TcParams & p)
 {
@@ -295,28 +298,56 @@ __device__ __forceinline__ void ScaleRow32(const OutT * cRow, int c0, bool rowOk
 #pragma unroll
         for (int e = 0; e < 32; e++)
             v[e] = p.alpha * v[e];
-        return;
     }
+    else {
 #pragma unroll
-    for (int g = 0; g < 32 / VN; g++) {
-        const int c = c0 + g * VN;
-        float * vv = v + g * VN;
-        if (p.cVec && c + VN <= p.N) {
-            float old[VN];
-            LoadVec(cRow + c, old);
+        for (int g = 0; g < 32 / VN; g++) {
+            const int c = c0 + g * VN;
+            float * vv = v + g * VN;
+            if (p.cVec && c + VN <= p.N) {
+                float old[VN];
+                LoadVec(cRow + c, old);
 #pragma unroll
-            for (int e = 0; e < VN; e++)
-                vv[e] = fmaf(p.beta, old[e], p.alpha * vv[e]);
-        }
-        else {
+                for (int e = 0; e < VN; e++)
+                    vv[e] = fmaf(p.beta, old[e], p.alpha * vv[e]);
+            }
+            else {
 #pragma unroll
-            for (int e = 0; e < VN; e++) {
-                float x = p.alpha * vv[e];
-                if (c + e < p.N)
-                    x = fmaf(p.beta, LoadOne(cRow + c + e), x);
-                vv[e] = x;
+                for (int e = 0; e < VN; e++) {
+                    float x = p.alpha * vv[e];
+                    if (c + e < p.N)
+                        x = fmaf(p.beta, LoadOne(cRow + c + e), x);
+                    vv[e] = x;
+                }
             }
         }
+    }
+    if (p.bias != nullptr) {
+        const OutT * bias = (const OutT *)p.bias;
+        const bool vec = (((uintptr_t)bias) & 15) == 0;
+#pragma unroll
+        for (int g = 0; g < 32 / VN; g++) {
+            const int c = c0 + g * VN;
+            float * vv = v + g * VN;
+            if (vec && c + VN <= p.N) {
+                float bv[VN];
+                LoadVec(bias + c, bv);
+#pragma unroll
+                for (int e = 0; e < VN; e++)
+                    vv[e] += bv[e];
+            }
+            else {
+#pragma unroll
+                for (int e = 0; e < VN; e++)
+                    if (c + e < p.N)
+                        vv[e] += LoadOne(bias + c + e);
+            }
+        }
+    }
+    if (p.act == NTB_ACT_RECTIFY) {
+#pragma unroll
+        for (int e = 0; e < 32; e++)
+            v[e] = fmaxf(v[e], 0.f);
     }
 }
 
@@ -1271,6 +1302,7 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
     tp.tilesN = (p.N + bn - 1) / bn;
     tp.totalTiles = (long long)tp.tilesM * tp.tilesN * p.count;
     tp.alpha = p.alpha; tp.beta = p.beta;
+    tp.bias = p.bias; tp.act = p.act;
     tp.status = ctx.status;
     tp.pfDist = Knob("NTB_PREFETCH_DIST", 0);
     tp.group = Knob("NTB_TILE_GROUP", 8);

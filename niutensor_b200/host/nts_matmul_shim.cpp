@@ -7,8 +7,9 @@
  *     source/tensor/core/arithmetic/MatrixMul2D.cpp, MatrixMul2D.cu
  *     source/tensor/core/arithmetic/MatrixMulBatched.cpp
  *     source/tensor/core/arithmetic/XTensorBLAS.cpp, XTensorBLAS.cu
+ *     source/tensor/core/arithmetic/MulAndShift.cpp
  * It defines every nts:: symbol those files define (declared in MatrixMul.h,
- * MatrixMul2D.h, MatrixMul2D.cuh, MatrixMulBatched.h, XTensorBLAS.h), with the same
+ * MatrixMul2D.h, MatrixMul2D.cuh, MatrixMulBatched.h, XTensorBLAS.h, MulAndShift.h), with the same
  * signatures and default arguments, so sample/fnnlm, sample/transformer, source/network
  * and the reference's own unit tests link and run unchanged. GPU tensors (devID >= 0) are
  * computed by the sm_100a kernels behind include/ntb_gemm.h; the cuBLAS handle arguments
@@ -37,6 +38,10 @@
 #include "tensor/core/arithmetic/MatrixMul2DParallel.h"
 #include "tensor/core/arithmetic/MatrixMulBatched.h"
 #include "tensor/core/arithmetic/XTensorBLAS.h"
+#include "tensor/core/arithmetic/MulAndShift.h"
+#include "tensor/core/arithmetic/Sum.h"
+#include "tensor/core/arithmetic/SumDim.h"
+#include "tensor/core/math/ScaleAndShift.h"
 #include "ntb_gemm.h"
 
 namespace nts {
@@ -509,6 +514,77 @@ XTensor MatrixMulBatched(const XTensor & a, MATRIX_TRANS_TYPE transposedA, const
 XTensor MatrixMulBatched(const XTensor & a, const XTensor & b, DTYPE alpha, XPRunner * parallelRunner)
 {
     return MatrixMulBatched(a, X_NOTRANS, b, X_NOTRANS, alpha, parallelRunner);
+}
+
+/* ------------------------------------------------------------------ MulAndShift
+   x * w + b (MulAndShift.cpp:38-110, 120-188). On the GPU, with the usual bias vector over
+   the last dimension, product and bias are one kernel (the reference writes the product to
+   a scratch tensor, then _SumDim reads and rewrites it). Every other case -- CPU tensors, a
+   scalar b, a bias along another dimension -- runs the product into c and lets the
+   reference's own _SumDim / ScaleAndShift add b in place. */
+
+namespace {
+
+XTensor MulAndShiftImpl(const XTensor & x, MATRIX_TRANS_TYPE tX, const XTensor & w, MATRIX_TRANS_TYPE tW,
+                        const XTensor & b, DTYPE alpha, XPRunner * runner)
+{
+    CheckNTErrors(x.dataType == w.dataType, "Input tensors should have the same data type!");
+    CheckNTErrors(x.order >= 2 && w.order >= 2, "Input tensors must have a order >= 2!");
+    int dims[2 * MAX_TENSOR_DIM_NUM];
+    const int order = GeneralShape(x, tX, w, tW, dims);
+    const float dr = (!x.isSparse || !w.isSparse) ? 1.0F : MAX(x.denseRatio, w.denseRatio);
+    XTensor c(order, dims, x.dataType, dr, x.devID, x.mem);
+    c.SetTMPFlag();
+
+    int n = -2;
+    if (b.order > 0) {
+        n = GetBroadcastDimIndex(c, b);
+        CheckNTErrors(n != -1, "TODO!");
+        CheckNTErrors(n >= 0 && n < c.order, "Something is wrong!");
+    }
+
+    const bool gpu = x.devID >= 0 && w.devID >= 0 && b.devID >= 0;
+    const bool fusable = gpu && b.order == 1 && n == c.order - 1 && b.dataType == c.dataType &&
+                         w.order == 2 && (x.order == 2 || tX == X_NOTRANS) && !x.isSparse && !w.isSparse;
+    if (fusable) {
+        CheckNTErrors(x.devID == w.devID && x.devID == b.devID, "The code must be run on the same GPU!");
+        const int xCols = x.dimSize[x.order - 1];
+        const int xRows = x.unitNum / xCols;            /* leading extents fold into rows */
+        const int cCols = c.dimSize[c.order - 1];
+        const int cRows = c.unitNum / cCols;
+        Fatal(ntb_gemm_bias_act(x.devID, NULL, x.data, (int)tX, w.data, (int)tW, b.data, c.data,
+                                (int)x.dataType, (int)c.dataType, xRows, xCols, w.dimSize[0], w.dimSize[1],
+                                cRows, cCols, xCols, w.dimSize[1], cCols, alpha, 0, NTB_ACT_NONE), "MulAndShift");
+    }
+    else {
+        _MatrixMul(&x, tX, &w, tW, &c, alpha, 0, runner);
+        if (b.order == 0)
+            _ScaleAndShiftMe(&c, 1.0F, b.Get0D());
+        else
+            _SumDim(&c, &b, n);
+    }
+
+    if (b.order > 0 && w.enableGrad && b.enableGrad) {
+        XLink::MakeLink(&x, &w, &b, &c, MATH_MULANDSHIFT);
+        XLink::AddParamToHeadInt(&c, n);
+        XLink::AddParamToHeadTrans(&c, tX);
+        XLink::AddParamToHeadTrans(&c, tW);
+        XLink::AddParamToHead(&c, alpha);
+    }
+    return c;
+}
+
+}
+
+XTensor MulAndShift(const XTensor & x, const XTensor & w, const XTensor & b, DTYPE alpha, XPRunner * parallelRunner)
+{
+    return MulAndShiftImpl(x, X_NOTRANS, w, X_NOTRANS, b, alpha, parallelRunner);
+}
+
+XTensor MulAndShift(const XTensor & x, MATRIX_TRANS_TYPE transposedX, const XTensor & w, MATRIX_TRANS_TYPE transposedW,
+                    const XTensor & b, DTYPE alpha, XPRunner * parallelRunner)
+{
+    return MulAndShiftImpl(x, transposedX, w, transposedW, b, alpha, parallelRunner);
 }
 
 }

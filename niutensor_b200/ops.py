@@ -8,6 +8,7 @@ Names, argument meaning and shape rules follow the reference:
   _MatrixMulBatched  source/tensor/core/arithmetic/MatrixMulBatched.cpp:49-138
   MatrixMul          source/tensor/core/arithmetic/MatrixMul.cpp:272-361
   MatrixMulBatched   source/tensor/core/arithmetic/MatrixMulBatched.cpp:291-390 (= BMMul)
+  MulAndShift        source/tensor/core/arithmetic/MulAndShift.cpp:38-110, 120-188
 Transposition flags are the reference's enum values: X_TRANS = 0, X_NOTRANS = 1.
 Where the reference prints an error and terminates, these raise NtError.
 """
@@ -148,3 +149,31 @@ def MatrixMulBatched(a, transposedA, b, transposedB, alpha=1.0):
 
 
 BMMul = MatrixMulBatched
+
+
+def MulAndShift(x, w, b, alpha=1.0, transposedX=X_NOTRANS, transposedW=X_NOTRANS, act=capi.ACT_NONE):
+    """alpha * op(x) * op(w) + b, b a vector added along the last dimension of the result
+    (the linear layer of the transformer). One kernel: the bias -- and with
+    act=capi.ACT_RECTIFY the feed-forward layer's Rectify -- is applied in the epilogue,
+    where the reference writes the product to a scratch tensor and runs _SumDim over it
+    (MulAndShift.cpp:66-88). Leading extents of an untransposed x fold into rows, as in
+    _MatrixMul; other higher-order combinations are not supported here."""
+    _check(x.dtype == w.dtype, "Input tensors should have the same data type!")
+    _check(x.dim() >= 2 and w.dim() >= 2, "Input tensors must have a order >= 2!")
+    _check(x.is_cuda and w.is_cuda and b.is_cuda, "this library has no CPU path: tensors must live on a CUDA device")
+    _check(w.dim() == 2 and (x.dim() == 2 or transposedX == X_NOTRANS),
+           "only a matrix w and an untransposed higher-order x are supported")
+    _check(x.is_contiguous() and w.is_contiguous() and b.is_contiguous(), "tensors must be dense and packed")
+    x2 = x.view(-1, x.shape[-1]) if x.dim() > 2 else x
+    xn, xm = (x2.shape[1], x2.shape[0]) if transposedX == X_TRANS else (x2.shape[0], x2.shape[1])
+    wn, wm = (w.shape[1], w.shape[0]) if transposedW == X_TRANS else (w.shape[0], w.shape[1])
+    _check(xm == wn, "Unmatched tensors in multiplication!")
+    _check(b.dim() == 1 and b.shape[0] == wm and b.dtype == x.dtype, "the bias must be a vector over the last dimension")
+    out_shape = tuple(x.shape[:-2]) + ((x.shape[-1] if transposedX == X_TRANS else x.shape[-2]), wm)
+    c = torch.empty(out_shape, dtype=x.dtype, device=x.device)
+    rc = capi.lib().ntb_gemm_bias_act(x.device.index, _stream(x), x2.data_ptr(), transposedX, w.data_ptr(), transposedW,
+                                      b.data_ptr(), c.data_ptr(), _dtype_code(x), _dtype_code(c),
+                                      x2.shape[0], x2.shape[1], w.shape[0], w.shape[1], xn, wm,
+                                      x2.shape[1], w.shape[1], wm, alpha, 0.0, act)
+    _raise_rc(rc, "MulAndShift")
+    return c

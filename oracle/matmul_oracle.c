@@ -193,3 +193,29 @@ void orc_matmul_broadcast_f32(const float * a, int transA, const float * b, int 
                              c + ((size_t)p * bBlockNum + q) * nc * mc,
                              na, ma, nb, mb, nc, mc, alpha, beta);
 }
+
+/*
+ * MulAndShift (source/tensor/core/arithmetic/MulAndShift.cpp:38-110, 120-188): the product
+ * alpha * op(x) * op(w) is written to a scratch tensor with beta = 0 (:69), then the bias
+ * vector b is added along the last dimension by _SumDim with beta = 1 (:88;
+ * source/tensor/core/arithmetic/SumDim.cpp: c = a + b * beta, one fp32 multiply-add per
+ * element, b indexed by the column). x holds `blocks` stacked matrices that the flatten
+ * rule of _MatrixMul folds into rows when x is not transposed; callers pass the folded
+ * row count. rectify != 0 applies the reference's Rectify afterwards (max(x, 0),
+ * source/tensor/function/Rectify.cpp), the next operator of the feed-forward layer.
+ */
+void orc_mulandshift_f32(const float * x, int transX, const float * w, int transW, const float * b,
+                         float * c, int nx, int mx, int nw, int mw, int nc, int mc,
+                         float alpha, int rectify)
+{
+    int i, j;
+    orc_matmul2d_f32(x, transX, w, transW, c, nx, mx, nw, mw, nc, mc, alpha, 0.0f);
+    for (i = 0; i < nc; i++) {
+        for (j = 0; j < mc; j++) {
+            float v = c[(size_t)i * mc + j] + b[j] * 1.0f;
+            if (rectify && v < 0)
+                v = 0;
+            c[(size_t)i * mc + j] = v;
+        }
+    }
+}

@@ -65,6 +65,8 @@ class Oracle:
         self.lib.orc_matmul_broadcast_f32.argtypes = [_F32P, ctypes.c_int, _F32P, ctypes.c_int, _F32P] + \
             [ctypes.c_int] * 8 + [ctypes.c_float] * 2
         self.lib.orc_set_threads.argtypes = [ctypes.c_int]
+        self.lib.orc_mulandshift_f32.argtypes = [_F32P, ctypes.c_int, _F32P, ctypes.c_int, _F32P, _F32P] + \
+            [ctypes.c_int] * 6 + [ctypes.c_float, ctypes.c_int]
 
     def set_threads(self, n):
         self.lib.orc_set_threads(int(n))
@@ -76,6 +78,23 @@ class Oracle:
         self.lib.orc_matmul2d_f32(_fp(a), tA, _fp(b), tB, _fp(c), a.shape[0], a.shape[1],
                                   b.shape[0], b.shape[1], M, N, alpha, beta)
         return c
+
+    def mulandshift(self, x, w, b, alpha=1.0, tX=X_NOTRANS, tW=X_NOTRANS, rectify=False):
+        """MulAndShift: alpha * op(x) * op(w) + b along the last dimension; leading extents
+        of an untransposed x fold into rows."""
+        x, w, b = _as_f32(x), _as_f32(w), _as_f32(b)
+        lead = x.shape[:-2]
+        if tX == X_NOTRANS and x.ndim > 2:
+            x2 = x.reshape(-1, x.shape[-1])
+        else:
+            if x.ndim != 2:
+                raise ValueError("a transposed x must be a matrix here")
+            x2 = x
+        M, N, _ = mm_dims(x2.shape, tX, w.shape, tW)
+        c = np.zeros((M, N), np.float32)
+        self.lib.orc_mulandshift_f32(_fp(x2), tX, _fp(w), tW, _fp(b), _fp(c), x2.shape[0], x2.shape[1],
+                                     w.shape[0], w.shape[1], M, N, alpha, 1 if rectify else 0)
+        return c.reshape(lead + (M // max(1, int(np.prod(lead, dtype=np.int64))), N)) if lead else c
 
     def matmul_batched(self, a, tA, b, tB, alpha=1.0, beta=0.0, c=None):
         """_MatrixMulBatched: equal leading extents, block i of a meets block i of b."""
@@ -149,6 +168,9 @@ class Reference:
             _F32P, ctypes.c_int, _I32P,
             ctypes.c_float, ctypes.c_float]
         self.lib.ref_set_blas_threads.argtypes = [ctypes.c_int]
+        self.lib.ref_mulandshift_f32.argtypes = [
+            _F32P, ctypes.c_int, _I32P, ctypes.c_int, _F32P, ctypes.c_int, _I32P, ctypes.c_int,
+            _F32P, ctypes.c_int, _F32P, ctypes.c_float]
 
     def set_threads(self, n):
         self.lib.ref_set_blas_threads(int(n))
@@ -173,6 +195,21 @@ class Reference:
                                 _fp(b), b.ndim, bd.ctypes.data_as(_I32P), tB,
                                 _fp(c), c.ndim, cd.ctypes.data_as(_I32P), alpha, beta)
         return c
+
+
+def ref_mulandshift(ref, x, w, b, alpha=1.0, tX=X_NOTRANS, tW=X_NOTRANS):
+    """The reference's own user-level MulAndShift on CPU tensors."""
+    x, w, b = _as_f32(x), _as_f32(w), _as_f32(b)
+    M, N, _ = mm_dims(x.shape, tX, w.shape, tW)
+    c = np.zeros(x.shape[:-2] + (M, N), np.float32)
+    xd = np.asarray(x.shape, np.int32)
+    wd = np.asarray(w.shape, np.int32)
+    rc = ref.lib.ref_mulandshift_f32(_fp(x), x.ndim, xd.ctypes.data_as(_I32P), tX,
+                                     _fp(w), w.ndim, wd.ctypes.data_as(_I32P), tW,
+                                     _fp(b), b.shape[0], _fp(c), alpha)
+    if rc != 0:
+        raise RuntimeError("ref_mulandshift_f32 failed: %d" % rc)
+    return c
 
 
 def round_to_half(x):

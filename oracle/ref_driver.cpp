@@ -16,6 +16,7 @@
 #include "tensor/core/arithmetic/MatrixMul.h"
 #include "tensor/core/arithmetic/MatrixMul2D.h"
 #include "tensor/core/arithmetic/MatrixMulBatched.h"
+#include "tensor/core/arithmetic/MulAndShift.h"
 #ifdef USE_BLAS
 #include "tensor/XBLAS.h"
 #endif
@@ -66,6 +67,32 @@ int ref_matmul_f32(int form,
     Drop(tb);
     Drop(tc);
     return 0;
+}
+
+/* the reference's user-level MulAndShift (source/tensor/core/arithmetic/MulAndShift.cpp:38,
+   120) on CPU tensors: y = alpha * op(x) * op(w) + bias along the last dimension */
+int ref_mulandshift_f32(const float * x, int xOrder, const int * xDims, int transX,
+                        const float * w, int wOrder, const int * wDims, int transW,
+                        const float * bias, int biasLen, float * y, float alpha)
+{
+    XTensor * tx = View((float*)x, xOrder, xDims);
+    XTensor * tw = View((float*)w, wOrder, wDims);
+    int bd[1] = { biasLen };
+    XTensor * tb = View((float*)bias, 1, bd);
+    int rc = 0;
+    {
+        XTensor out = (transX == 1 && transW == 1)
+            ? MulAndShift(*tx, *tw, *tb, alpha)
+            : MulAndShift(*tx, transX == 0 ? X_TRANS : X_NOTRANS, *tw, transW == 0 ? X_TRANS : X_NOTRANS, *tb, alpha);
+        if (out.data == NULL)
+            rc = 1;
+        else
+            memcpy(y, out.data, sizeof(float) * (size_t)out.unitNum);
+    }
+    Drop(tx);
+    Drop(tw);
+    Drop(tb);
+    return rc;
 }
 
 /* 1 when this build routes dense fp32 GEMMs to cblas_sgemm (XTensorBLAS.cpp:39) */

@@ -49,3 +49,21 @@ def seeded_cases():
     return out
 
 
+
+
+def mulandshift_cases():
+    """(x, w, b, alpha, transposedX, transposedW) for MulAndShift: matrices and a
+    higher-order x folded into rows; the transposed forms take matrices only."""
+    rng = np.random.default_rng(20241)
+    out = []
+    for (lead, M, K, N, alpha, tX, tW) in [((), 7, 5, 3, 1.0, X_NOTRANS, X_NOTRANS),
+                                           ((2, 3), 16, 24, 40, 1.0, X_NOTRANS, X_NOTRANS),
+                                           ((4,), 33, 65, 17, 0.5, X_NOTRANS, X_NOTRANS),
+                                           ((), 20, 36, 16, 1.0, X_TRANS, X_NOTRANS),
+                                           ((), 67, 35, 66, -0.75, X_NOTRANS, X_TRANS),
+                                           ((), 9, 1, 9, 1.0, X_TRANS, X_TRANS)]:
+        x = stored(rng, lead, M, K, tX)
+        w = stored(rng, (), K, N, tW)
+        b = rng.normal(size=(N,)).astype(np.float32)
+        out.append((x, w, b, alpha, tX, tW))
+    return out

@@ -14,6 +14,9 @@ without either.
                    combinations x alpha/beta pairs x 2-D / batched / broadcast /
                    flatten forms, ragged sizes included. Only the outputs are stored.
 
+  ref_mulandshift.npz  outputs of the reference's user-level MulAndShift (CPU) on the
+                   seeded inputs of tests/golden/cases.py::mulandshift_cases.
+
 Usage: python tests/golden/make_golden.py
 """
 import json
@@ -28,8 +31,8 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 REF = os.environ.get("REF", "/root/reference")
 
-from oracle.oracle import Reference, X_TRANS, X_NOTRANS  # noqa: E402
-from tests.golden.cases import seeded_cases  # noqa: E402
+from oracle.oracle import Reference, ref_mulandshift, X_TRANS, X_NOTRANS  # noqa: E402
+from tests.golden.cases import seeded_cases, mulandshift_cases  # noqa: E402
 
 TEST_FILES = ["TMatrixMul.cpp", "TMatrixMul2D.cpp", "TMatrixMul2DParallel.cpp",
               "TMatrixMulBatched.cpp"]
@@ -84,6 +87,12 @@ def main():
     arrays["meta"] = np.frombuffer(json.dumps(meta).encode(), dtype=np.uint8)
     np.savez_compressed(os.path.join(HERE, "ref_seeded.npz"), **arrays)
     print("ref_seeded.npz: %d cases" % len(meta))
+
+    arrays = {}
+    for i, (x, w, b, alpha, tX, tW) in enumerate(mulandshift_cases()):
+        arrays["y%d" % i] = ref_mulandshift(ref, x, w, b, alpha, tX, tW)
+    np.savez_compressed(os.path.join(HERE, "ref_mulandshift.npz"), **arrays)
+    print("ref_mulandshift.npz: %d cases" % len(arrays))
 
 
 if __name__ == "__main__":

@@ -15,7 +15,7 @@ import torch
 from niutensor_b200 import capi, ops
 from niutensor_b200.capi import X_TRANS, X_NOTRANS
 from oracle.oracle import rel_fro, round_to_half
-from tests.golden.cases import seeded_cases, FORM_GENERAL, FORM_BATCHED, FORM_2D
+from tests.golden.cases import seeded_cases, mulandshift_cases, FORM_GENERAL, FORM_BATCHED, FORM_2D
 from tests.test_oracle import is_float_equal, kat_cases, run_form
 
 pytestmark = pytest.mark.gpu
@@ -350,6 +350,72 @@ def test_errors_mirror_the_reference():
     # MatrixMul re-makes a c of the wrong shape (CheckMMulShape)
     out = ops.MatrixMul(a, X_NOTRANS, torch.zeros(5, 3, device=DEV), X_NOTRANS, c=c)
     assert tuple(out.shape) == (4, 3)
+
+
+# --------------------------------------------------------------- fused bias / activation
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_mulandshift_against_stored_reference_outputs(dtype, oracle):
+    z = np.load(os.path.join(GOLD, "ref_mulandshift.npz"))
+    for i, (x, w, b, alpha, tX, tW) in enumerate(mulandshift_cases()):
+        if dtype == torch.float16:
+            x, w, b = round_to_half(x), round_to_half(w), round_to_half(b)
+            want = oracle.mulandshift(x, w, b, alpha, tX, tW)
+        else:
+            want = z["y%d" % i]
+        y = ops.MulAndShift(to_dev(x, dtype), to_dev(w, dtype), to_dev(b, dtype), alpha, tX, tW)
+        assert tuple(y.shape) == want.shape
+        assert rel_fro(y.float().cpu().numpy(), want) <= TOL[dtype], i
+    status_ok()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_feed_forward_layer_shapes_with_bias_and_rectify(dtype, oracle):
+    """x[rows, 512] * w1[512, 2048] + b1 with the rectifier fused, then * w2 + b2."""
+    rng = np.random.default_rng(400)
+    rows, d, f = 384, 512, 2048
+    x = rng.normal(size=(3, rows // 3, d)).astype(np.float32)
+    w1 = (rng.normal(size=(d, f)) / np.sqrt(d)).astype(np.float32)
+    b1 = rng.normal(size=(f,)).astype(np.float32)
+    w2 = (rng.normal(size=(f, d)) / np.sqrt(f)).astype(np.float32)
+    b2 = rng.normal(size=(d,)).astype(np.float32)
+    if dtype == torch.float16:
+        x, w1, b1, w2, b2 = [round_to_half(t) for t in (x, w1, b1, w2, b2)]
+    h = ops.MulAndShift(to_dev(x, dtype), to_dev(w1, dtype), to_dev(b1, dtype), act=capi.ACT_RECTIFY)
+    assert capi.lib().ntb_last_route() != capi.ROUTE_SIMT
+    want_h = oracle.mulandshift(x, w1, b1, rectify=True)
+    assert float(h.min()) >= 0.0
+    assert rel_fro(h.float().cpu().numpy(), want_h) <= TOL[dtype]
+    hh = h.float().cpu().numpy()
+    y = ops.MulAndShift(h, to_dev(w2, dtype), to_dev(b2, dtype))
+    assert rel_fro(y.float().cpu().numpy(), oracle.mulandshift(hh, w2, b2)) <= TOL[dtype]
+    status_ok()
+
+
+def test_bias_with_beta_through_the_c_abi_on_both_routes(oracle):
+    rng = np.random.default_rng(401)
+    L = capi.lib()
+    M, N, K = 136, 200, 72
+    a = stored(rng, (), M, K, X_NOTRANS)
+    b = stored(rng, (), K, N, X_NOTRANS)
+    bias = rng.normal(size=(N,)).astype(np.float32)
+    c0 = rng.normal(size=(M, N)).astype(np.float32)
+    want = np.maximum(oracle.matmul2d(a, X_NOTRANS, b, X_NOTRANS, 0.5, 0.25, c0) + bias[None, :], 0)
+    for route in (0, capi.ROUTE_SIMT):
+        L.ntb_set_route(route)
+        try:
+            c = to_dev(c0, torch.float32)
+            ta, tb, tbias = to_dev(a, torch.float32), to_dev(b, torch.float32), to_dev(bias, torch.float32)
+            rc = L.ntb_gemm_bias_act(0, None, ta.data_ptr(), X_NOTRANS, tb.data_ptr(), X_NOTRANS, tbias.data_ptr(),
+                                     c.data_ptr(), capi.X_FLOAT, capi.X_FLOAT, M, K, K, N, M, N, K, N, N,
+                                     0.5, 0.25, capi.ACT_RECTIFY)
+            assert rc == capi.OK
+            assert rel_fro(c.cpu().numpy(), want) <= 1e-5
+        finally:
+            L.ntb_set_route(0)
+    assert L.ntb_gemm_bias_act(0, None, 1, X_NOTRANS, 1, X_NOTRANS, None, 1, capi.X_FLOAT, capi.X_FLOAT,
+                               8, 8, 8, 8, 8, 8, 8, 8, 8, 1.0, 0.0, 7) == capi.ERR_ARG
+    status_ok()
 
 
 # --------------------------------------------------------------- list planner, host entry

@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 
 from oracle.oracle import (Oracle, Reference, ref_available, rel_fro, X_TRANS, X_NOTRANS)
-from tests.golden.cases import seeded_cases, FORM_GENERAL, FORM_BATCHED, FORM_2D
+from tests.golden.cases import seeded_cases, mulandshift_cases, FORM_GENERAL, FORM_BATCHED, FORM_2D
 
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
@@ -60,6 +60,19 @@ def test_oracle_matches_stored_reference_outputs_bit_for_bit(oracle):
         want = z["c%d" % i]
         assert got.shape == want.shape
         assert np.array_equal(got, want), "case %d %s" % (i, m)
+
+
+def test_mulandshift_oracle_matches_stored_reference_outputs_bit_for_bit(oracle):
+    z = np.load(os.path.join(GOLD, "ref_mulandshift.npz"))
+    cases = mulandshift_cases()
+    assert len(cases) == len(z.files) == 6
+    for i, (x, w, b, alpha, tX, tW) in enumerate(cases):
+        got = oracle.mulandshift(x, w, b, alpha, tX, tW)
+        assert got.shape == z["y%d" % i].shape
+        assert np.array_equal(got, z["y%d" % i]), i
+    x, w, b = cases[1][:3]
+    r = oracle.mulandshift(x, w, b, rectify=True)
+    assert np.array_equal(r, np.maximum(oracle.mulandshift(x, w, b), 0))
 
 
 def test_thread_count_does_not_change_bits():
