@@ -155,7 +155,10 @@ int ntb_gemm_list(int devID, void * stream,
  * the strided-batched GEMM, copies c back and synchronises the stream. This is what a
  * caller holding CPU tensors does through the reference with SetDevice/FlushToDevice
  * (source/tensor/XTensor.cpp:533-539, 1992-1999) around MatrixMul. Staging buffers grow
- * on demand and are kept until ntb_release().
+ * on demand and are kept until ntb_release(). A single large 2-D product is cut into
+ * column chunks whose copy-in, product and copy-out overlap on internal streams (this
+ * needs pinned host memory to take effect). Calls on one device share the staging buffers:
+ * do not overlap them.
  */
 int ntb_gemm_host(int devID, void * stream,
                   const void * a, int transA, const void * b, int transB, void * c,

@@ -128,6 +128,24 @@ int Dispatch(int devID, cudaStream_t stream, Problem & p)
     return rc;
 }
 
+/* streams and events of the pipelined host-buffer path, created once per device */
+bool EnsurePipe(DeviceCtx * ctx)
+{
+    std::lock_guard<std::mutex> g(gLock);
+    if (ctx->pipeReady)
+        return true;
+    bool ok = cudaStreamCreateWithFlags(&ctx->copyIn, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaStreamCreateWithFlags(&ctx->copyOut, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaEventCreateWithFlags(&ctx->evStart, cudaEventDisableTiming) == cudaSuccess;
+    for (int i = 0; ok && i < 16; i++)
+        ok = cudaEventCreateWithFlags(&ctx->evIn[i], cudaEventDisableTiming) == cudaSuccess &&
+             cudaEventCreateWithFlags(&ctx->evOut[i], cudaEventDisableTiming) == cudaSuccess;
+    if (!ok)
+        cudaGetLastError();
+    ctx->pipeReady = ok;
+    return ok;
+}
+
 int GrowStage(DeviceCtx * ctx, int slot, size_t bytes)
 {
     if (ctx->stageBytes[slot] >= bytes)
@@ -376,6 +394,66 @@ int ntb_gemm_host(int devID, void * stream,
             GrowStage(ctx, 2, cBytes) != NTB_OK)
             return NTB_ERR_CUDA;
     }
+    /* One large 2-D product: cut C (and the matching part of B) into column chunks and
+       overlap the copy-in of chunk j+1 and the copy-out of chunk j-1 with the product of
+       chunk j. PCIe is full duplex, so the result rides back while operands still arrive. */
+    const long long N = transB == NTB_X_TRANS ? nb : mb;
+    if (count == 1 && N >= 2048 && aBytes + bBytes + cBytes >= ((size_t)64 << 20) && EnsurePipe(ctx)) {
+        const int chunks = 8;
+        const long long step = ((N + chunks - 1) / chunks + 63) / 64 * 64;      /* columns per chunk */
+        rc = NTB_ERR_CUDA;
+        do {
+            if (cudaEventRecord(ctx->evStart, st) != cudaSuccess ||
+                cudaStreamWaitEvent(ctx->copyIn, ctx->evStart, 0) != cudaSuccess ||
+                cudaStreamWaitEvent(ctx->copyOut, ctx->evStart, 0) != cudaSuccess)
+                break;
+            if (cudaMemcpyAsync(ctx->stage[0], a, aBytes, cudaMemcpyHostToDevice, ctx->copyIn) != cudaSuccess)
+                break;
+            bool fail = false;
+            int used = 0;
+            for (long long n0 = 0; n0 < N && !fail; n0 += step, used++) {
+                const long long w = N - n0 < step ? N - n0 : step;
+                /* B: columns [n0, n0+w) of a stored k x N matrix, or rows of a stored N x k one */
+                if (transB == NTB_X_TRANS)
+                    fail |= cudaMemcpyAsync((char *)ctx->stage[1] + (size_t)n0 * mb * esAB, (const char *)b + (size_t)n0 * mb * esAB,
+                                            (size_t)w * mb * esAB, cudaMemcpyHostToDevice, ctx->copyIn) != cudaSuccess;
+                else
+                    fail |= cudaMemcpy2DAsync((char *)ctx->stage[1] + n0 * esAB, (size_t)mb * esAB, (const char *)b + n0 * esAB,
+                                              (size_t)mb * esAB, (size_t)w * esAB, nb, cudaMemcpyHostToDevice, ctx->copyIn) != cudaSuccess;
+                if (beta != 0.f)
+                    fail |= cudaMemcpy2DAsync((char *)ctx->stage[2] + n0 * esC, (size_t)mc * esC, (const char *)c + n0 * esC,
+                                              (size_t)mc * esC, (size_t)w * esC, nc, cudaMemcpyHostToDevice, ctx->copyIn) != cudaSuccess;
+                fail |= cudaEventRecord(ctx->evIn[used], ctx->copyIn) != cudaSuccess;
+                fail |= cudaStreamWaitEvent(st, ctx->evIn[used], 0) != cudaSuccess;
+                if (fail)
+                    break;
+                int r2;
+                if (transB == NTB_X_TRANS)
+                    r2 = ntb_gemm(devID, stream, ctx->stage[0], transA, (char *)ctx->stage[1] + (size_t)n0 * mb * esAB, transB,
+                                  (char *)ctx->stage[2] + n0 * esC, dtypeAB, dtypeC, na, ma, (int)w, mb, nc, (int)w,
+                                  ma, mb, mc, alpha, beta);
+                else
+                    r2 = ntb_gemm(devID, stream, ctx->stage[0], transA, (char *)ctx->stage[1] + n0 * esAB, transB,
+                                  (char *)ctx->stage[2] + n0 * esC, dtypeAB, dtypeC, na, ma, nb, (int)w, nc, (int)w,
+                                  ma, mb, mc, alpha, beta);
+                if (r2 != NTB_OK) { rc = r2; fail = true; break; }
+                fail |= cudaEventRecord(ctx->evOut[used], st) != cudaSuccess;
+                fail |= cudaStreamWaitEvent(ctx->copyOut, ctx->evOut[used], 0) != cudaSuccess;
+                fail |= cudaMemcpy2DAsync((char *)c + n0 * esC, (size_t)mc * esC, (char *)ctx->stage[2] + n0 * esC,
+                                          (size_t)mc * esC, (size_t)w * esC, nc, cudaMemcpyDeviceToHost, ctx->copyOut) != cudaSuccess;
+            }
+            /* even after a failure, let everything issued so far drain before returning */
+            const bool s1 = cudaStreamSynchronize(ctx->copyIn) == cudaSuccess;
+            const bool s2 = cudaStreamSynchronize(st) == cudaSuccess;
+            const bool s3 = cudaStreamSynchronize(ctx->copyOut) == cudaSuccess;
+            if (!fail && s1 && s2 && s3)
+                rc = NTB_OK;
+        } while (0);
+        if (rc == NTB_ERR_CUDA)
+            cudaGetLastError();
+        return rc;
+    }
+
     if (cudaMemcpyAsync(ctx->stage[0], a, aBytes, cudaMemcpyHostToDevice, st) != cudaSuccess ||
         cudaMemcpyAsync(ctx->stage[1], b, bBytes, cudaMemcpyHostToDevice, st) != cudaSuccess)
         return NTB_ERR_CUDA;
@@ -447,6 +525,15 @@ void ntb_release(void)
             for (int s = 0; s < 3; s++)
                 if (c->stage[s])
                     cudaFree(c->stage[s]);
+            if (c->pipeReady) {
+                cudaStreamDestroy(c->copyIn);
+                cudaStreamDestroy(c->copyOut);
+                cudaEventDestroy(c->evStart);
+                for (int i = 0; i < 16; i++) {
+                    cudaEventDestroy(c->evIn[i]);
+                    cudaEventDestroy(c->evOut[i]);
+                }
+            }
             cudaFree(c->status);
         }
         if (prev >= 0)

@@ -37,6 +37,10 @@ struct DeviceCtx {
     int * status;           /* device word written by a kernel that gave up a wait */
     void * stage[3];        /* host-buffer entry point: device staging for a, b, c */
     size_t stageBytes[3];
+    /* host-buffer entry point, pipelined form: copy-in and copy-out streams, one event pair per chunk */
+    cudaStream_t copyIn, copyOut;
+    cudaEvent_t evIn[16], evOut[16], evStart;
+    bool pipeReady;
 };
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,

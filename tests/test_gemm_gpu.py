@@ -352,6 +352,30 @@ def test_errors_mirror_the_reference():
     assert tuple(out.shape) == (4, 3)
 
 
+def test_host_buffer_entry_pipelined_large_product(oracle):
+    """Large single products take the chunked, overlapped path; both layouts of B."""
+    L = capi.lib()
+    rng = np.random.default_rng(16)
+    M, N, K = 1024, 4160, 4096          # N not a multiple of the chunk width
+    a = rng.uniform(-1, 1, (M, K)).astype(np.float16)
+    for tB in (X_NOTRANS, X_TRANS):
+        b = rng.uniform(-1, 1, (K, N) if tB == X_NOTRANS else (N, K)).astype(np.float16)
+        c0 = rng.normal(size=(M, N)).astype(np.float16)
+        c = c0.copy()
+        rc = L.ntb_gemm_host(0, None, a.ctypes.data, X_NOTRANS, b.ctypes.data, tB, c.ctypes.data,
+                             capi.X_FLOAT16, capi.X_FLOAT16, M, K, b.shape[0], b.shape[1], M, N, 0, 0, 0, 1, 1.0, 0.5)
+        assert rc == capi.OK
+        rows = np.arange(0, M, 37)
+        want = oracle.matmul2d(a[rows].astype(np.float32), X_NOTRANS, b.astype(np.float32), tB, 1.0, 0.5,
+                               c0[rows].astype(np.float32))
+        assert rel_fro(c[rows].astype(np.float32), want) <= 2e-3
+        # whole-matrix check against the resident-operand entry point
+        ta, tb, tc = to_dev(a, torch.float16), to_dev(b, torch.float16), to_dev(c0, torch.float16)
+        ops._MatrixMul2D(ta, X_NOTRANS, tb, tB, tc, 1.0, 0.5)
+        assert np.array_equal(tc.cpu().numpy(), c)
+    status_ok()
+
+
 # --------------------------------------------------------------- fused bias / activation
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
