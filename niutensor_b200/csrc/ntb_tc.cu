@@ -45,6 +45,23 @@ constexpr int CONV_THREADS = NTB_CONV_THREADS;
 constexpr int FP32_CHUNK_BLOCKS = 8;  /* fp32 route: 8 k-blocks = 256 of K per TMEM accumulation chain */
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;   /* about two seconds */
 
+/* Division of a 31-bit unsigned number by a run-time constant as multiply-high, add and
+   shift: the tile walk and the batch indices need several divisions per tile, and a
+   hardware-emulated integer division costs about two hundred clocks of latency each. */
+struct FastDiv {
+    uint32_t d, m, s;
+    __host__ void Set(uint32_t div)
+    {
+        d = div ? div : 1;
+        s = 0;
+        while ((1ull << s) < d)
+            s++;
+        m = (uint32_t)((((1ull << 32) * ((1ull << s) - d)) / d) + 1);
+    }
+    __device__ __forceinline__ uint32_t Div(uint32_t n) const { return (__umulhi(n, m) + n) >> s; }
+    __device__ __forceinline__ void DivMod(uint32_t n, uint32_t & q, uint32_t & r) const { q = Div(n); r = n - q * d; }
+};
+
 struct TcParams {
     void * c;
     long long ldc, sCp, sCq;
@@ -52,12 +69,14 @@ struct TcParams {
     int aSel, bSel;         /* which index walks the operand's batch dimension: 0 none, 1 p, 2 q, 3 i */
     int aMN, bMN;
     int tilesM, tilesN;
-    long long totalTiles;
+    int totalTiles;
     int cVec;               /* C rows can be accessed with 16-byte vectors */
     int cTma;               /* C is written with TMA stores from swizzled staging boxes */
     int cSel;               /* index that walks C's batch dimension in its tensor map (as aSel) */
     int pfDist;             /* producer asks L2 for the boxes of k-block kb + pfDist while loading kb; 0 = off */
     int group;              /* m-blocks per band of the tile walk */
+    FastDiv fdPerProb, fdBand, fdGroup, fdLast, fdQ;   /* tiles per problem, tiles per band, rows of a full / of the last band, Q */
+    int epiHint;            /* suspend-time hint (ns) of the epilogue warps' barrier probes */
     float alpha, beta;
     const void * bias;      /* N values of C's type added to every output row, or NULL */
     int act;                /* 1: max(x, 0) applied last */
@@ -70,8 +89,14 @@ struct TcParams {
    4 kernel cycles of CTA 0's producer lane, 5 CTAs counted */
 #ifdef NTB_WAIT_STATS
 __device__ unsigned long long gWaitStats[8];
+/* timeline of CTA 0 of the single-CTA kernel, in SM clocks since kernel entry:
+   0 set-up done, 1 first TMA issued, 2 first stage landed, 3 first tile's MMAs committed,
+   4 epilogue saw the accumulator, 5 epilogue stores issued, 6 stores complete, 7 kernel end */
+__device__ unsigned long long gTimeline[16];
+#define NTB_MARK(slot) do { if (blockIdx.x == 0 && tlShared[slot] == 0) tlShared[slot] = (unsigned long long)(clock64() - kernelT0) + 1; } while (0)
 #define NTB_TIMED(slot, expr) do { long long t0_ = clock64(); expr; wstat[slot] += clock64() - t0_; } while (0)
 #else
+#define NTB_MARK(slot) do { } while (0)
 #define NTB_TIMED(slot, expr) do { expr; } while (0)
 #endif
 
@@ -159,6 +184,13 @@ __device__ __forceinline__ void TmaPrefetch3D(const CUtensorMap * map, int c0, i
                  :: "l"(map), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 
+/* starts the fetch of a tensor map into the descriptor cache, so that the first copy that
+   uses it does not wait for it */
+__device__ __forceinline__ void PrefetchTensorMap(const CUtensorMap * map)
+{
+    asm volatile("prefetch.tensormap [%0];" :: "l"(map) : "memory");
+}
+
 __device__ __forceinline__ void TcFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void TcFenceAfter()  { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -197,6 +229,30 @@ __device__ __forceinline__ void TmemLoad32(uint32_t taddr, float * v)
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
     for (int i = 0; i < 32; i++)
+        v[i] = __uint_as_float(r[i]);
+}
+
+/* 64 consecutive fp32 columns of this thread's TMEM lane in one instruction */
+__device__ __forceinline__ void TmemLoad64(uint32_t taddr, float * v)
+{
+    uint32_t r[64];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+                 "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+                 "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];\n\t"
+                 "tcgen05.wait::ld.sync.aligned;"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]),
+                   "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]),
+                   "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]),
+                   "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]),
+                   "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+                 : "r"(taddr) : "memory");
+#pragma unroll
+    for (int i = 0; i < 64; i++)
         v[i] = __uint_as_float(r[i]);
 }
 
@@ -449,11 +505,12 @@ struct TileWriter {
         }
     }
 
-    /* all of this warp's stores have completed */
+    /* all of this warp's stores have read their staging boxes, so shared memory may go
+       away; the writes themselves complete before the grid does */
     __device__ __forceinline__ void Finish(int lane)
     {
         if (lane == 0)
-            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         __syncwarp();
     }
 };
@@ -467,24 +524,41 @@ struct TileCoord {
 /* Tiles of one problem are visited in bands of `GROUP` m-blocks, n fastest inside a band's
    column, so the CTAs running at the same time share A row panels and B column panels
    in L2. */
-__device__ __forceinline__ TileCoord DecodeTile(long long t, int tilesM, int tilesN, int GROUP)
+__device__ __forceinline__ TileCoord DecodeTile(int t, const TcParams & p)
 {
-    const int perProb = tilesM * tilesN;
     TileCoord tc;
-    tc.prob = (int)(t / perProb);
-    int r = (int)(t % perProb);
-    int band = r / (GROUP * tilesN);
-    int first = band * GROUP;
-    int rows = min(tilesM - first, GROUP);
-    int inBand = r % (GROUP * tilesN);
-    tc.mBlk = first + inBand % rows;
-    tc.nBlk = inBand / rows;
+    uint32_t prob, r, band, inBand, q, rem;
+    p.fdPerProb.DivMod((uint32_t)t, prob, r);
+    p.fdBand.DivMod(r, band, inBand);
+    const int first = (int)band * p.group;
+    if (p.tilesM - first >= p.group)
+        p.fdGroup.DivMod(inBand, q, rem);
+    else
+        p.fdLast.DivMod(inBand, q, rem);
+    tc.prob = (int)prob;
+    tc.mBlk = first + (int)rem;
+    tc.nBlk = (int)q;
     return tc;
 }
 
-__device__ __forceinline__ int BatchCoord(int sel, int prob, int Q)
+/* (p, q) = (prob / Q, prob % Q) */
+__device__ __forceinline__ void SplitProb(const TcParams & p, int prob, int & pp, int & qq)
 {
-    return sel == 1 ? prob / Q : sel == 2 ? prob % Q : sel == 3 ? prob : 0;
+    uint32_t a, b;
+    p.fdQ.DivMod((uint32_t)prob, a, b);
+    pp = (int)a;
+    qq = (int)b;
+}
+
+__device__ __forceinline__ int BatchCoord(int sel, int prob, const TcParams & p)
+{
+    if (sel == 0)
+        return 0;
+    if (sel == 3)
+        return prob;
+    int pp, qq;
+    SplitProb(p, prob, pp, qq);
+    return sel == 1 ? pp : qq;
 }
 
 /* ---------------------------------------------------------------- the kernel */
@@ -505,6 +579,12 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     constexpr int KSTEPS = ROW_BYTES / UMMA_K_BYTES;                 /* 4 */
     static_assert(BN == 64 || BN == 128 || BN == 256, "tile width");
 
+#ifdef NTB_WAIT_STATS
+    const long long kernelT0 = clock64();
+    __shared__ unsigned long long tlShared[16];
+    if (threadIdx.x < 16) tlShared[threadIdx.x] = 0;
+    __syncthreads();
+#endif
     extern __shared__ uint8_t smemRaw[];
     __shared__ __align__(8) uint64_t barFull[STAGES];
     __shared__ __align__(8) uint64_t barEmpty[STAGES];
@@ -519,7 +599,18 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     const uint32_t smemBase = (SmemAddr(smemRaw) + 1023u) & ~1023u;
     volatile int * abortPtr = &abortFlag;
 
+    if (threadIdx.x == 64) {
+        /* an idle epilogue lane pulls the kernel parameters and the tensor maps towards the SM
+           while the other warps set up, so the producer's first use of them does not stall */
+        PrefetchTensorMap(&tmA);
+        PrefetchTensorMap(&tmB);
+        if (p.cTma)
+            PrefetchTensorMap(&tmC);
+        int touch = p.totalTiles + p.tilesM + p.tilesN + p.K + p.Q + p.group + p.aSel + p.bSel + p.aMN + p.bMN;
+        asm volatile("" :: "r"(touch));
+    }
     if (threadIdx.x == 0) {
+        NTB_MARK(8);
         for (int s = 0; s < STAGES; s++) {
             MbarInit(SmemAddr(&barFull[s]), 1);
             MbarInit(SmemAddr(&barEmpty[s]), 1);
@@ -530,28 +621,41 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             MbarInit(SmemAddr(&barTEmpty[b]), 4);
         }
         abortFlag = 0;
+        NTB_MARK(9);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        NTB_MARK(10);
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      :: "r"(SmemAddr(&tmemBaseSlot)), "r"((uint32_t)TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (lane == 0) NTB_MARK(11);
     }
-    TcFenceBefore();
-    __syncthreads();
-    TcFenceAfter();
-    const uint32_t tmemBase = *(volatile uint32_t *)&tmemBaseSlot;
+    /* The producer warp initialised the barriers itself and needs no TMEM: it signals the
+       CTA-wide barrier without waiting and starts loading, so the TMEM allocation and the
+       hand-shake overlap the first copies. Everybody else waits for both. */
+    uint32_t tmemBase = 0;
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("bar.arrive 1, %0;" :: "r"((uint32_t)blockDim.x) : "memory");
+    }
+    else {
+        TcFenceBefore();
+        asm volatile("bar.sync 1, %0;" :: "r"((uint32_t)blockDim.x) : "memory");
+        TcFenceAfter();
+        tmemBase = *(volatile uint32_t *)&tmemBaseSlot;
+    }
 
 #ifdef NTB_WAIT_STATS
     long long wstat[4] = {0, 0, 0, 0};
-    const long long kernelT0 = clock64();
 #endif
+    if (threadIdx.x == 0) NTB_MARK(0);
     const int kBlocks = (p.K + EPR - 1) / EPR;
     /* k-blocks accumulated in TMEM before the partial sum is handed to the epilogue */
     const int chunkBlocks = MODE == 0 ? kBlocks : FP32_CHUNK_BLOCKS;
-    const long long firstTile = blockIdx.x;
-    const long long tileStep = gridDim.x;
+    const int firstTile = blockIdx.x;
+    const int tileStep = gridDim.x;
 
     if (warp == 0) {
         /* ------------------------------------------------------------ TMA producer */
@@ -559,13 +663,15 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
-            for (long long t = firstTile; ok && t < p.totalTiles; t += tileStep) {
-                TileCoord tc = DecodeTile(t, p.tilesM, p.tilesN, p.group);
+            for (int t = firstTile; ok && t < p.totalTiles; t += tileStep) {
+                TileCoord tc = DecodeTile(t, p);
                 const int m0 = tc.mBlk * BM, n0 = tc.nBlk * BN;
-                const int ba = BatchCoord(p.aSel, tc.prob, p.Q);
-                const int bb = BatchCoord(p.bSel, tc.prob, p.Q);
+                const int ba = BatchCoord(p.aSel, tc.prob, p);
+                const int bb = BatchCoord(p.bSel, tc.prob, p);
+                NTB_MARK(12);
                 for (int kb = 0; kb < kBlocks; kb++) {
                     NTB_TIMED(0, ok = MbarWait(SmemAddr(&barEmpty[s]), ph ^ 1u, abortPtr, p.status));
+                    NTB_MARK(13);
                     if (!ok)
                         break;
                     const uint32_t full = SmemAddr(&barFull[s]);
@@ -573,6 +679,7 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                     const uint32_t bDst = aDst + A_TILE_BYTES;
                     const int k0 = kb * EPR;
                     MbarExpectTx(full, PLANE_BYTES);
+                    NTB_MARK(14);
                     if (!p.aMN) {
                         TmaLoad3D(aDst, &tmA, full, k0, m0, ba);
                     }
@@ -608,6 +715,7 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                                 TmaPrefetch3D(&tmB, n0 + j * EPR, kp, bb);
                         }
                     }
+                    NTB_MARK(1);
                     if (++s == STAGES) { s = 0; ph ^= 1u; }
                 }
             }
@@ -633,7 +741,7 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             uint32_t ph = 0;
             uint32_t it = 0;                      /* accumulator hand-overs so far */
             bool ok = true;
-            for (long long t = firstTile; ok && t < p.totalTiles; t += tileStep) {
+            for (int t = firstTile; ok && t < p.totalTiles; t += tileStep) {
                 for (int kb0 = 0; ok && kb0 < kBlocks; kb0 += chunkBlocks, ++it) {
                     const uint32_t buf = it & 1u;
                     NTB_TIMED(2, ok = MbarWait(SmemAddr(&barTEmpty[buf]), ((it >> 1) & 1u) ^ 1u, abortPtr, p.status));
@@ -646,6 +754,7 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                         NTB_TIMED(1, ok = MbarWait(SmemAddr(MODE == 0 ? &barFull[s] : &barConv[s]), ph, abortPtr, p.status));
                         if (!ok)
                             break;
+                        NTB_MARK(2);
                         TcFenceAfter();
                         const uint32_t aHi = smemBase + s * STAGE_BYTES;
                         const uint32_t bHi = aHi + A_TILE_BYTES;
@@ -670,6 +779,7 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                     }
                     if (ok)
                         TcCommit(SmemAddr(&barTFull[buf]));
+                    NTB_MARK(3);
                 }
             }
         }
@@ -681,31 +791,35 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         bool ok = true;
         TileWriter<OutT> writer;
         writer.Init(smemBase + STAGES * STAGE_BYTES, sub, &tmC);
-        for (long long t = firstTile; ok && t < p.totalTiles; t += tileStep) {
-            TileCoord tc = DecodeTile(t, p.tilesM, p.tilesN, p.group);
+        for (int t = firstTile; ok && t < p.totalTiles; t += tileStep) {
+            TileCoord tc = DecodeTile(t, p);
             const int row0 = tc.mBlk * BM + sub * 32;
             const int row = row0 + lane;
             const int n0 = tc.nBlk * BN;
-            const int pp = tc.prob / p.Q, qq = tc.prob % p.Q;
-            const int bc = BatchCoord(p.cSel, tc.prob, p.Q);
+            int pp, qq;
+            SplitProb(p, tc.prob, pp, qq);
+            const int bc = BatchCoord(p.cSel, tc.prob, p);
             OutT * cRow = (OutT *)p.c + pp * p.sCp + qq * p.sCq + (long long)row * p.ldc;
             const bool rowOk = row < p.M;
             if (MODE == 0) {
                 /* one accumulator hand-over per tile: load 32 columns, scale, store */
                 const uint32_t buf = it & 1u;
-                ok = MbarWaitWarp(SmemAddr(&barTFull[buf]), (it >> 1) & 1u, abortPtr, p.status, 2000);
+                ok = MbarWaitWarp(SmemAddr(&barTFull[buf]), (it >> 1) & 1u, abortPtr, p.status, (uint32_t)p.epiHint);
                 if (!ok)
                     break;
+                if (warp == 2 && lane == 0) NTB_MARK(4);
                 TcFenceAfter();
                 const uint32_t tRow = tmemBase + ((uint32_t)(sub * 32) << 16) + buf * BN;
 #pragma unroll 1
-                for (int ch = 0; ch < BN / 32; ch++) {
-                    const int c0 = n0 + ch * 32;
+                for (int ch = 0; ch < BN / 64; ch++) {
+                    const int c0 = n0 + ch * 64;
                     if (c0 >= p.N)
                         break;                     /* uniform across the warp */
-                    float v[32];
-                    TmemLoad32(tRow + ch * 32, v);
+                    float v[64];
+                    TmemLoad64(tRow + ch * 64, v);
                     writer.Put32(p, cRow, rowOk, row0, c0, bc, v, lane);
+                    if (c0 + 32 < p.N)
+                        writer.Put32(p, cRow, rowOk, row0, c0 + 32, bc, v + 32, lane);
                 }
                 TcFenceBefore();
                 __syncwarp();
@@ -723,7 +837,7 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 const uint32_t tRun = tmemBase + ((uint32_t)(sub * 32) << 16) + 2 * BN;   /* running sum */
                 for (int kb0 = 0; ok && kb0 < kBlocks; kb0 += chunkBlocks, ++it) {
                     const uint32_t buf = it & 1u;
-                    ok = MbarWaitWarp(SmemAddr(&barTFull[buf]), (it >> 1) & 1u, abortPtr, p.status, 2000);
+                    ok = MbarWaitWarp(SmemAddr(&barTFull[buf]), (it >> 1) & 1u, abortPtr, p.status, (uint32_t)p.epiHint);
                     if (!ok)
                         break;
                     TcFenceAfter();
@@ -756,7 +870,9 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 }
             }
         }
+        if (warp == 2 && lane == 0) NTB_MARK(5);
         writer.Finish(lane);
+        if (warp == 2 && lane == 0) NTB_MARK(6);
     }
     else if (MODE != 0) {
         /* ------------------------------------------------------------ fp32 hi/lo split */
@@ -764,7 +880,7 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         int s = 0;
         uint32_t ph = 0;
         bool ok = true;
-        for (long long t = firstTile; ok && t < p.totalTiles; t += tileStep) {
+        for (int t = firstTile; ok && t < p.totalTiles; t += tileStep) {
             for (int kb = 0; kb < kBlocks; kb++) {
                 ok = MbarWait(SmemAddr(&barFull[s]), ph, abortPtr, p.status);
                 if (!ok)
@@ -812,6 +928,11 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
                      :: "r"(tmemBase), "r"((uint32_t)TMEM_COLS) : "memory");
     }
+#ifdef NTB_WAIT_STATS
+    if (threadIdx.x == 32) NTB_MARK(7);
+    __syncthreads();
+    if (blockIdx.x == 0 && threadIdx.x < 16) gTimeline[threadIdx.x] = tlShared[threadIdx.x];
+#endif
 }
 
 /* ---------------------------------------------------------------- the CTA-pair kernel */
@@ -916,6 +1037,16 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t smemBase = (SmemAddr(smemRaw) + 1023u) & ~1023u;
     volatile int * abortPtr = &abortFlag;
 
+    if (threadIdx.x == 64) {
+        /* an idle epilogue lane pulls the kernel parameters and the tensor maps towards the SM
+           while the other warps set up, so the producer's first use of them does not stall */
+        PrefetchTensorMap(&tmA);
+        PrefetchTensorMap(&tmB);
+        if (p.cTma)
+            PrefetchTensorMap(&tmC);
+        int touch = p.totalTiles + p.tilesM + p.tilesN + p.K + p.Q + p.group + p.aSel + p.bSel + p.aMN + p.bMN;
+        asm volatile("" :: "r"(touch));
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
             MbarInit(SmemAddr(&barFull[s]), 1);
@@ -944,20 +1075,20 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const long long kernelT0 = clock64();
 #endif
     const int kBlocks = (p.K + EPR - 1) / EPR;
-    const long long firstTile = blockIdx.x >> 1;
-    const long long tileStep = gridDim.x >> 1;
+    const int firstTile = blockIdx.x >> 1;
+    const int tileStep = gridDim.x >> 1;
 
     if (warp == 0) {
         if (lane == 0) {
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
-            for (long long t = firstTile; ok && t < p.totalTiles; t += tileStep) {
-                TileCoord tc = DecodeTile(t, p.tilesM, p.tilesN, p.group);
+            for (int t = firstTile; ok && t < p.totalTiles; t += tileStep) {
+                TileCoord tc = DecodeTile(t, p);
                 const int m0 = tc.mBlk * PM + (int)rank * BM;
                 const int n0 = tc.nBlk * BN + (int)rank * BNH;
-                const int ba = BatchCoord(p.aSel, tc.prob, p.Q);
-                const int bb = BatchCoord(p.bSel, tc.prob, p.Q);
+                const int ba = BatchCoord(p.aSel, tc.prob, p);
+                const int bb = BatchCoord(p.bSel, tc.prob, p);
                 for (int kb = 0; kb < kBlocks; kb++) {
                     NTB_TIMED(0, ok = MbarWait(SmemAddr(&barEmpty[s]), ph ^ 1u, abortPtr, p.status));
                     if (!ok)
@@ -1006,7 +1137,7 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             uint32_t ph = 0;
             uint32_t it = 0;
             bool ok = true;
-            for (long long t = firstTile; ok && t < p.totalTiles; t += tileStep, ++it) {
+            for (int t = firstTile; ok && t < p.totalTiles; t += tileStep, ++it) {
                 const uint32_t buf = it % NBUF;
                 NTB_TIMED(2, ok = MbarWait(SmemAddr(&barTEmpty[buf]), ((it / NBUF) & 1u) ^ 1u, abortPtr, p.status));
                 if (!ok)
@@ -1043,14 +1174,15 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         bool ok = true;
         TileWriter<OutT> writer;
         writer.Init(smemBase + STAGES * STAGE_BYTES, sub32, &tmC);
-        for (long long t = firstTile; ok && t < p.totalTiles; t += tileStep, ++it) {
-            TileCoord tc = DecodeTile(t, p.tilesM, p.tilesN, p.group);
+        for (int t = firstTile; ok && t < p.totalTiles; t += tileStep, ++it) {
+            TileCoord tc = DecodeTile(t, p);
             const int n0 = tc.nBlk * BN;
-            const int pp = tc.prob / p.Q, qq = tc.prob % p.Q;
-            const int bc = BatchCoord(p.cSel, tc.prob, p.Q);
+            int pp, qq;
+            SplitProb(p, tc.prob, pp, qq);
+            const int bc = BatchCoord(p.cSel, tc.prob, p);
             OutT * cBase = (OutT *)p.c + pp * p.sCp + qq * p.sCq;
             const uint32_t buf = it % NBUF;
-            NTB_TIMED(3, ok = MbarWaitWarp(SmemAddr(&barTFull[buf]), (it / NBUF) & 1u, abortPtr, p.status, 2000));
+            NTB_TIMED(3, ok = MbarWaitWarp(SmemAddr(&barTFull[buf]), (it / NBUF) & 1u, abortPtr, p.status, (uint32_t)p.epiHint));
             if (!ok)
                 break;
             TcFenceAfter();
@@ -1062,13 +1194,15 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 const bool rowOk = row < p.M;
                 const uint32_t tRow = tmemBase + ((uint32_t)(sub32 * 32) << 16) + buf * (MSUB * BN) + sub * BN;
 #pragma unroll 1
-                for (int ch = 0; ch < BN / 32; ch++) {
-                    const int c0 = n0 + ch * 32;
+                for (int ch = 0; ch < BN / 64; ch++) {
+                    const int c0 = n0 + ch * 64;
                     if (c0 >= p.N)
                         break;
-                    float v[32];
-                    TmemLoad32(tRow + ch * 32, v);
+                    float v[64];
+                    TmemLoad64(tRow + ch * 64, v);
                     writer.Put32(p, cRow, rowOk, row0, c0, bc, v, lane);
+                    if (c0 + 32 < p.N)
+                        writer.Put32(p, cRow, rowOk, row0, c0 + 32, bc, v + 32, lane);
                 }
             }
             TcFenceBefore();
@@ -1300,7 +1434,10 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
     tp.aMN = p.aMN; tp.bMN = p.bMN;
     tp.tilesM = pair ? (p.M + 2 * BM * msub - 1) / (2 * BM * msub) : (p.M + BM - 1) / BM;
     tp.tilesN = (p.N + bn - 1) / bn;
-    tp.totalTiles = (long long)tp.tilesM * tp.tilesN * p.count;
+    const long long tiles64 = (long long)tp.tilesM * tp.tilesN * p.count;
+    if (tiles64 > 2147483647LL - 1024)
+        return NTB_ERR_LIMIT;
+    tp.totalTiles = (int)tiles64;
     tp.alpha = p.alpha; tp.beta = p.beta;
     tp.bias = p.bias; tp.act = p.act;
     tp.status = ctx.status;
@@ -1308,6 +1445,12 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
     tp.group = Knob("NTB_TILE_GROUP", 8);
     if (tp.group < 1)
         tp.group = 1;
+    tp.epiHint = Knob("NTB_EPI_HINT_NS", 2000);
+    tp.fdPerProb.Set((uint32_t)(tp.tilesM * tp.tilesN));
+    tp.fdBand.Set((uint32_t)(tp.group * tp.tilesN));
+    tp.fdGroup.Set((uint32_t)tp.group);
+    tp.fdLast.Set((uint32_t)(tp.tilesM % tp.group ? tp.tilesM % tp.group : tp.group));
+    tp.fdQ.Set((uint32_t)p.Q);
     const long long ces = ElemSize(p.dtC);
     tp.cVec = (((uintptr_t)p.c & 15) == 0) && ((p.ldc * ces) % 16 == 0) &&
               ((p.sCp * ces) % 16 == 0) && ((p.sCq * ces) % 16 == 0);
@@ -1372,6 +1515,14 @@ extern "C" void ntb_debug_wait_stats(unsigned long long * out)
     cudaMemcpyFromSymbol(out, gWaitStats, sizeof(unsigned long long) * 8);
     unsigned long long zero[8] = {0};
     cudaMemcpyToSymbol(gWaitStats, zero, sizeof(zero));
+}
+
+extern "C" void ntb_debug_timeline(unsigned long long * out)
+{
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, gTimeline, sizeof(unsigned long long) * 16);
+    unsigned long long zero[16] = {0};
+    cudaMemcpyToSymbol(gTimeline, zero, sizeof(zero));
 }
 #endif
 
