@@ -1341,14 +1341,14 @@ int Knob(const char * name, int dflt)
 /*
  * Cost model for the tile shape, in SM clocks per CTA: waves x (k-blocks x clocks per
  * k-block + epilogue and hand-over cost of one tile). A k-block costs the larger of its MMA
- * time and the time its operand bytes take to arrive (an SM takes in about 57 bytes per
+ * time and the time its operand bytes take to arrive (an SM takes in about 60 bytes per
  * clock here, measured on the large product). Returns the tile width of the single-CTA
  * kernel, or 0 / -1 for the CTA-pair kernel with 256 x 256 / 512 x 256 tiles. Constants
  * were fitted to timings of the benchmark configurations on a B200.
  */
 int PickBN(const Problem & p, int smCount, int mode)
 {
-    const double ingest = 57.0;                       /* bytes per clock per SM */
+    const double ingest = 62.0;                       /* bytes per clock per SM */
     const int es = mode == 0 ? 2 : 4;
     const int kElems = ROW_BYTES / es;
     const double kBlocks = (double)((p.K + kElems - 1) / kElems);
