@@ -106,6 +106,25 @@ int ntb_gemm_bias_act(int devID, void * stream,
                       float alpha, float beta, int act);
 
 /*
+ * Fused scaled-dot-product attention on half tensors:
+ *
+ *        out = softmax(scale * q * k^T + mask) * v        for each of `blocks` blocks
+ *
+ * q, out: [blocks, lenQ, dim]; k, v: [blocks, lenK, dim], packed, X_FLOAT16. mask is NULL or
+ * fp32, additive, [lenQ, lenK] per block with maskBlockStride elements between blocks
+ * (0 = one mask for all blocks). One kernel instead of the inference-time chain of the
+ * transformer sample -- BMMul(q, k^T), ConvertDataType, Sum(mask), Softmax, ConvertDataType,
+ * BMMul(att, v) (source/sample/transformer/submodel/Attention.cpp:206-238) -- whose score
+ * tensor never reaches HBM here. Softmax as source/tensor/function/Softmax.cpp:60-115
+ * (maximum subtracted, fp32, a row whose sum is 0 gives zeros). Limits of this version:
+ * dim == 64 and lenK <= 256, else NTB_ERR_LIMIT; no dropout.
+ */
+int ntb_attention(int devID, void * stream,
+                  const void * q, const void * k, const void * v, const float * mask, void * out,
+                  int dtype, int blocks, int lenQ, int lenK, int dim,
+                  long long maskBlockStride, float scale);
+
+/*
  * `count` GEMMs of one shape whose matrices lie at constant element strides; a stride
  * of 0 reuses one matrix for every problem. One launch covers all problems.
  * Replaces _CudaBLASMatrixMULBatchedStrided

@@ -164,6 +164,11 @@ int GrowStage(DeviceCtx * ctx, int slot, size_t bytes)
 
 }
 
+DeviceCtx * CtxFor(int dev)
+{
+    return GetCtx(dev);
+}
+
 void CountLaunch()
 {
     gLaunches.fetch_add(1);

@@ -55,6 +55,9 @@ bool TcEligible(const Problem & p);
 int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int * route);
 int LaunchSimt(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream);
 
+/* the device's context (created on first use); the caller has made `dev` current */
+DeviceCtx * CtxFor(int dev);
+
 void CountLaunch();
 int ForcedRoute();           /* value of the last ntb_set_route() */
 

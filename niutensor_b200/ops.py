@@ -177,3 +177,38 @@ def MulAndShift(x, w, b, alpha=1.0, transposedX=X_NOTRANS, transposedW=X_NOTRANS
                                       x2.shape[1], w.shape[1], wm, alpha, 0.0, act)
     _raise_rc(rc, "MulAndShift")
     return c
+
+
+def ScaledDotProductAttention(q, k, v, mask=None, scale=None):
+    """softmax(scale * q k^T + mask) v over the last two dimensions, leading dimensions being
+    (head, batch) blocks: the fused form of the chain in Attention::MakeAttention
+    (source/sample/transformer/submodel/Attention.cpp:206-238; inference, no dropout).
+    q [..., lenQ, 64], k, v [..., lenK, 64] half tensors; mask None or fp32 of shape
+    [lenQ, lenK] (shared) or [..., lenQ, lenK]; scale defaults to 1 / sqrt(64)."""
+    _check(q.is_cuda and k.is_cuda and v.is_cuda, "this library has no CPU path: tensors must live on a CUDA device")
+    _check(q.dtype == torch.float16 and k.dtype == q.dtype and v.dtype == q.dtype, "Unsupported data type!")
+    _check(q.dim() >= 2 and q.shape[:-2] == k.shape[:-2] == v.shape[:-2], "Incorrect tensor sizes!")
+    _check(k.shape == v.shape and q.shape[-1] == k.shape[-1], "Unmatched tensors in multiplication!")
+    _check(q.is_contiguous() and k.is_contiguous() and v.is_contiguous(), "tensors must be dense and packed")
+    lenQ, d = q.shape[-2], q.shape[-1]
+    lenK = k.shape[-2]
+    blocks = 1
+    for n in q.shape[:-2]:
+        blocks *= n
+    stride = 0
+    mptr = None
+    if mask is not None:
+        _check(mask.is_cuda and mask.dtype == torch.float32 and mask.is_contiguous(), "the mask must be a packed fp32 CUDA tensor")
+        if mask.dim() == 2:
+            _check(tuple(mask.shape) == (lenQ, lenK), "Incorrect tensor sizes!")
+        else:
+            _check(tuple(mask.shape) == tuple(q.shape[:-2]) + (lenQ, lenK), "Incorrect tensor sizes!")
+            stride = lenQ * lenK
+        mptr = mask.data_ptr()
+    out = torch.empty_like(q)
+    if scale is None:
+        scale = 1.0 / (d ** 0.5)
+    rc = capi.lib().ntb_attention(q.device.index, _stream(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), mptr,
+                                  out.data_ptr(), X_FLOAT16, blocks, lenQ, lenK, d, stride, scale)
+    _raise_rc(rc, "ScaledDotProductAttention")
+    return out

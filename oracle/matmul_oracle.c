@@ -19,6 +19,8 @@
 #include <stddef.h>
 #include <string.h>
 #include <pthread.h>
+#include <math.h>
+#include <stdlib.h>
 
 #define ORC_TRANS 0
 #define ORC_NOTRANS 1
@@ -218,4 +220,62 @@ void orc_mulandshift_f32(const float * x, int transX, const float * w, int trans
             c[(size_t)i * mc + j] = v;
         }
     }
+}
+
+/*
+ * Scaled-dot-product attention as the transformer sample composes it in inference
+ * (source/sample/transformer/submodel/Attention.cpp:206-238): q is scaled in place (:206),
+ * att = BMMul(q, k^T) (:212), the additive mask is summed in (:221-224), Softmax over the
+ * last dimension (:227; source/tensor/function/Softmax.cpp:60-115: subtract the row
+ * maximum, exp, divide by the row sum, clamp to [0, 1], an all-zero row when the sum is 0),
+ * out = BMMul(att, v) (:236). All in fp32 here. The row sum is accumulated left to right;
+ * the reference's _ReduceSum sums in vector lanes (source/tensor/core/reduce/
+ * ReduceSum.cpp), so this function agrees with the compiled reference to rounding error,
+ * not bit for bit -- the test pins it at 1e-6.
+ * q: [blocks, lenQ, dim], k, v: [blocks, lenK, dim], mask: NULL or [.., lenQ, lenK] with
+ * maskBlockStride elements between blocks (0 = one mask for all), out: [blocks, lenQ, dim].
+ */
+void orc_attention_f32(const float * q, const float * k, const float * v, const float * mask, float * out,
+                       int blocks, int lenQ, int lenK, int dim, long long maskBlockStride, float scale)
+{
+    int b, i, j;
+    float * qs = (float *)malloc(sizeof(float) * (size_t)lenQ * dim);
+    float * att = (float *)malloc(sizeof(float) * (size_t)lenQ * lenK);
+    for (b = 0; b < blocks; b++) {
+        const float * qb = q + (size_t)b * lenQ * dim;
+        const float * kb = k + (size_t)b * lenK * dim;
+        const float * vb = v + (size_t)b * lenK * dim;
+        const float * mb = mask ? mask + (size_t)b * maskBlockStride : NULL;
+        for (i = 0; i < lenQ * dim; i++)
+            qs[i] = qb[i] * scale;
+        orc_matmul2d_f32(qs, ORC_NOTRANS, kb, ORC_TRANS, att, lenQ, dim, lenK, dim, lenQ, lenK, 1.0f, 0.0f);
+        for (i = 0; i < lenQ; i++) {
+            float * row = att + (size_t)i * lenK;
+            float mx, sum = 0;
+            if (mb)
+                for (j = 0; j < lenK; j++)
+                    row[j] = row[j] + mb[(size_t)i * lenK + j];
+            mx = row[0];
+            for (j = 1; j < lenK; j++)
+                if (row[j] > mx)
+                    mx = row[j];
+            for (j = 0; j < lenK; j++)
+                sum += (float)exp(row[j] - mx);
+            for (j = 0; j < lenK; j++) {
+                float r = 0;
+                if (sum != 0) {
+                    r = (float)exp(row[j] - mx) / sum;
+                    if (r > 1.0f)
+                        r = 1.0f;
+                    else if (r < 0)
+                        r = 0;
+                }
+                row[j] = r;
+            }
+        }
+        orc_matmul2d_f32(att, ORC_NOTRANS, vb, ORC_NOTRANS, out + (size_t)b * lenQ * dim,
+                         lenQ, lenK, lenK, dim, lenQ, dim, 1.0f, 0.0f);
+    }
+    free(qs);
+    free(att);
 }

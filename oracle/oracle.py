@@ -65,6 +65,8 @@ class Oracle:
         self.lib.orc_matmul_broadcast_f32.argtypes = [_F32P, ctypes.c_int, _F32P, ctypes.c_int, _F32P] + \
             [ctypes.c_int] * 8 + [ctypes.c_float] * 2
         self.lib.orc_set_threads.argtypes = [ctypes.c_int]
+        self.lib.orc_attention_f32.argtypes = [_F32P, _F32P, _F32P, _F32P, _F32P] + [ctypes.c_int] * 4 + \
+            [ctypes.c_longlong, ctypes.c_float]
         self.lib.orc_mulandshift_f32.argtypes = [_F32P, ctypes.c_int, _F32P, ctypes.c_int, _F32P, _F32P] + \
             [ctypes.c_int] * 6 + [ctypes.c_float, ctypes.c_int]
 
@@ -95,6 +97,21 @@ class Oracle:
         self.lib.orc_mulandshift_f32(_fp(x2), tX, _fp(w), tW, _fp(b), _fp(c), x2.shape[0], x2.shape[1],
                                      w.shape[0], w.shape[1], M, N, alpha, 1 if rectify else 0)
         return c.reshape(lead + (M // max(1, int(np.prod(lead, dtype=np.int64))), N)) if lead else c
+
+    def attention(self, q, k, v, mask=None, scale=1.0):
+        """softmax(scale * q k^T + mask) v per block; q [blocks, lenQ, d], k, v [blocks, lenK, d],
+        mask None, [lenQ, lenK] (shared) or [blocks, lenQ, lenK]."""
+        q, k, v = _as_f32(q), _as_f32(k), _as_f32(v)
+        blocks, lenQ, d = q.shape
+        lenK = k.shape[1]
+        out = np.zeros((blocks, lenQ, d), np.float32)
+        mp, stride = None, 0
+        if mask is not None:
+            mask = _as_f32(mask)
+            mp = _fp(mask)
+            stride = lenQ * lenK if mask.ndim == 3 else 0
+        self.lib.orc_attention_f32(_fp(q), _fp(k), _fp(v), mp, _fp(out), blocks, lenQ, lenK, d, stride, scale)
+        return out
 
     def matmul_batched(self, a, tA, b, tB, alpha=1.0, beta=0.0, c=None):
         """_MatrixMulBatched: equal leading extents, block i of a meets block i of b."""
@@ -210,6 +227,23 @@ def ref_mulandshift(ref, x, w, b, alpha=1.0, tX=X_NOTRANS, tW=X_NOTRANS):
     if rc != 0:
         raise RuntimeError("ref_mulandshift_f32 failed: %d" % rc)
     return c
+
+
+def ref_attention(ref, q, k, v, mask=None, scale=1.0):
+    """The reference's own CPU operator chain for inference-time attention."""
+    q, k, v = _as_f32(q), _as_f32(k), _as_f32(v)
+    blocks, lenQ, d = q.shape
+    lenK = k.shape[1]
+    out = np.zeros((blocks, lenQ, d), np.float32)
+    ref.lib.ref_attention_f32.argtypes = [_F32P, _F32P, _F32P, _F32P, _F32P] + [ctypes.c_int] * 4 + [ctypes.c_float]
+    mp = None
+    if mask is not None:
+        mask = _as_f32(np.broadcast_to(mask, (blocks, lenQ, lenK)))
+        mp = _fp(mask)
+    rc = ref.lib.ref_attention_f32(_fp(q), _fp(k), _fp(v), mp, _fp(out), blocks, lenQ, lenK, d, scale)
+    if rc != 0:
+        raise RuntimeError("ref_attention_f32 failed")
+    return out
 
 
 def round_to_half(x):

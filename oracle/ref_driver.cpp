@@ -17,6 +17,9 @@
 #include "tensor/core/arithmetic/MatrixMul2D.h"
 #include "tensor/core/arithmetic/MatrixMulBatched.h"
 #include "tensor/core/arithmetic/MulAndShift.h"
+#include "tensor/core/arithmetic/Sum.h"
+#include "tensor/core/math/ScaleAndShift.h"
+#include "tensor/function/Softmax.h"
 #ifdef USE_BLAS
 #include "tensor/XBLAS.h"
 #endif
@@ -93,6 +96,37 @@ int ref_mulandshift_f32(const float * x, int xOrder, const int * xDims, int tran
     Drop(tw);
     Drop(tb);
     return rc;
+}
+
+/* The inference-time attention chain of source/sample/transformer/submodel/Attention.cpp:
+   206-238 with the reference's own CPU operators: scale q, BMMul(q, k^T), add the mask,
+   Softmax over the last dimension, BMMul(att, v). mask may be NULL; otherwise it has the
+   shape of the scores. */
+int ref_attention_f32(const float * q, const float * k, const float * v, const float * mask, float * out,
+                      int blocks, int lenQ, int lenK, int dim, float scale)
+{
+    int dq[3] = { blocks, lenQ, dim }, dk[3] = { blocks, lenK, dim }, ds[3] = { blocks, lenQ, lenK };
+    XTensor tq, att, att2;
+    InitTensorV2(&tq, 3, dq, X_FLOAT, 1.0F, -1);
+    InitTensorV2(&att, 3, ds, X_FLOAT, 1.0F, -1);
+    InitTensorV2(&att2, 3, ds, X_FLOAT, 1.0F, -1);
+    memcpy(tq.data, q, sizeof(float) * (size_t)tq.unitNum);
+    XTensor * tk = View((float*)k, 3, dk);
+    XTensor * tv = View((float*)v, 3, dk);
+    XTensor * to = View(out, 3, dq);
+    _ScaleAndShiftMe(&tq, scale, 0);
+    _MatrixMulBatched(&tq, X_NOTRANS, tk, X_TRANS, &att);
+    if (mask != NULL) {
+        XTensor * tm = View((float*)mask, 3, ds);
+        _Sum(&att, tm, &att);
+        Drop(tm);
+    }
+    _Softmax(&att, &att2, 2);
+    _MatrixMulBatched(&att2, X_NOTRANS, tv, X_NOTRANS, to);
+    Drop(tk);
+    Drop(tv);
+    Drop(to);
+    return 0;
 }
 
 /* 1 when this build routes dense fp32 GEMMs to cblas_sgemm (XTensorBLAS.cpp:39) */

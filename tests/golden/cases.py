@@ -67,3 +67,23 @@ def mulandshift_cases():
         b = rng.normal(size=(N,)).astype(np.float32)
         out.append((x, w, b, alpha, tX, tW))
     return out
+
+
+def attention_cases():
+    """(q, k, v, mask, scale): small blocks with the head size the fused kernel supports;
+    mask None, shared [lenQ, lenK] or per block, with -1e9 entries as padding masks have."""
+    rng = np.random.default_rng(20242)
+    out = []
+    for (blocks, lenQ, lenK, kind) in [(2, 5, 7, "none"), (3, 33, 65, "block"), (2, 130, 200, "shared"),
+                                       (1, 1, 1, "none"), (2, 64, 256, "block")]:
+        q = rng.normal(size=(blocks, lenQ, 64)).astype(np.float32)
+        k = rng.normal(size=(blocks, lenK, 64)).astype(np.float32)
+        v = rng.normal(size=(blocks, lenK, 64)).astype(np.float32)
+        mask = None
+        if kind == "shared":
+            mask = np.where(np.arange(lenK)[None, :] > np.arange(lenQ)[:, None] + 70, -1e9, 0.0).astype(np.float32)
+        elif kind == "block":
+            mask = np.where(rng.uniform(size=(blocks, lenQ, lenK)) < 0.25, -1e9, 0.0).astype(np.float32)
+            mask[:, :, 0] = 0.0
+        out.append((q, k, v, mask, 0.125))
+    return out

@@ -17,6 +17,10 @@ without either.
   ref_mulandshift.npz  outputs of the reference's user-level MulAndShift (CPU) on the
                    seeded inputs of tests/golden/cases.py::mulandshift_cases.
 
+  ref_attention.npz  outputs of the reference's CPU operator chain for inference-time
+                   attention (scale, BMMul, Sum(mask), Softmax, BMMul) on the seeded inputs
+                   of tests/golden/cases.py::attention_cases.
+
 Usage: python tests/golden/make_golden.py
 """
 import json
@@ -31,8 +35,8 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 REF = os.environ.get("REF", "/root/reference")
 
-from oracle.oracle import Reference, ref_mulandshift, X_TRANS, X_NOTRANS  # noqa: E402
-from tests.golden.cases import seeded_cases, mulandshift_cases  # noqa: E402
+from oracle.oracle import Reference, ref_mulandshift, ref_attention, X_TRANS, X_NOTRANS  # noqa: E402
+from tests.golden.cases import seeded_cases, mulandshift_cases, attention_cases  # noqa: E402
 
 TEST_FILES = ["TMatrixMul.cpp", "TMatrixMul2D.cpp", "TMatrixMul2DParallel.cpp",
               "TMatrixMulBatched.cpp"]
@@ -93,6 +97,12 @@ def main():
         arrays["y%d" % i] = ref_mulandshift(ref, x, w, b, alpha, tX, tW)
     np.savez_compressed(os.path.join(HERE, "ref_mulandshift.npz"), **arrays)
     print("ref_mulandshift.npz: %d cases" % len(arrays))
+
+    arrays = {}
+    for i, (q, k, v, mask, scale) in enumerate(attention_cases()):
+        arrays["o%d" % i] = ref_attention(ref, q, k, v, mask, scale)
+    np.savez_compressed(os.path.join(HERE, "ref_attention.npz"), **arrays)
+    print("ref_attention.npz: %d cases" % len(arrays))
 
 
 if __name__ == "__main__":

@@ -9,7 +9,8 @@ import numpy as np
 import pytest
 
 from oracle.oracle import (Oracle, Reference, ref_available, rel_fro, X_TRANS, X_NOTRANS)
-from tests.golden.cases import seeded_cases, mulandshift_cases, FORM_GENERAL, FORM_BATCHED, FORM_2D
+from tests.golden.cases import (seeded_cases, mulandshift_cases, attention_cases, FORM_GENERAL, FORM_BATCHED,
+                                FORM_2D)
 
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
@@ -73,6 +74,17 @@ def test_mulandshift_oracle_matches_stored_reference_outputs_bit_for_bit(oracle)
     x, w, b = cases[1][:3]
     r = oracle.mulandshift(x, w, b, rectify=True)
     assert np.array_equal(r, np.maximum(oracle.mulandshift(x, w, b), 0))
+
+
+def test_attention_oracle_matches_stored_reference_outputs(oracle):
+    """Pinned at 1e-6: the reference's row sums run in vector lanes, the oracle's left to right."""
+    z = np.load(os.path.join(GOLD, "ref_attention.npz"))
+    cases = attention_cases()
+    assert len(cases) == len(z.files) == 5
+    for i, (q, k, v, mask, scale) in enumerate(cases):
+        got = oracle.attention(q, k, v, mask, scale)
+        assert got.shape == z["o%d" % i].shape
+        assert rel_fro(got, z["o%d" % i]) <= 1e-6, i
 
 
 def test_thread_count_does_not_change_bits():
