@@ -125,6 +125,24 @@ int ntb_attention(int devID, void * stream,
                   long long maskBlockStride, float scale);
 
 /*
+ * Row-wise log-softmax over the last dimension in two halves, for logits whose rows are
+ * spread over several GPUs (vocabulary shards of the output layer,
+ * source/sample/transformer/submodel/Output.cpp:86-101, LogSoftmax.cpp:40-170).
+ * ntb_row_stats: rowMax[r] = max_c x[r, c], rowSumExp[r] = sum_c exp(x[r, c] - rowMax[r])
+ * over the local `cols` columns (fp32 device arrays of `rows` entries). The caller
+ * combines shards: M = max of the maxima, S = sum of rowSumExp * exp(rowMax - M).
+ * ntb_logsoftmax_apply: y[r, c] = log(exp(x[r, c] - M[r]) / S[r]), floored at -20, NaN and
+ * infinities replaced by -20, zeros for a row with S == 0, as the reference does; y may be
+ * x. x, y: X_FLOAT16 or X_FLOAT device matrices with row pitches ldx, ldy (elements).
+ * With one shard, the two calls in sequence are the reference's LogSoftmax.
+ */
+int ntb_row_stats(int devID, void * stream, const void * x, int dtype, int rows, int cols, long long ld,
+                  float * rowMax, float * rowSumExp);
+int ntb_logsoftmax_apply(int devID, void * stream, const void * x, void * y, int dtype,
+                         int rows, int cols, long long ldx, long long ldy,
+                         const float * rowMax, const float * rowSumExp);
+
+/*
  * `count` GEMMs of one shape whose matrices lie at constant element strides; a stride
  * of 0 reuses one matrix for every problem. One launch covers all problems.
  * Replaces _CudaBLASMatrixMULBatchedStrided

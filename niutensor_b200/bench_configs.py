@@ -189,9 +189,42 @@ def run_attention(iters, use_graph, with_cublas, dev):
     return line
 
 
+def run_output_layer(iters, use_graph, with_cublas, dev):
+    """Config 4 followed by the log-softmax over the vocabulary (one shard = the whole of it)."""
+    from . import shard
+    rows, hidden, vocab = 256, 512, 65536
+    g = torch.Generator(device=dev)
+    g.manual_seed(1004)
+    ring = 3
+    sets = [(torch.randn(rows, hidden, device=dev, generator=g).half(),
+             (torch.randn(vocab, hidden, device=dev, generator=g) * 0.02).half()) for _ in range(ring)]
+
+    def ours(i):
+        h, w = sets[i % ring]
+        shard.vocab_parallel_output(h, w)
+
+    def cublas(i):
+        h, w = sets[i % ring]
+        torch.log_softmax(torch.matmul(h, w.t()).float(), dim=-1).half()
+
+    us = time_calls(ours, ring * max(1, iters // ring), use_graph)
+    flops = 2.0 * rows * hidden * vocab
+    nbytes = 2.0 * (rows * hidden + vocab * hidden + 3 * rows * vocab)     # logits written, read twice, written once more... see note
+    peak_tf, peak_gb, src = peaks()
+    line = {"config": "4lsm", "what": "output layer + LogSoftmax over the vocabulary (3 kernels)", "dtype": "f16",
+            "M": rows, "N": vocab, "K": hidden, "us_per_call": us, "tflops": flops / us / 1e6,
+            "algorithmic_mb": 2.0 * (rows * hidden + vocab * hidden + rows * vocab) / 1e6,
+            "moved_mb_by_three_kernels": nbytes / 1e6, "bound": "hbm", "peaks": src,
+            "frac_of_hbm_peak": 2.0 * (rows * hidden + vocab * hidden + rows * vocab) / us / 1e3 / peak_gb,
+            "timing": "cuda graph replay" if use_graph else "back-to-back calls"}
+    if with_cublas:
+        line["torch_matmul_log_softmax_us"] = time_calls(cublas, ring * max(1, iters // ring), use_graph)
+    return line
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--configs", default="1,2a,2b,3a,3b,3fused,4,5,5f32")
+    ap.add_argument("--configs", default="1,2a,2b,3a,3b,3fused,4,4lsm,5,5f32")
     ap.add_argument("--iters", type=int, default=60)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--cublas", action="store_true")
@@ -201,6 +234,9 @@ def main():
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     for name in args.configs.split(","):
+        if name == "4lsm":
+            print(json.dumps(run_output_layer(args.iters, not args.no_graph, args.cublas, dev)), flush=True)
+            continue
         if name == "3fused":
             print(json.dumps(run_attention(args.iters, not args.no_graph, args.cublas, dev)), flush=True)
             continue

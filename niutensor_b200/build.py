@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libntb_gemm.so")
-SOURCES = ["ntb_api.cu", "ntb_tc.cu", "ntb_simt.cu", "ntb_noalloc.cu", "ntb_attn.cu"]
+SOURCES = ["ntb_api.cu", "ntb_tc.cu", "ntb_simt.cu", "ntb_noalloc.cu", "ntb_attn.cu", "ntb_logsoftmax.cu"]
 HEADERS = [os.path.join(CSRC, "ntb_internal.h"), os.path.join(CSRC, "ntb_ptx.cuh"),
            os.path.join(os.path.dirname(HERE), "include", "ntb_gemm.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

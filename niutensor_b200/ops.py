@@ -212,3 +212,34 @@ def ScaledDotProductAttention(q, k, v, mask=None, scale=None):
                                   out.data_ptr(), X_FLOAT16, blocks, lenQ, lenK, d, stride, scale)
     _raise_rc(rc, "ScaledDotProductAttention")
     return out
+
+
+def RowStats(x):
+    """(row maximum, sum of exp(x - maximum)) over the last dimension of a 2-D tensor, fp32."""
+    _check(x.is_cuda and x.dim() == 2 and x.stride(1) == 1, "a CUDA matrix with unit column stride is required")
+    rows, cols = x.shape
+    mx = torch.empty(rows, dtype=torch.float32, device=x.device)
+    sm = torch.empty(rows, dtype=torch.float32, device=x.device)
+    rc = capi.lib().ntb_row_stats(x.device.index, _stream(x), x.data_ptr(), _dtype_code(x), rows, cols, x.stride(0),
+                                  mx.data_ptr(), sm.data_ptr())
+    _raise_rc(rc, "RowStats")
+    return mx, sm
+
+
+def LogSoftmaxApply(x, row_max, row_sum, out=None):
+    """log(exp(x - row_max) / row_sum) with the reference's floor of -20 (LogSoftmax.cpp:133-148)."""
+    _check(x.is_cuda and x.dim() == 2 and x.stride(1) == 1, "a CUDA matrix with unit column stride is required")
+    y = x if out is None else out
+    rows, cols = x.shape
+    rc = capi.lib().ntb_logsoftmax_apply(x.device.index, _stream(x), x.data_ptr(), y.data_ptr(), _dtype_code(x),
+                                         rows, cols, x.stride(0), y.stride(0), row_max.data_ptr(), row_sum.data_ptr())
+    _raise_rc(rc, "LogSoftmaxApply")
+    return y
+
+
+def LogSoftmax(x):
+    """Log-softmax over the last dimension (source/tensor/function/LogSoftmax.cpp:40), in place
+    on a copy: leading dimensions fold into rows."""
+    x2 = x.reshape(-1, x.shape[-1]).clone()
+    mx, sm = RowStats(x2)
+    return LogSoftmaxApply(x2, mx, sm).view(x.shape)

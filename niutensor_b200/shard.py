@@ -85,3 +85,24 @@ def gather_batch(c_local, count, group=None):
     pieces = [torch.empty_like(piece) for _ in range(world)]
     dist.all_gather(pieces, piece, group=group)
     return torch.cat([pieces[r][:hi - lo] for r, (lo, hi) in enumerate(sizes)], dim=0)
+
+
+def vocab_parallel_output(h, w_local, group=None, normalized=True):
+    """The output layer with the vocabulary matrix sharded by rows across the group
+    (source/sample/transformer/submodel/Output.cpp:86-101: MMul(h, w^T), then LogSoftmax
+    over the vocabulary for beam search). Every rank holds all of h [rows, hidden] and its
+    rows of w [vocab / world, hidden]; it returns its columns of the log-probabilities.
+    The logits are never gathered: the ranks exchange one maximum and one sum per row."""
+    from . import ops
+    logits = ops.MatrixMul(h.reshape(-1, h.shape[-1]), X_NOTRANS, w_local, X_TRANS)
+    if not normalized:
+        return logits
+    mx, sm = ops.RowStats(logits)
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        gmx = mx.clone()
+        dist.all_reduce(gmx, op=dist.ReduceOp.MAX, group=group)
+        # a shard whose row is entirely -inf contributes nothing
+        sm = torch.where(torch.isinf(mx) & (mx < 0), torch.zeros_like(sm), sm * torch.exp(mx - gmx))
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM, group=group)
+        mx = gmx
+    return ops.LogSoftmaxApply(logits, mx, sm)

@@ -279,3 +279,41 @@ void orc_attention_f32(const float * q, const float * k, const float * v, const 
     free(qs);
     free(att);
 }
+
+/*
+ * LogSoftmax over the last dimension as the reference's CPU path computes it
+ * (source/tensor/function/LogSoftmax.cpp:87-88, 123-148): row maximum, row sum of
+ * exp(x - max), then r = log(exp(x - max) / sum); NaN and infinities become LOGPROB_MIN
+ * (-20, source/tensor/XGlobal.h:69) and r is floored at LOGPROB_MIN; a row whose sum is 0
+ * becomes zeros; a dimension of size 1 gives zeros (:50-53). The row sum is accumulated
+ * left to right here (the reference sums in vector lanes): agreement to rounding error.
+ */
+void orc_logsoftmax_f32(const float * x, float * y, int rows, int cols)
+{
+    int i, j;
+    for (i = 0; i < rows; i++) {
+        const float * ip = x + (size_t)i * cols;
+        float * op = y + (size_t)i * cols;
+        float mx = ip[0], sum = 0;
+        if (cols == 1) {
+            op[0] = 0;
+            continue;
+        }
+        for (j = 1; j < cols; j++)
+            if (ip[j] > mx)
+                mx = ip[j];
+        for (j = 0; j < cols; j++)
+            sum += (float)exp(ip[j] - mx);
+        for (j = 0; j < cols; j++) {
+            float r = 0;
+            if (sum != 0) {
+                r = (float)log(exp(ip[j] - mx) / sum);
+                if (isnan(r) || isinf(r))
+                    r = -20.0f;
+                if (r < -20.0f)
+                    r = -20.0f;
+            }
+            op[j] = r;
+        }
+    }
+}

@@ -65,6 +65,7 @@ class Oracle:
         self.lib.orc_matmul_broadcast_f32.argtypes = [_F32P, ctypes.c_int, _F32P, ctypes.c_int, _F32P] + \
             [ctypes.c_int] * 8 + [ctypes.c_float] * 2
         self.lib.orc_set_threads.argtypes = [ctypes.c_int]
+        self.lib.orc_logsoftmax_f32.argtypes = [_F32P, _F32P, ctypes.c_int, ctypes.c_int]
         self.lib.orc_attention_f32.argtypes = [_F32P, _F32P, _F32P, _F32P, _F32P] + [ctypes.c_int] * 4 + \
             [ctypes.c_longlong, ctypes.c_float]
         self.lib.orc_mulandshift_f32.argtypes = [_F32P, ctypes.c_int, _F32P, ctypes.c_int, _F32P, _F32P] + \
@@ -97,6 +98,17 @@ class Oracle:
         self.lib.orc_mulandshift_f32(_fp(x2), tX, _fp(w), tW, _fp(b), _fp(c), x2.shape[0], x2.shape[1],
                                      w.shape[0], w.shape[1], M, N, alpha, 1 if rectify else 0)
         return c.reshape(lead + (M // max(1, int(np.prod(lead, dtype=np.int64))), N)) if lead else c
+
+    def logsoftmax(self, x):
+        """LogSoftmax over the last dimension with the reference's floor of -20."""
+        x = _as_f32(x)
+        y = np.zeros_like(x)
+        self.lib.orc_logsoftmax_f32(_fp(x), _fp(y), int(np.prod(x.shape[:-1], dtype=np.int64)), x.shape[-1])
+        return y
+
+    def output_layer(self, h, w):
+        """log-probabilities of the output layer: LogSoftmax(h w^T), w stored [vocab, hidden]."""
+        return self.logsoftmax(self.matmul2d(_as_f32(h), X_NOTRANS, _as_f32(w), X_TRANS))
 
     def attention(self, q, k, v, mask=None, scale=1.0):
         """softmax(scale * q k^T + mask) v per block; q [blocks, lenQ, d], k, v [blocks, lenK, d],
@@ -243,6 +255,19 @@ def ref_attention(ref, q, k, v, mask=None, scale=1.0):
     rc = ref.lib.ref_attention_f32(_fp(q), _fp(k), _fp(v), mp, _fp(out), blocks, lenQ, lenK, d, scale)
     if rc != 0:
         raise RuntimeError("ref_attention_f32 failed")
+    return out
+
+
+def ref_output_layer(ref, h, w):
+    """The reference's CPU MMul + LogSoftmax of the normalised output layer."""
+    h, w = _as_f32(h), _as_f32(w)
+    rows, hidden = h.shape
+    vocab = w.shape[0]
+    out = np.zeros((rows, vocab), np.float32)
+    ref.lib.ref_output_layer_f32.argtypes = [_F32P, _F32P, _F32P, _F32P, ctypes.c_int, ctypes.c_int, ctypes.c_int]
+    rc = ref.lib.ref_output_layer_f32(_fp(h), _fp(w), None, _fp(out), rows, hidden, vocab)
+    if rc != 0:
+        raise RuntimeError("ref_output_layer_f32 failed")
     return out
 
 

@@ -20,6 +20,7 @@
 #include "tensor/core/arithmetic/Sum.h"
 #include "tensor/core/math/ScaleAndShift.h"
 #include "tensor/function/Softmax.h"
+#include "tensor/function/LogSoftmax.h"
 #ifdef USE_BLAS
 #include "tensor/XBLAS.h"
 #endif
@@ -126,6 +127,28 @@ int ref_attention_f32(const float * q, const float * k, const float * v, const f
     Drop(tk);
     Drop(tv);
     Drop(to);
+    return 0;
+}
+
+/* The normalised output layer of source/sample/transformer/submodel/Output.cpp:86-101 with
+   the reference's CPU operators: logits = h * w^T (w stored [vocab, hidden]), then
+   LogSoftmax over the vocabulary. logits may be NULL. */
+int ref_output_layer_f32(const float * h, const float * w, float * logits, float * logprob,
+                         int rows, int hidden, int vocab)
+{
+    int dh[2] = { rows, hidden }, dw[2] = { vocab, hidden }, dy[2] = { rows, vocab };
+    XTensor * th = View((float*)h, 2, dh);
+    XTensor * tw = View((float*)w, 2, dw);
+    XTensor * ty = View(logprob, 2, dy);
+    XTensor tmp;
+    InitTensorV2(&tmp, 2, dy, X_FLOAT, 1.0F, -1);
+    _MatrixMul(th, X_NOTRANS, tw, X_TRANS, &tmp);
+    if (logits != NULL)
+        memcpy(logits, tmp.data, sizeof(float) * (size_t)tmp.unitNum);
+    _LogSoftmax(&tmp, ty, 1);
+    Drop(th);
+    Drop(tw);
+    Drop(ty);
     return 0;
 }
 

@@ -87,3 +87,15 @@ def attention_cases():
             mask[:, :, 0] = 0.0
         out.append((q, k, v, mask, 0.125))
     return out
+
+
+def output_layer_cases():
+    """(h, w): hidden states and a [vocab, hidden] matrix; the third case has logits spread
+    wide enough for the -20 floor of the reference's LogSoftmax to act."""
+    rng = np.random.default_rng(20243)
+    out = []
+    for (rows, hidden, vocab, wscale) in [(5, 16, 7, 0.5), (33, 64, 1000, 0.02), (16, 32, 300, 3.0), (3, 8, 1, 1.0)]:
+        h = rng.normal(size=(rows, hidden)).astype(np.float32)
+        w = (rng.normal(size=(vocab, hidden)) * wscale).astype(np.float32)
+        out.append((h, w))
+    return out

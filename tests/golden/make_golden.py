@@ -21,6 +21,9 @@ without either.
                    attention (scale, BMMul, Sum(mask), Softmax, BMMul) on the seeded inputs
                    of tests/golden/cases.py::attention_cases.
 
+  ref_output_layer.npz  outputs of the reference's CPU MMul(h, w^T) + LogSoftmax on
+                   tests/golden/cases.py::output_layer_cases.
+
 Usage: python tests/golden/make_golden.py
 """
 import json
@@ -35,8 +38,8 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 REF = os.environ.get("REF", "/root/reference")
 
-from oracle.oracle import Reference, ref_mulandshift, ref_attention, X_TRANS, X_NOTRANS  # noqa: E402
-from tests.golden.cases import seeded_cases, mulandshift_cases, attention_cases  # noqa: E402
+from oracle.oracle import Reference, ref_mulandshift, ref_attention, ref_output_layer, X_TRANS, X_NOTRANS  # noqa: E402
+from tests.golden.cases import seeded_cases, mulandshift_cases, attention_cases, output_layer_cases  # noqa: E402
 
 TEST_FILES = ["TMatrixMul.cpp", "TMatrixMul2D.cpp", "TMatrixMul2DParallel.cpp",
               "TMatrixMulBatched.cpp"]
@@ -103,6 +106,12 @@ def main():
         arrays["o%d" % i] = ref_attention(ref, q, k, v, mask, scale)
     np.savez_compressed(os.path.join(HERE, "ref_attention.npz"), **arrays)
     print("ref_attention.npz: %d cases" % len(arrays))
+
+    arrays = {}
+    for i, (h, w) in enumerate(output_layer_cases()):
+        arrays["y%d" % i] = ref_output_layer(ref, h, w)
+    np.savez_compressed(os.path.join(HERE, "ref_output_layer.npz"), **arrays)
+    print("ref_output_layer.npz: %d cases" % len(arrays))
 
 
 if __name__ == "__main__":

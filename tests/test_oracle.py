@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 
 from oracle.oracle import (Oracle, Reference, ref_available, rel_fro, X_TRANS, X_NOTRANS)
-from tests.golden.cases import (seeded_cases, mulandshift_cases, attention_cases, FORM_GENERAL, FORM_BATCHED,
+from tests.golden.cases import (seeded_cases, mulandshift_cases, attention_cases, output_layer_cases, FORM_GENERAL, FORM_BATCHED,
                                 FORM_2D)
 
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
@@ -85,6 +85,19 @@ def test_attention_oracle_matches_stored_reference_outputs(oracle):
         got = oracle.attention(q, k, v, mask, scale)
         assert got.shape == z["o%d" % i].shape
         assert rel_fro(got, z["o%d" % i]) <= 1e-6, i
+
+
+def test_output_layer_oracle_matches_stored_reference_outputs(oracle):
+    z = np.load(os.path.join(GOLD, "ref_output_layer.npz"))
+    cases = output_layer_cases()
+    assert len(cases) == len(z.files) == 4
+    for i, (h, w) in enumerate(cases):
+        got = oracle.output_layer(h, w)
+        want = z["y%d" % i]
+        assert got.shape == want.shape
+        assert rel_fro(got, want) <= 1e-6, i
+        assert got.min() >= -20.0
+    assert (z["y2"] == -20.0).any(), "the floor case must reach the floor"
 
 
 def test_thread_count_does_not_change_bits():
