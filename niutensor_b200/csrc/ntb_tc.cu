@@ -9,12 +9,16 @@
  *               instructions of a stage and commits them to empty[s]; after the last
  *               k-block of a tile it commits to tfull[buf].
  *   warps 2-5   epilogue: tcgen05.ld of the finished accumulator (each warp reads the 32
- *               TMEM lanes of its sub-partition), alpha/beta, cast, stores to C, then
- *               release of the accumulator through tempty[buf]. Two accumulators
- *               alternate, so the epilogue of tile i overlaps the main loop of tile i+1.
+ *               TMEM lanes of its sub-partition), alpha / beta / bias / rectifier in
+ *               fp32, cast, staging in swizzled shared memory and TMA stores to C (direct
+ *               stores when C is not 16-byte aligned), then release of the accumulator
+ *               through tempty[buf]. Two accumulators alternate, so the epilogue of tile
+ *               i overlaps the main loop of tile i+1.
  *   warps 6-9   (fp32 inputs only) split every fp32 operand value x in shared memory
  *               into hi = tf32(x) and lo = x - hi; the MMA lane then issues three
  *               kind::tf32 products per k-step, lo*hi + hi*lo + hi*hi, small terms first.
+ *               K is cut into chains of 256; the epilogue warps add the chains' partial
+ *               sums into a running sum held in a third TMEM region.
  *
  * One CTA per SM walks output tiles tile = blockIdx.x + i * gridDim.x over
  * (problem, mBlock, nBlock); all problems of a batched / broadcast call are covered by
