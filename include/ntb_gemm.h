@@ -143,6 +143,30 @@ int ntb_logsoftmax_apply(int devID, void * stream, const void * x, void * y, int
                          const float * rowMax, const float * rowSumExp);
 
 /*
+ * Both gradient products of c = alpha * op(a) * op(b) in one launch:
+ *
+ *        deda += alpha * (...),   dedb += alpha * (...)        (beta = 1, accumulating)
+ *
+ * with the operand order and transposition flags of the reference's backward pass
+ * (source/network/XBackwardMath.cpp:655-699 for MatrixMul, :714-786 for MatrixMulBatched):
+ *   N/N: deda += dedc * b^T,    dedb += a^T * dedc
+ *   T/N: deda += b * dedc^T,    dedb += a * dedc
+ *   N/T: deda += dedc * b,      dedb += dedc^T * a
+ *   T/T: deda += b^T * dedc^T,  dedb += dedc^T * a^T
+ * a: na x ma, b: nb x mb (stored), dedc: the shape of c; deda, dedb: the shapes of a, b; all
+ * packed, `count` matrices back to back (count = 1 for the 2-D form). Either gradient
+ * pointer may be NULL (that product is skipped, the reference's isEfficient case). The
+ * reference issues two GEMMs; here the tiles of both products are walked by one persistent
+ * kernel, so the second product starts while the first one's last tiles finish and dedc is
+ * read once into L2 for both. Operands the tensor-core route cannot address fall back to
+ * two launches.
+ */
+int ntb_gemm_grad(int devID, void * stream,
+                  const void * a, int transA, const void * b, int transB, const void * dedc,
+                  void * deda, void * dedb, int dtype,
+                  int na, int ma, int nb, int mb, int count, float alpha);
+
+/*
  * `count` GEMMs of one shape whose matrices lie at constant element strides; a stride
  * of 0 reuses one matrix for every problem. One launch covers all problems.
  * Replaces _CudaBLASMatrixMULBatchedStrided

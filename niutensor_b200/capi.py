@@ -28,6 +28,7 @@ PROTOTYPES = {
     "ntb_attention": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _ll, _f]),
     "ntb_row_stats": (_i, [_i, _vp, _vp, _i, _i, _i, _ll, _vp, _vp]),
     "ntb_logsoftmax_apply": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _vp, _vp]),
+    "ntb_gemm_grad": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f]),
     "ntb_gemm_strided_batched": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _i, _i] + [_i] * 6 + [_ll] * 6 + [_i, _f, _f]),
     "ntb_gemm_broadcast": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _i, _i] + [_i] * 6 + [_i, _i, _f, _f]),
     "ntb_gemm_list": (_i, [_i, _vp, ctypes.POINTER(_vp), _i, ctypes.POINTER(_vp), _i, ctypes.POINTER(_vp),

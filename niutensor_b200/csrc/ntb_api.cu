@@ -260,6 +260,97 @@ int ntb_gemm_bias_act(int devID, void * stream,
     return Dispatch(devID, (cudaStream_t)stream, p);
 }
 
+namespace {
+
+/* one packed, batched product out (+)= alpha * op(x) * op(y) + beta * out as a Problem */
+int FillPacked(Problem & p, const void * x, int tX, int xr, int xc, const void * y, int tY, int yr, int yc,
+               void * out, int outr, int outc, int dtype, int count, float alpha, float beta)
+{
+    memset(&p, 0, sizeof(p));
+    int rc = SetShape(p, tX, tY, xr, xc, yr, yc, outr, outc);
+    if (rc != NTB_OK)
+        return rc;
+    p.a = x; p.b = y; p.c = out;
+    p.dtAB = dtype; p.dtC = dtype;
+    p.lda = xc; p.ldb = yc; p.ldc = outc;
+    p.count = count; p.Q = 1;
+    p.sAp = (long long)xr * xc; p.sBp = (long long)yr * yc; p.sCp = (long long)outr * outc;
+    p.alpha = alpha; p.beta = beta;
+    return NTB_OK;
+}
+
+}
+
+int ntb_gemm_grad(int devID, void * stream,
+                  const void * a, int transA, const void * b, int transB, const void * dedc,
+                  void * deda, void * dedb, int dtype,
+                  int na, int ma, int nb, int mb, int count, float alpha)
+{
+    if ((transA != NTB_X_TRANS && transA != NTB_X_NOTRANS) || (transB != NTB_X_TRANS && transB != NTB_X_NOTRANS))
+        return NTB_ERR_ARG;
+    if (na < 0 || ma < 0 || nb < 0 || mb < 0 || count < 0)
+        return NTB_ERR_ARG;
+    int rc = CheckDtypes(dtype, dtype);
+    if (rc != NTB_OK)
+        return rc;
+    const bool tA = transA == NTB_X_TRANS, tB = transB == NTB_X_TRANS;
+    const int an = tA ? ma : na, am = tA ? na : ma;
+    const int bn = tB ? mb : nb, bm = tB ? nb : mb;
+    if (am != bn)
+        return NTB_ERR_SHAPE;
+    const int cn = an, cm = bm;                       /* dedc is cn x cm */
+    if (count == 0 || (!deda && !dedb))
+        return NTB_OK;
+    if (!a || !b || !dedc)
+        return NTB_ERR_ARG;
+    const int T = NTB_X_TRANS, N = NTB_X_NOTRANS;
+    Problem pa, pb;
+    int ra = NTB_OK, rb = NTB_OK;
+    if (!tA && !tB) {
+        ra = FillPacked(pa, dedc, N, cn, cm, b, T, nb, mb, deda, na, ma, dtype, count, alpha, 1.f);
+        rb = FillPacked(pb, a, T, na, ma, dedc, N, cn, cm, dedb, nb, mb, dtype, count, alpha, 1.f);
+    }
+    else if (tA && !tB) {
+        ra = FillPacked(pa, b, N, nb, mb, dedc, T, cn, cm, deda, na, ma, dtype, count, alpha, 1.f);
+        rb = FillPacked(pb, a, N, na, ma, dedc, N, cn, cm, dedb, nb, mb, dtype, count, alpha, 1.f);
+    }
+    else if (!tA && tB) {
+        ra = FillPacked(pa, dedc, N, cn, cm, b, N, nb, mb, deda, na, ma, dtype, count, alpha, 1.f);
+        rb = FillPacked(pb, dedc, T, cn, cm, a, N, na, ma, dedb, nb, mb, dtype, count, alpha, 1.f);
+    }
+    else {
+        ra = FillPacked(pa, b, T, nb, mb, dedc, T, cn, cm, deda, na, ma, dtype, count, alpha, 1.f);
+        rb = FillPacked(pb, dedc, T, cn, cm, a, T, na, ma, dedb, nb, mb, dtype, count, alpha, 1.f);
+    }
+    if (ra != NTB_OK)
+        return ra;
+    if (rb != NTB_OK)
+        return rb;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!deda)
+        return Dispatch(devID, st, pb);
+    if (!dedb)
+        return Dispatch(devID, st, pa);
+    const int forced = ForcedRoute();
+    const bool empty = pa.M == 0 || pa.N == 0 || pb.M == 0 || pb.N == 0;
+    if (!empty && forced != NTB_ROUTE_SIMT && TcEligible(pa) && TcEligible(pb)) {
+        DeviceGuard guard(devID);
+        if (!guard.ok) {
+            cudaGetLastError();
+            return NTB_ERR_CUDA;
+        }
+        DeviceCtx * ctx = GetCtx(devID);
+        if (!ctx)
+            return NTB_ERR_CUDA;
+        rc = LaunchTcTwo(*ctx, pa, pb, st);
+        if (rc == NTB_OK)
+            tLastRoute = dtype == NTB_X_FLOAT16 ? NTB_ROUTE_TC_F16 : NTB_ROUTE_TC_3XTF32;
+        return rc;
+    }
+    rc = Dispatch(devID, st, pa);
+    return rc != NTB_OK ? rc : Dispatch(devID, st, pb);
+}
+
 int ntb_gemm(int devID, void * stream,
              const void * a, int transA, const void * b, int transB, void * c,
              int dtypeAB, int dtypeC,

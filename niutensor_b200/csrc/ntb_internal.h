@@ -54,6 +54,8 @@ bool TcEligible(const Problem & p);
 /* *route receives the NTB_ROUTE_* code of the kernel launched */
 int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int * route);
 int LaunchSimt(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream);
+/* two tensor-core-eligible problems of equal operand and output types in one launch */
+int LaunchTcTwo(const DeviceCtx & ctx, const Problem & p0, const Problem & p1, cudaStream_t stream);
 
 /* the device's context (created on first use); the caller has made `dev` current */
 DeviceCtx * CtxFor(int dev);

@@ -358,10 +358,31 @@ __device__ __forceinline__ int BatchCoord(int sel, int prob, const TcParams & p)
 
 /* ---------------------------------------------------------------- the kernel */
 
+/* Up to two problems of different shapes in one launch (the two gradient products of a
+   matrix multiplication): tiles [0, split) belong to problem 0, the rest to problem 1. */
+struct TcGroup {
+    CUtensorMap tm[2][3];      /* A, B, C maps of each problem */
+    TcParams p[2];
+    int n, split, total;
+};
+
+/* per-tile view of the problem a tile belongs to; names match the single-problem code */
+#define NTB_SELECT_PROBLEM() \
+    const int gi = t >= grp.split ? 1 : 0; \
+    const TcParams & p = grp.p[gi]; \
+    const CUtensorMap & tmA = grp.tm[gi][0]; \
+    const CUtensorMap & tmB = grp.tm[gi][1]; \
+    const CUtensorMap & tmC = grp.tm[gi][2]; \
+    (void)tmA; (void)tmB; (void)tmC; \
+    const int tl = t - gi * grp.split; \
+    const int kBlocks = (p.K + EPR - 1) / EPR; \
+    /* k-blocks accumulated in TMEM before the partial sum is handed to the epilogue */ \
+    const int chunkBlocks = MODE == 0 ? kBlocks : FP32_CHUNK_BLOCKS; \
+    (void)chunkBlocks
+
 template <int MODE, int BN, int STAGES, typename OutT>
 __global__ void __launch_bounds__(MODE == 0 ? 192 : 192 + CONV_THREADS, 1)
-GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-             const __grid_constant__ CUtensorMap tmC, TcParams p)
+GemmTcKernel(const __grid_constant__ TcGroup grp)
 {
     constexpr int ES = MODE == 0 ? 2 : 4;               /* operand element size */
     constexpr int EPR = ROW_BYTES / ES;                 /* elements per 128-byte row = K per stage */
@@ -397,11 +418,15 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     if (threadIdx.x == 64) {
         /* an idle epilogue lane pulls the kernel parameters and the tensor maps towards the SM
            while the other warps set up, so the producer's first use of them does not stall */
-        PrefetchTensorMap(&tmA);
-        PrefetchTensorMap(&tmB);
-        if (p.cTma)
-            PrefetchTensorMap(&tmC);
-        int touch = p.totalTiles + p.tilesM + p.tilesN + p.K + p.Q + p.group + p.aSel + p.bSel + p.aMN + p.bMN;
+        int touch = grp.total + grp.split;
+        for (int gi = 0; gi < grp.n; gi++) {
+            const TcParams & p = grp.p[gi];
+            PrefetchTensorMap(&grp.tm[gi][0]);
+            PrefetchTensorMap(&grp.tm[gi][1]);
+            if (p.cTma)
+                PrefetchTensorMap(&grp.tm[gi][2]);
+            touch += p.tilesM + p.tilesN + p.K + p.Q + p.group + p.aSel + p.bSel + p.aMN + p.bMN;
+        }
         asm volatile("" :: "r"(touch));
     }
     if (threadIdx.x == 0) {
@@ -446,9 +471,6 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     long long wstat[4] = {0, 0, 0, 0};
 #endif
     if (threadIdx.x == 0) NTB_MARK(0);
-    const int kBlocks = (p.K + EPR - 1) / EPR;
-    /* k-blocks accumulated in TMEM before the partial sum is handed to the epilogue */
-    const int chunkBlocks = MODE == 0 ? kBlocks : FP32_CHUNK_BLOCKS;
     const int firstTile = blockIdx.x;
     const int tileStep = gridDim.x;
 
@@ -458,8 +480,9 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
-            for (int t = firstTile; ok && t < p.totalTiles; t += tileStep) {
-                TileCoord tc = DecodeTile(t, p);
+            for (int t = firstTile; ok && t < grp.total; t += tileStep) {
+                NTB_SELECT_PROBLEM();
+                TileCoord tc = DecodeTile(tl, p);
                 const int m0 = tc.mBlk * BM, n0 = tc.nBlk * BN;
                 const int ba = BatchCoord(p.aSel, tc.prob, p);
                 const int bb = BatchCoord(p.bSel, tc.prob, p);
@@ -519,24 +542,26 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     else if (warp == 1) {
         /* ------------------------------------------------------------ MMA issuer */
         if (lane == 0) {
-            const uint32_t iDesc = InstrDesc(MODE, p.aMN, p.bMN, BN);
-            /* K-major: rows of 128 B, 8-row groups 1024 B apart, k-step = 32 B along the row.
-               MN-major: boxes of EPR k-rows x 128 B; 64- (or 32-) element MN chunks are
-               EPR*128 B apart (leading offset), 8-k-row groups 1024 B apart (stride offset),
-               k-step = UMMA_K k-rows. */
-            const uint32_t aLbo = p.aMN ? EPR * ROW_BYTES : 16, bLbo = p.bMN ? EPR * ROW_BYTES : 16;
-            const uint32_t mnStep = (UMMA_K_BYTES / ES) * ROW_BYTES;
-            const uint32_t aStep = p.aMN ? mnStep : UMMA_K_BYTES;
-            const uint32_t bStep = p.bMN ? mnStep : UMMA_K_BYTES;
-            /* MN-major fp32 tiles are loaded with the 32-byte-chunk swizzle, whose pattern
-               repeats every 4 k-rows (512 B) instead of every 8 */
-            const uint32_t aLay = (MODE != 0 && p.aMN) ? 1u : 2u, bLay = (MODE != 0 && p.bMN) ? 1u : 2u;
-            const uint32_t aSbo = (MODE != 0 && p.aMN) ? 512u : 1024u, bSbo = (MODE != 0 && p.bMN) ? 512u : 1024u;
             int s = 0;
             uint32_t ph = 0;
             uint32_t it = 0;                      /* accumulator hand-overs so far */
             bool ok = true;
-            for (int t = firstTile; ok && t < p.totalTiles; t += tileStep) {
+            for (int t = firstTile; ok && t < grp.total; t += tileStep) {
+                NTB_SELECT_PROBLEM();
+                (void)tl;
+                const uint32_t iDesc = InstrDesc(MODE, p.aMN, p.bMN, BN);
+                /* K-major: rows of 128 B, 8-row groups 1024 B apart, k-step = 32 B along the row.
+                   MN-major: boxes of EPR k-rows x 128 B; 64- (or 32-) element MN chunks are
+                   EPR*128 B apart (leading offset), 8-k-row groups 1024 B apart (stride offset),
+                   k-step = UMMA_K k-rows. */
+                const uint32_t aLbo = p.aMN ? EPR * ROW_BYTES : 16, bLbo = p.bMN ? EPR * ROW_BYTES : 16;
+                const uint32_t mnStep = (UMMA_K_BYTES / ES) * ROW_BYTES;
+                const uint32_t aStep = p.aMN ? mnStep : UMMA_K_BYTES;
+                const uint32_t bStep = p.bMN ? mnStep : UMMA_K_BYTES;
+                /* MN-major fp32 tiles are loaded with the 32-byte-chunk swizzle, whose pattern
+                   repeats every 4 k-rows (512 B) instead of every 8 */
+                const uint32_t aLay = (MODE != 0 && p.aMN) ? 1u : 2u, bLay = (MODE != 0 && p.bMN) ? 1u : 2u;
+                const uint32_t aSbo = (MODE != 0 && p.aMN) ? 512u : 1024u, bSbo = (MODE != 0 && p.bMN) ? 512u : 1024u;
                 for (int kb0 = 0; ok && kb0 < kBlocks; kb0 += chunkBlocks, ++it) {
                     const uint32_t buf = it & 1u;
                     NTB_TIMED(2, ok = MbarWait(SmemAddr(&barTEmpty[buf]), ((it >> 1) & 1u) ^ 1u, abortPtr, p.status));
@@ -585,9 +610,11 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         uint32_t it = 0;
         bool ok = true;
         TileWriter<OutT> writer;
-        writer.Init(smemBase + STAGES * STAGE_BYTES, sub, &tmC);
-        for (int t = firstTile; ok && t < p.totalTiles; t += tileStep) {
-            TileCoord tc = DecodeTile(t, p);
+        writer.Init(smemBase + STAGES * STAGE_BYTES, sub, nullptr);
+        for (int t = firstTile; ok && t < grp.total; t += tileStep) {
+            NTB_SELECT_PROBLEM();
+            writer.map = &tmC;
+            TileCoord tc = DecodeTile(tl, p);
             const int row0 = tc.mBlk * BM + sub * 32;
             const int row = row0 + lane;
             const int n0 = tc.nBlk * BN;
@@ -675,7 +702,9 @@ GemmTcKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         int s = 0;
         uint32_t ph = 0;
         bool ok = true;
-        for (int t = firstTile; ok && t < p.totalTiles; t += tileStep) {
+        for (int t = firstTile; ok && t < grp.total; t += tileStep) {
+            NTB_SELECT_PROBLEM();
+            (void)tl;
             for (int kb = 0; kb < kBlocks; kb++) {
                 ok = MbarWait(SmemAddr(&barFull[s]), ph, abortPtr, p.status);
                 if (!ok)
@@ -1043,11 +1072,8 @@ bool BatchSelector(long long sp, long long sq, int P, int Q, int * sel, long lon
 }
 
 template <int MODE, int BN, int STAGES, typename OutT>
-int LaunchOne(const CUtensorMap & tmA, const CUtensorMap & tmB, const CUtensorMap & tmC, const TcParams & tp, int grid,
-              cudaStream_t stream)
+int LaunchOne(const TcGroup & grp, int smCount, cudaStream_t stream)
 {
-    constexpr int ES = MODE == 0 ? 2 : 4;
-    (void)ES;
     constexpr int stage = (A_TILE_BYTES + BN * ROW_BYTES) * (MODE == 0 ? 1 : 2);
     constexpr int smem = stage * STAGES + EPI_BYTES + 1024;
     auto kern = GemmTcKernel<MODE, BN, STAGES, OutT>;
@@ -1059,9 +1085,26 @@ int LaunchOne(const CUtensorMap & tmA, const CUtensorMap & tmB, const CUtensorMa
             return NTB_ERR_CUDA;
         configured[dev] = true;
     }
-    kern<<<grid, MODE == 0 ? 192 : 192 + CONV_THREADS, smem, stream>>>(tmA, tmB, tmC, tp);
+    const int grid = grp.total < smCount ? grp.total : smCount;
+    kern<<<grid, MODE == 0 ? 192 : 192 + CONV_THREADS, smem, stream>>>(grp);
     CountLaunch();
     return cudaGetLastError() == cudaSuccess ? NTB_OK : NTB_ERR_CUDA;
+}
+
+/* single-CTA kernel for a group, chosen by operand mode, tile width and output type */
+int LaunchGroup(const TcGroup & grp, int mode, int bn, int dtC, int smCount, cudaStream_t stream)
+{
+    if (mode == 0) {
+        const bool half = dtC == NTB_X_FLOAT16;
+        if (bn == 256)
+            return half ? LaunchOne<0, 256, 4, __half>(grp, smCount, stream) : LaunchOne<0, 256, 4, float>(grp, smCount, stream);
+        if (bn == 128)
+            return half ? LaunchOne<0, 128, 6, __half>(grp, smCount, stream) : LaunchOne<0, 128, 6, float>(grp, smCount, stream);
+        return half ? LaunchOne<0, 64, 8, __half>(grp, smCount, stream) : LaunchOne<0, 64, 8, float>(grp, smCount, stream);
+    }
+    if (bn == 128)
+        return LaunchOne<1, 128, 3, float>(grp, smCount, stream);
+    return LaunchOne<1, 64, 4, float>(grp, smCount, stream);
 }
 
 template <int MSUB, int STAGES, typename OutT>
@@ -1204,33 +1247,21 @@ bool TcEligible(const Problem & p)
     return true;
 }
 
-int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int * route)
-{
-    const int mode = p.dtAB == NTB_X_FLOAT16 ? 0 : 1;
-    int bn = PickBN(p, ctx.smCount, mode);
-    const int forced = ForcedRoute();
-    const int knobBN = Knob("NTB_BN", 0);           /* tuning: force the single-CTA tile width */
-    if (knobBN == 64 || knobBN == 128 || (knobBN == 256 && mode == 0))
-        bn = knobBN;
-    if (mode == 0 && forced == NTB_ROUTE_TC_F16_PAIR && ctx.smCount >= 2 && bn > 0)
-        bn = Knob("NTB_PAIR_MSUB", 2) == 1 ? 0 : -1;
-    if (bn <= 0 && forced == NTB_ROUTE_TC_F16)
-        bn = 256;
-    const bool pair = bn <= 0;
-    const int msub = bn == -1 ? 2 : 1;
-    if (pair)
-        bn = 256;
-    *route = mode != 0 ? NTB_ROUTE_TC_3XTF32 : pair ? NTB_ROUTE_TC_F16_PAIR : NTB_ROUTE_TC_F16;
-    const int P = p.count / p.Q;
+namespace {
 
-    TcParams tp;
+/* kernel parameters and tensor maps of one problem for tile width bn (pair: CTA-pair
+   kernel with msub 128-row sub-tiles per CTA) */
+int Prepare(const DeviceCtx & ctx, const Problem & p, int mode, int bn, bool pair, int msub,
+            TcParams & tp, CUtensorMap * maps)
+{
+    const int P = p.count / p.Q;
     tp.c = p.c; tp.ldc = p.ldc; tp.sCp = p.sCp; tp.sCq = p.sCq;
     tp.M = p.M; tp.N = p.N; tp.K = p.K; tp.count = p.count; tp.Q = p.Q;
     tp.aMN = p.aMN; tp.bMN = p.bMN;
     tp.tilesM = pair ? (p.M + 2 * BM * msub - 1) / (2 * BM * msub) : (p.M + BM - 1) / BM;
     tp.tilesN = (p.N + bn - 1) / bn;
     const long long tiles64 = (long long)tp.tilesM * tp.tilesN * p.count;
-    if (tiles64 > 2147483647LL - 1024)
+    if (tiles64 > 1073741823LL)
         return NTB_ERR_LIMIT;
     tp.totalTiles = (int)tiles64;
     tp.alpha = p.alpha; tp.beta = p.beta;
@@ -1255,51 +1286,108 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
     BatchSelector(p.sAp, p.sAq, P, p.Q, &tp.aSel, &stA, &extA);
     BatchSelector(p.sBp, p.sBq, P, p.Q, &tp.bSel, &stB, &extB);
 
-    CUtensorMap tmA, tmB;
-    int rc = EncodeOperand(&tmA, mode, p.a, p.aMN, p.aRows, p.aCols, p.lda, stA, extA, BM);
+    int rc = EncodeOperand(&maps[0], mode, p.a, p.aMN, p.aRows, p.aCols, p.lda, stA, extA, BM);
     if (rc != NTB_OK)
         return rc;
-    rc = EncodeOperand(&tmB, mode, p.b, p.bMN, p.bRows, p.bCols, p.ldb, stB, extB, pair ? 128 : bn);
+    rc = EncodeOperand(&maps[1], mode, p.b, p.bMN, p.bRows, p.bCols, p.ldb, stB, extB, pair ? 128 : bn);
     if (rc != NTB_OK)
         return rc;
 
     /* C through TMA stores when its base, pitch and batch strides are 16-byte aligned and
        its batch offset is one index times one stride; otherwise direct stores */
-    CUtensorMap tmC = tmA;
+    maps[2] = maps[0];
     long long stC = 0;
     int extC = 1;
     tp.cSel = 0;
     tp.cTma = tp.cVec && Knob("NTB_TMA_STORE", 1) != 0 && p.ldc >= p.N &&
               BatchSelector(p.sCp, p.sCq, P, p.Q, &tp.cSel, &stC, &extC) && stC >= 0;
     if (tp.cTma) {
-        rc = EncodeOutput(&tmC, p.dtC, p.c, p.M, p.N, p.ldc, stC, extC);
+        rc = EncodeOutput(&maps[2], p.dtC, p.c, p.M, p.N, p.ldc, stC, extC);
         if (rc != NTB_OK)
             return rc;
     }
+    return NTB_OK;
+}
 
-    const int grid = (int)(tp.totalTiles < ctx.smCount ? tp.totalTiles : ctx.smCount);
+}
+
+int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int * route)
+{
+    const int mode = p.dtAB == NTB_X_FLOAT16 ? 0 : 1;
+    int bn = PickBN(p, ctx.smCount, mode);
+    const int forced = ForcedRoute();
+    const int knobBN = Knob("NTB_BN", 0);           /* tuning: force the single-CTA tile width */
+    if (knobBN == 64 || knobBN == 128 || (knobBN == 256 && mode == 0))
+        bn = knobBN;
+    if (mode == 0 && forced == NTB_ROUTE_TC_F16_PAIR && ctx.smCount >= 2 && bn > 0)
+        bn = Knob("NTB_PAIR_MSUB", 2) == 1 ? 0 : -1;
+    if (bn <= 0 && forced == NTB_ROUTE_TC_F16)
+        bn = 256;
+    const bool pair = bn <= 0;
+    const int msub = bn == -1 ? 2 : 1;
+    if (pair)
+        bn = 256;
+    *route = mode != 0 ? NTB_ROUTE_TC_3XTF32 : pair ? NTB_ROUTE_TC_F16_PAIR : NTB_ROUTE_TC_F16;
+
+    TcGroup grp;
+    grp.n = 1;
+    int rc = Prepare(ctx, p, mode, bn, pair, msub, grp.p[0], grp.tm[0]);
+    if (rc != NTB_OK)
+        return rc;
+    grp.p[1] = grp.p[0];
+    for (int i = 0; i < 3; i++)
+        grp.tm[1][i] = grp.tm[0][i];
+    grp.split = grp.total = grp.p[0].totalTiles;
+
     if (pair) {
+        const TcParams & tp = grp.p[0];
         const int pairs = (int)(tp.totalTiles < ctx.smCount / 2 ? tp.totalTiles : ctx.smCount / 2);
         if (msub == 2)
-            return p.dtC == NTB_X_FLOAT16 ? LaunchPair<2, 4, __half>(tmA, tmB, tmC, tp, pairs, stream)
-                                          : LaunchPair<2, 4, float>(tmA, tmB, tmC, tp, pairs, stream);
-        return p.dtC == NTB_X_FLOAT16 ? LaunchPair<1, 6, __half>(tmA, tmB, tmC, tp, pairs, stream)
-                                      : LaunchPair<1, 6, float>(tmA, tmB, tmC, tp, pairs, stream);
+            return p.dtC == NTB_X_FLOAT16 ? LaunchPair<2, 4, __half>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, pairs, stream)
+                                          : LaunchPair<2, 4, float>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, pairs, stream);
+        return p.dtC == NTB_X_FLOAT16 ? LaunchPair<1, 6, __half>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, pairs, stream)
+                                      : LaunchPair<1, 6, float>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, pairs, stream);
     }
-    if (mode == 0) {
-        const bool half = p.dtC == NTB_X_FLOAT16;
-        if (bn == 256)
-            return half ? LaunchOne<0, 256, 4, __half>(tmA, tmB, tmC, tp, grid, stream)
-                        : LaunchOne<0, 256, 4, float>(tmA, tmB, tmC, tp, grid, stream);
-        if (bn == 128)
-            return half ? LaunchOne<0, 128, 6, __half>(tmA, tmB, tmC, tp, grid, stream)
-                        : LaunchOne<0, 128, 6, float>(tmA, tmB, tmC, tp, grid, stream);
-        return half ? LaunchOne<0, 64, 8, __half>(tmA, tmB, tmC, tp, grid, stream)
-                    : LaunchOne<0, 64, 8, float>(tmA, tmB, tmC, tp, grid, stream);
+    return LaunchGroup(grp, mode, bn, p.dtC, ctx.smCount, stream);
+}
+
+/*
+ * Two problems of the same operand and output types in ONE launch of the single-CTA
+ * kernel: the tile walk covers the tiles of the first, then of the second. Used for the
+ * two gradient products of a matrix multiplication, which share dE/dc. The tile width is
+ * the one the cost model prefers for the two problems taken together.
+ */
+int LaunchTcTwo(const DeviceCtx & ctx, const Problem & p0, const Problem & p1, cudaStream_t stream)
+{
+    const int mode = p0.dtAB == NTB_X_FLOAT16 ? 0 : 1;
+    const int cand[3] = { 256, 128, 64 };
+    int bn = 128;
+    double bestCost = 1e300;
+    for (int i = (mode == 0 ? 0 : 1); i < 3; i++) {
+        const int w = cand[i];
+        const long long t0 = (long long)((p0.M + BM - 1) / BM) * ((p0.N + w - 1) / w) * p0.count;
+        const long long t1 = (long long)((p1.M + BM - 1) / BM) * ((p1.N + w - 1) / w) * p1.count;
+        const long long waves = (t0 + t1 + ctx.smCount - 1) / ctx.smCount;
+        const int kElems = ROW_BYTES / (mode == 0 ? 2 : 4);
+        const double kb = 0.5 * ((p0.K + kElems - 1) / kElems + (p1.K + kElems - 1) / kElems);
+        const double perK = fmax((mode == 0 ? 2.0 : 6.0) * w, (double)(BM + w) * ROW_BYTES / 62.0);
+        const double cost = (double)waves * (kb * perK + 1500.0 + 4.0 * w);
+        if (cost < bestCost) { bestCost = cost; bn = w; }
     }
-    if (bn == 128)
-        return LaunchOne<1, 128, 3, float>(tmA, tmB, tmC, tp, grid, stream);
-    return LaunchOne<1, 64, 4, float>(tmA, tmB, tmC, tp, grid, stream);
+    const int knobBN = Knob("NTB_BN", 0);
+    if (knobBN == 64 || knobBN == 128 || (knobBN == 256 && mode == 0))
+        bn = knobBN;
+    TcGroup grp;
+    grp.n = 2;
+    int rc = Prepare(ctx, p0, mode, bn, false, 1, grp.p[0], grp.tm[0]);
+    if (rc != NTB_OK)
+        return rc;
+    rc = Prepare(ctx, p1, mode, bn, false, 1, grp.p[1], grp.tm[1]);
+    if (rc != NTB_OK)
+        return rc;
+    grp.split = grp.p[0].totalTiles;
+    grp.total = grp.p[0].totalTiles + grp.p[1].totalTiles;
+    return LaunchGroup(grp, mode, bn, p0.dtC, ctx.smCount, stream);
 }
 
 

@@ -243,3 +243,28 @@ def LogSoftmax(x):
     x2 = x.reshape(-1, x.shape[-1]).clone()
     mx, sm = RowStats(x2)
     return LogSoftmaxApply(x2, mx, sm).view(x.shape)
+
+
+def GradMatrixMul(a, transposedA, b, transposedB, dedc, deda, dedb, alpha=1.0):
+    """Backward of c = alpha * op(a) * op(b) (2-D or batched with equal leading extents):
+    deda and dedb are accumulated into (beta = 1) with the operand table of
+    XMathGrad::GradMatrixMul / GradMatrixMulBatched (source/network/XBackwardMath.cpp:655-699,
+    :714-786). Both products run in one launch. Either gradient may be None."""
+    _check(a.is_cuda and b.is_cuda and dedc.is_cuda, "this library has no CPU path: tensors must live on a CUDA device")
+    _check(a.dtype == b.dtype == dedc.dtype, "Input tensors should have the same data type!")
+    _check(a.dim() == b.dim() and a.dim() >= 2 and tuple(a.shape[:-2]) == tuple(b.shape[:-2]), "Incorrect tensor sizes!")
+    for t in (a, b, dedc, deda, dedb):
+        _check(t is None or t.is_contiguous(), "tensors must be dense and packed")
+    _check(deda is None or deda.shape == a.shape, "Incorrect tensor sizes!")
+    _check(dedb is None or dedb.shape == b.shape, "Incorrect tensor sizes!")
+    an = a.shape[-1] if transposedA == X_TRANS else a.shape[-2]
+    bm = b.shape[-2] if transposedB == X_TRANS else b.shape[-1]
+    _check(tuple(dedc.shape) == tuple(a.shape[:-2]) + (an, bm), "Unmatched tensors in multiplication!")
+    count = 1
+    for n in a.shape[:-2]:
+        count *= n
+    rc = capi.lib().ntb_gemm_grad(a.device.index, _stream(a), a.data_ptr(), transposedA, b.data_ptr(), transposedB,
+                                  dedc.data_ptr(), None if deda is None else deda.data_ptr(),
+                                  None if dedb is None else dedb.data_ptr(), _dtype_code(a),
+                                  a.shape[-2], a.shape[-1], b.shape[-2], b.shape[-1], count, alpha)
+    _raise_rc(rc, "GradMatrixMul")

@@ -271,6 +271,21 @@ def ref_output_layer(ref, h, w):
     return out
 
 
+def grad_matmul(oracle, a, tA, b, tB, dedc, deda, dedb, alpha=1.0):
+    """The two accumulating products of XMathGrad::GradMatrixMul / GradMatrixMulBatched
+    (source/network/XBackwardMath.cpp:655-699, :714-786) computed with the oracle's
+    batched matmul (beta = 1). Returns the new (deda, dedb)."""
+    N, T = X_NOTRANS, X_TRANS
+    mm = oracle.matmul_batched
+    if tA == N and tB == N:
+        return mm(dedc, N, b, T, alpha, 1.0, deda), mm(a, T, dedc, N, alpha, 1.0, dedb)
+    if tA == T and tB == N:
+        return mm(b, N, dedc, T, alpha, 1.0, deda), mm(a, N, dedc, N, alpha, 1.0, dedb)
+    if tA == N and tB == T:
+        return mm(dedc, N, b, N, alpha, 1.0, deda), mm(dedc, T, a, N, alpha, 1.0, dedb)
+    return mm(b, T, dedc, T, alpha, 1.0, deda), mm(dedc, T, a, T, alpha, 1.0, dedb)
+
+
 def round_to_half(x):
     """IEEE round-to-nearest-even fp32 -> fp16 -> fp32: the values an X_FLOAT16 tensor
     holds. The reference has no CPU fp16 arithmetic (MatrixMul.cpp:181 "TODO!"), so the
