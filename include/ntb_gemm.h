@@ -158,8 +158,8 @@ int ntb_logsoftmax_apply(int devID, void * stream, const void * x, void * y, int
  * pointer may be NULL (that product is skipped, the reference's isEfficient case). The
  * reference issues two GEMMs; here the tiles of both products are walked by one persistent
  * kernel, so the second product starts while the first one's last tiles finish and dedc is
- * read once into L2 for both. Operands the tensor-core route cannot address fall back to
- * two launches.
+ * read once into L2 for both. Operands the tensor-core route cannot address, and products
+ * large enough for the CTA-pair or split-K kernels, are issued as two launches.
  */
 int ntb_gemm_grad(int devID, void * stream,
                   const void * a, int transA, const void * b, int transB, const void * dedc,

@@ -342,10 +342,14 @@ int ntb_gemm_grad(int devID, void * stream,
         DeviceCtx * ctx = GetCtx(devID);
         if (!ctx)
             return NTB_ERR_CUDA;
-        rc = LaunchTcTwo(*ctx, pa, pb, st);
-        if (rc == NTB_OK)
-            tLastRoute = dtype == NTB_X_FLOAT16 ? NTB_ROUTE_TC_F16 : NTB_ROUTE_TC_3XTF32;
-        return rc;
+        /* one shared launch pays when both products are small enough for the single-CTA
+           kernel; a product that wants CTA pairs or a split of K gets its own launch */
+        if (TcTileChoice(*ctx, pa) > 0 && TcTileChoice(*ctx, pb) > 0) {
+            rc = LaunchTcTwo(*ctx, pa, pb, st);
+            if (rc == NTB_OK)
+                tLastRoute = dtype == NTB_X_FLOAT16 ? NTB_ROUTE_TC_F16 : NTB_ROUTE_TC_3XTF32;
+            return rc;
+        }
     }
     rc = Dispatch(devID, st, pa);
     return rc != NTB_OK ? rc : Dispatch(devID, st, pb);

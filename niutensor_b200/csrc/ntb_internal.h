@@ -54,6 +54,8 @@ bool TcEligible(const Problem & p);
 /* *route receives the NTB_ROUTE_* code of the kernel launched */
 int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int * route);
 int LaunchSimt(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream);
+/* tile choice of the cost model for p alone: > 0 single-CTA width, <= 0 a cluster kernel (pair or split-K) */
+int TcTileChoice(const DeviceCtx & ctx, const Problem & p);
 /* two tensor-core-eligible problems of equal operand and output types in one launch */
 int LaunchTcTwo(const DeviceCtx & ctx, const Problem & p0, const Problem & p1, cudaStream_t stream);
 

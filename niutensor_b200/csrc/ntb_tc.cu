@@ -1059,6 +1059,297 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
 }
 
+/* ---------------------------------------------------------------- the split-K kernel */
+
+/* barrier probe that also acquires what other CTAs of the cluster wrote before arriving */
+__device__ __forceinline__ uint32_t MbarTryWaitCluster(uint32_t bar, uint32_t parity, uint32_t hintNs)
+{
+    uint32_t done;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done) : "r"(bar), "r"(parity), "r"(hintNs) : "memory");
+    return done;
+}
+
+__device__ __forceinline__ bool MbarWaitClusterWarp(uint32_t bar, uint32_t parity, volatile int * abortFlag, int * status)
+{
+    uint32_t ok = 1;
+    if ((threadIdx.x & 31) == 0) {
+        const long long t0 = clock64();
+        for (uint32_t it = 0; ; ++it) {
+            if (MbarTryWaitCluster(bar, parity, 200))
+                break;
+            if ((it & 63u) == 63u) {
+                if (*abortFlag) { ok = 0; break; }
+                if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                    *abortFlag = 1;
+                    atomicExch(status, NTB_ERR_DEVICE_WAIT);
+                    ok = 0;
+                    break;
+                }
+            }
+        }
+    }
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    /* every lane acquires at cluster scope before it reads what the peers wrote */
+    asm volatile("fence.acq_rel.cluster;" ::: "memory");
+    return ok != 0;
+}
+
+/*
+ * fp16 GEMM for products with few output tiles and a long K (weight gradients: K is the
+ * number of tokens): a cluster of S CTAs shares one 128 x 128 output tile, CTA r running the
+ * main loop over the r-th part of the k-blocks with its own TMA pipeline and TMEM
+ * accumulators. The partial sums are combined through distributed shared memory as a
+ * reduce-scatter: CTA d owns columns [d*W, (d+1)*W) of the tile (W = 128 / S); every other
+ * CTA writes its fp32 partial of that slice into CTA d's receive area (st.shared::cluster,
+ * swizzled so that one-row-per-lane writes do not collide) and arrives on CTA d's barrier;
+ * CTA d adds the S - 1 partials to its own in rank order -- a fixed order, so results do not
+ * depend on timing -- and runs the usual epilogue on its slice. No global workspace, no
+ * atomics. The receive area is double-buffered; a sender cannot be two tiles ahead of a
+ * receiver, because its own wait for tile i+1 needs the receiver's partials of tile i+1,
+ * which the receiver's warp sends only after it has consumed tile i.
+ */
+template <int S, int STAGES, typename OutT>
+__global__ void __cluster_dims__(S, 1, 1) __launch_bounds__(192, 1)
+GemmTcSplitKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ CUtensorMap tmC, TcParams p)
+{
+    constexpr int ES = 2;
+    constexpr int EPR = ROW_BYTES / ES;
+    constexpr int BN = 128;
+    constexpr int W = BN / S;                           /* columns of the tile this CTA finishes */
+    constexpr int B_TILE_BYTES = BN * ROW_BYTES;
+    constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+    constexpr int TMEM_COLS = 256;
+    constexpr int KSTEPS = ROW_BYTES / UMMA_K_BYTES;
+    constexpr int SLOT_BYTES = BM * W * 4;              /* one sender's slice: 128 rows x W floats */
+    constexpr int RECV_BYTES = 2 * (S - 1) * SLOT_BYTES;
+    static_assert(S == 2 || S == 4, "cluster size");
+
+    extern __shared__ uint8_t smemRaw[];
+    __shared__ __align__(8) uint64_t barFull[STAGES];
+    __shared__ __align__(8) uint64_t barEmpty[STAGES];
+    __shared__ __align__(8) uint64_t barTFull[2];
+    __shared__ __align__(8) uint64_t barTEmpty[2];
+    __shared__ __align__(8) uint64_t barRecv[2];
+    __shared__ uint32_t tmemBaseSlot;
+    __shared__ int abortFlag;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = ClusterCtaRank();
+    const uint32_t smemBase = (SmemAddr(smemRaw) + 1023u) & ~1023u;
+    const uint32_t recvBase = smemBase + STAGES * STAGE_BYTES;
+    volatile int * abortPtr = &abortFlag;
+
+    if (threadIdx.x == 64) {
+        PrefetchTensorMap(&tmA);
+        PrefetchTensorMap(&tmB);
+        if (p.cTma)
+            PrefetchTensorMap(&tmC);
+    }
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            MbarInit(SmemAddr(&barFull[s]), 1);
+            MbarInit(SmemAddr(&barEmpty[s]), 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            MbarInit(SmemAddr(&barTFull[b]), 1);
+            MbarInit(SmemAddr(&barTEmpty[b]), 4);
+            MbarInit(SmemAddr(&barRecv[b]), (S - 1) * 4);
+        }
+        abortFlag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     :: "r"(SmemAddr(&tmemBaseSlot)), "r"((uint32_t)TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    TcFenceBefore();
+    ClusterSync();              /* every CTA's barriers exist before a peer signals them */
+    TcFenceAfter();
+    const uint32_t tmemBase = *(volatile uint32_t *)&tmemBaseSlot;
+
+    const int kBlocks = (p.K + EPR - 1) / EPR;
+    const int kbLo = (int)((long long)kBlocks * rank / S), kbHi = (int)((long long)kBlocks * (rank + 1) / S);
+    const int firstTile = blockIdx.x / S;
+    const int tileStep = gridDim.x / S;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int t = firstTile; ok && t < p.totalTiles; t += tileStep) {
+                TileCoord tc = DecodeTile(t, p);
+                const int m0 = tc.mBlk * BM, n0 = tc.nBlk * BN;
+                const int ba = BatchCoord(p.aSel, tc.prob, p);
+                const int bb = BatchCoord(p.bSel, tc.prob, p);
+                for (int kb = kbLo; kb < kbHi; kb++) {
+                    ok = MbarWait(SmemAddr(&barEmpty[s]), ph ^ 1u, abortPtr, p.status);
+                    if (!ok)
+                        break;
+                    const uint32_t full = SmemAddr(&barFull[s]);
+                    const uint32_t aDst = smemBase + s * STAGE_BYTES;
+                    const uint32_t bDst = aDst + A_TILE_BYTES;
+                    const int k0 = kb * EPR;
+                    MbarExpectTx(full, STAGE_BYTES);
+                    if (!p.aMN) {
+                        TmaLoad3D(aDst, &tmA, full, k0, m0, ba);
+                    }
+                    else {
+#pragma unroll
+                        for (int j = 0; j < BM / EPR; j++)
+                            TmaLoad3D(aDst + j * EPR * ROW_BYTES, &tmA, full, m0 + j * EPR, k0, ba);
+                    }
+                    if (!p.bMN) {
+                        TmaLoad3D(bDst, &tmB, full, k0, n0, bb);
+                    }
+                    else {
+#pragma unroll
+                        for (int j = 0; j < BN / EPR; j++)
+                            TmaLoad3D(bDst + j * EPR * ROW_BYTES, &tmB, full, n0 + j * EPR, k0, bb);
+                    }
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    }
+    else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t iDesc = InstrDesc(0, p.aMN, p.bMN, BN);
+            const uint32_t aLbo = p.aMN ? EPR * ROW_BYTES : 16, bLbo = p.bMN ? EPR * ROW_BYTES : 16;
+            const uint32_t mnStep = (UMMA_K_BYTES / ES) * ROW_BYTES;
+            const uint32_t aStep = p.aMN ? mnStep : UMMA_K_BYTES;
+            const uint32_t bStep = p.bMN ? mnStep : UMMA_K_BYTES;
+            int s = 0;
+            uint32_t ph = 0, it = 0;
+            bool ok = true;
+            for (int t = firstTile; ok && t < p.totalTiles; t += tileStep, ++it) {
+                const uint32_t buf = it & 1u;
+                ok = MbarWait(SmemAddr(&barTEmpty[buf]), ((it >> 1) & 1u) ^ 1u, abortPtr, p.status);
+                if (!ok)
+                    break;
+                TcFenceAfter();
+                const uint32_t dTmem = tmemBase + buf * BN;
+                for (int kb = kbLo; kb < kbHi; kb++) {
+                    ok = MbarWait(SmemAddr(&barFull[s]), ph, abortPtr, p.status);
+                    if (!ok)
+                        break;
+                    TcFenceAfter();
+                    const uint32_t aT = smemBase + s * STAGE_BYTES;
+                    const uint32_t bT = aT + A_TILE_BYTES;
+#pragma unroll
+                    for (int k = 0; k < KSTEPS; k++)
+                        TcMma<0>(dTmem, SmemDesc(aT + k * aStep, aLbo, 1024, 2), SmemDesc(bT + k * bStep, bLbo, 1024, 2),
+                                 iDesc, (kb != kbLo || k != 0) ? 1u : 0u);
+                    TcCommit(SmemAddr(&barEmpty[s]));
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                }
+                if (ok)
+                    TcCommit(SmemAddr(&barTFull[buf]));
+            }
+        }
+    }
+    else {
+        const int sub = warp & 3;
+        const int rowInTile = sub * 32 + lane;
+        uint32_t it = 0;
+        bool ok = true;
+        TileWriter<OutT> writer;
+        writer.Init(recvBase + RECV_BYTES, sub, &tmC);
+        for (int t = firstTile; ok && t < p.totalTiles; t += tileStep, ++it) {
+            TileCoord tc = DecodeTile(t, p);
+            const uint32_t buf = it & 1u;
+            const int row0 = tc.mBlk * BM + sub * 32, row = row0 + lane;
+            const int n0 = tc.nBlk * BN;
+            int pp, qq;
+            SplitProb(p, tc.prob, pp, qq);
+            const int bc = BatchCoord(p.cSel, tc.prob, p);
+            OutT * cRow = (OutT *)p.c + pp * p.sCp + qq * p.sCq + (long long)row * p.ldc;
+            const bool rowOk = row < p.M;
+            ok = MbarWaitWarp(SmemAddr(&barTFull[buf]), (it >> 1) & 1u, abortPtr, p.status, (uint32_t)p.epiHint);
+            if (!ok)
+                break;
+            TcFenceAfter();
+            const uint32_t tRow = tmemBase + ((uint32_t)(sub * 32) << 16) + buf * BN;
+            /* this CTA's partial sums of the other CTAs' column slices go to their receive areas */
+#pragma unroll
+            for (int dd = 1; dd < S; dd++) {
+                const uint32_t d = (rank + dd) % S;
+                const uint32_t slot = rank < d ? rank : rank - 1;          /* position among d's senders */
+                const uint32_t dstRow = MapToCta(recvBase + (buf * (S - 1) + slot) * SLOT_BYTES
+                                                 + rowInTile * (W * 4), d);
+#pragma unroll
+                for (int cc = 0; cc < W / 32; cc++) {
+                    float v[32];
+                    TmemLoad32(tRow + d * W + cc * 32, v);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        const uint32_t chunk = (uint32_t)((cc * 8 + j) ^ (lane & 7));
+                        asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};"
+                                     :: "r"(dstRow + (chunk << 4)), "f"(v[j * 4]), "f"(v[j * 4 + 1]), "f"(v[j * 4 + 2]),
+                                        "f"(v[j * 4 + 3]) : "memory");
+                    }
+                }
+            }
+            asm volatile("fence.acq_rel.cluster;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+#pragma unroll
+                for (int dd = 1; dd < S; dd++)
+                    MbarArriveCluster(MapToCta(SmemAddr(&barRecv[buf]), (rank + dd) % S));
+            }
+            /* this CTA's slice: own partial plus the others', in rank order */
+            ok = MbarWaitClusterWarp(SmemAddr(&barRecv[buf]), (it >> 1) & 1u, abortPtr, p.status);
+            if (!ok)
+                break;
+#pragma unroll
+            for (int cc = 0; cc < W / 32; cc++) {
+                float v[32];
+                TmemLoad32(tRow + rank * W + cc * 32, v);
+#pragma unroll
+                for (int sl = 0; sl < S - 1; sl++) {
+                    const uint32_t srcRow = recvBase + (buf * (S - 1) + sl) * SLOT_BYTES + rowInTile * (W * 4);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        const uint32_t chunk = (uint32_t)((cc * 8 + j) ^ (lane & 7));
+                        float4 r;
+                        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                     : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "r"(srcRow + (chunk << 4)) : "memory");
+                        v[j * 4] += r.x; v[j * 4 + 1] += r.y; v[j * 4 + 2] += r.z; v[j * 4 + 3] += r.w;
+                    }
+                }
+                const int c0 = n0 + (int)rank * W + cc * 32;
+                if (c0 < p.N)
+                    writer.Put32(p, cRow, rowOk, row0, c0, bc, v, lane);
+            }
+            TcFenceBefore();
+            __syncwarp();
+            if (lane == 0)
+                MbarArrive(SmemAddr(&barTEmpty[buf]));
+        }
+        writer.Finish(lane);
+    }
+
+    __syncwarp();
+    if (*abortPtr) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) { }
+    }
+    TcFenceBefore();
+    ClusterSync();              /* no CTA's shared memory goes away while a peer may still write to it */
+    TcFenceAfter();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                     :: "r"(tmemBase), "r"((uint32_t)TMEM_COLS) : "memory");
+    }
+}
+
 /* ---------------------------------------------------------------- host side */
 
 /* offset of operand x for problem i is idx * stride with idx in {p, q, i}; find which */
@@ -1087,6 +1378,25 @@ int LaunchOne(const TcGroup & grp, int smCount, cudaStream_t stream)
     }
     const int grid = grp.total < smCount ? grp.total : smCount;
     kern<<<grid, MODE == 0 ? 192 : 192 + CONV_THREADS, smem, stream>>>(grp);
+    CountLaunch();
+    return cudaGetLastError() == cudaSuccess ? NTB_OK : NTB_ERR_CUDA;
+}
+
+template <int S, int STAGES, typename OutT>
+int LaunchSplit(const CUtensorMap & tmA, const CUtensorMap & tmB, const CUtensorMap & tmC, const TcParams & tp, int clusters,
+                cudaStream_t stream)
+{
+    constexpr int smem = (A_TILE_BYTES + 128 * ROW_BYTES) * STAGES + 2 * (S - 1) * (BM * (128 / S) * 4) + EPI_BYTES + 1024;
+    auto kern = GemmTcSplitKernel<S, STAGES, OutT>;
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return NTB_ERR_CUDA;
+        configured[dev] = true;
+    }
+    kern<<<S * clusters, 192, smem, stream>>>(tmA, tmB, tmC, tp);
     CountLaunch();
     return cudaGetLastError() == cudaSuccess ? NTB_OK : NTB_ERR_CUDA;
 }
@@ -1181,7 +1491,8 @@ int Knob(const char * name, int dflt)
  * k-block + epilogue and hand-over cost of one tile). A k-block costs the larger of its MMA
  * time and the time its operand bytes take to arrive (an SM takes in about 60 bytes per
  * clock here, measured on the large product). Returns the tile width of the single-CTA
- * kernel, or 0 / -1 for the CTA-pair kernel with 256 x 256 / 512 x 256 tiles. Constants
+ * kernel, 0 / -1 for the CTA-pair kernel with 256 x 256 / 512 x 256 tiles, -2 / -4 for the
+ * split-K kernel with clusters of 2 / 4 CTAs. Constants
  * were fitted to timings of the benchmark configurations on a B200.
  */
 int PickBN(const Problem & p, int smCount, int mode)
@@ -1213,6 +1524,20 @@ int PickBN(const Problem & p, int smCount, int mode)
                epilogue is exposed; pairs also pay for cluster start-up and hand-shakes */
             const double cost = (double)waves * (kBlocks * perK + 2524.0 * msub + (msub == 2 ? 6000.0 : 0.0)) + 2000.0;
             if (cost < bestCost) { bestCost = cost; best = msub == 1 ? 0 : -1; }
+        }
+    }
+    if (mode == 0) {
+        /* split-K clusters: S CTAs share a 128 x 128 tile and a 1/S part of K each, then
+           exchange partial sums through distributed shared memory */
+        for (int sp = 2; sp <= 4; sp *= 2) {
+            if (kBlocks < 4.0 * sp || smCount < sp)
+                continue;
+            const long long tiles = (long long)((p.M + BM - 1) / BM) * ((p.N + 127) / 128) * p.count;
+            const long long clusters = smCount / sp;
+            const long long waves = (tiles + clusters - 1) / clusters;
+            const double perK = fmax(256.0, (double)(BM + 128) * ROW_BYTES / ingest);
+            const double cost = (double)waves * (ceil(kBlocks / sp) * perK + 2012.0 + 2500.0) + 2000.0;
+            if (cost < bestCost) { bestCost = cost; best = -sp; }
         }
     }
     return best;
@@ -1319,10 +1644,21 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
     const int knobBN = Knob("NTB_BN", 0);           /* tuning: force the single-CTA tile width */
     if (knobBN == 64 || knobBN == 128 || (knobBN == 256 && mode == 0))
         bn = knobBN;
+    const int knobSplit = Knob("NTB_SPLIT_K", -1);  /* tuning: 0 forbids, 2 / 4 force the split-K kernel */
+    if (mode == 0 && (knobSplit == 2 || knobSplit == 4) && (p.K + 63) / 64 >= knobSplit && ctx.smCount >= knobSplit)
+        bn = -knobSplit;
+    if (bn <= -2 && (knobSplit == 0 || forced == NTB_ROUTE_TC_F16_PAIR)) {
+        Problem q = p;
+        q.K = 64;                                   /* too short to split: re-ask the model */
+        bn = PickBN(q, ctx.smCount, mode);
+    }
     if (mode == 0 && forced == NTB_ROUTE_TC_F16_PAIR && ctx.smCount >= 2 && bn > 0)
         bn = Knob("NTB_PAIR_MSUB", 2) == 1 ? 0 : -1;
-    if (bn <= 0 && forced == NTB_ROUTE_TC_F16)
+    if (bn <= 0 && bn >= -1 && forced == NTB_ROUTE_TC_F16)
         bn = 256;
+    const int split = bn <= -2 ? -bn : 0;
+    if (split)
+        bn = 128;
     const bool pair = bn <= 0;
     const int msub = bn == -1 ? 2 : 1;
     if (pair)
@@ -1339,6 +1675,19 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
         grp.tm[1][i] = grp.tm[0][i];
     grp.split = grp.total = grp.p[0].totalTiles;
 
+    if (split) {
+        /* a 32-column slice of half values is half a store box: direct stores instead */
+        if (split == 4 && p.dtC == NTB_X_FLOAT16)
+            grp.p[0].cTma = 0;
+        const TcParams & tp = grp.p[0];
+        const int clusters = (int)(tp.totalTiles < ctx.smCount / split ? tp.totalTiles : ctx.smCount / split);
+        const bool half = p.dtC == NTB_X_FLOAT16;
+        if (split == 2)
+            return half ? LaunchSplit<2, 4, __half>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, clusters, stream)
+                        : LaunchSplit<2, 4, float>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, clusters, stream);
+        return half ? LaunchSplit<4, 3, __half>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, clusters, stream)
+                    : LaunchSplit<4, 3, float>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, clusters, stream);
+    }
     if (pair) {
         const TcParams & tp = grp.p[0];
         const int pairs = (int)(tp.totalTiles < ctx.smCount / 2 ? tp.totalTiles : ctx.smCount / 2);
@@ -1349,6 +1698,12 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
                                       : LaunchPair<1, 6, float>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, pairs, stream);
     }
     return LaunchGroup(grp, mode, bn, p.dtC, ctx.smCount, stream);
+}
+
+/* what the cost model would launch for p alone: > 0 single-CTA tile width, <= 0 a cluster kernel */
+int TcTileChoice(const DeviceCtx & ctx, const Problem & p)
+{
+    return PickBN(p, ctx.smCount, p.dtAB == NTB_X_FLOAT16 ? 0 : 1);
 }
 
 /*

@@ -244,6 +244,57 @@ def test_cta_pair_route(msub, oracle):
     status_ok()
 
 
+@pytest.mark.parametrize("split", ["2", "4"])
+def test_split_k_cluster_route(split, oracle):
+    """Clusters of 2 / 4 CTAs share a tile and a part of K each and exchange partial sums
+    through distributed shared memory; forced here on shapes with ragged edges, a K that
+    does not divide evenly, batches, every transposition, alpha/beta and fp32 output."""
+    rng = np.random.default_rng(600 + int(split))
+    L = capi.lib()
+    os.environ["NTB_SPLIT_K"] = split
+    try:
+        shapes = [(128, 128, 512), (200, 136, 1032), (72, 264, 448), (256, 128, 4096)]
+        n = 0
+        for tA in (X_TRANS, X_NOTRANS):
+            for tB in (X_TRANS, X_NOTRANS):
+                for (M, N, K) in shapes:
+                    alpha, beta = AB[n % len(AB)]
+                    n += 1
+                    cnt = 1 + n % 2
+                    a = round_to_half(stored(rng, (cnt,), M, K, tA))
+                    b = round_to_half(stored(rng, (cnt,), K, N, tB))
+                    c0 = round_to_half(rng.normal(size=(cnt, M, N)).astype(np.float32))
+                    out_dtype = torch.float32 if n % 3 == 0 else torch.float16
+                    c = to_dev(c0, out_dtype)
+                    before = L.ntb_launch_count()
+                    ops._MatrixMulBatched(to_dev(a, torch.float16), tA, to_dev(b, torch.float16), tB, c, alpha, beta)
+                    assert L.ntb_launch_count() == before + 1
+                    err = rel_fro(c.float().cpu().numpy(), oracle.matmul_batched(a, tA, b, tB, alpha, beta, c0))
+                    assert err <= 2e-3, (M, N, K, tA, tB, alpha, beta, err)
+    finally:
+        os.environ.pop("NTB_SPLIT_K", None)
+    status_ok()
+
+
+def test_split_k_is_chosen_for_weight_gradient_shapes_and_is_deterministic(oracle):
+    """a^T * dedc with K = 4096 tokens and 64 output tiles: the cost model picks the split."""
+    g = torch.Generator(device=DEV)
+    g.manual_seed(21)
+    a = torch.randn(4096, 1024, device=DEV, generator=g).half()
+    d = torch.randn(4096, 512, device=DEV, generator=g).half()
+    outs = []
+    for _ in range(3):
+        c = torch.zeros(1024, 512, device=DEV, dtype=torch.float16)
+        ops._MatrixMul2D(a, X_TRANS, d, X_NOTRANS, c, 1.0 / 64, 0.0)
+        outs.append(c)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
+    rows = np.arange(0, 1024, 41)
+    want = oracle.matmul2d(np.ascontiguousarray(a.float().cpu().numpy()[:, rows]), X_TRANS,
+                           d.float().cpu().numpy(), X_NOTRANS, 1.0 / 64, 0.0)
+    assert rel_fro(outs[0][rows].float().cpu().numpy(), want) <= 2e-3
+    status_ok()
+
+
 # --------------------------------------------------------------- semantics corners
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
