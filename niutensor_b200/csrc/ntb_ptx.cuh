@@ -23,6 +23,10 @@ constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;   /* about two seconds */
 
 /* ---------------------------------------------------------------- PTX wrappers */
 
+#ifndef NTB_WAIT_HINT_NS
+#define NTB_WAIT_HINT_NS 200
+#endif
+
 __device__ __forceinline__ uint32_t SmemAddr(const void * p)
 {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -49,6 +53,13 @@ __device__ __forceinline__ void MbarArrive(uint32_t bar)
 __device__ __forceinline__ uint32_t MbarTryWait(uint32_t bar, uint32_t parity, uint32_t hintNs)
 {
     uint32_t done;
+    if (hintNs == 0) {
+        asm volatile("{\n\t.reg .pred p;\n\t"
+                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                     "selp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        return done;
+    }
     asm volatile("{\n\t.reg .pred p;\n\t"
                  "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
                  "selp.u32 %0, 1, 0, p;\n\t}"
@@ -59,8 +70,19 @@ __device__ __forceinline__ uint32_t MbarTryWait(uint32_t bar, uint32_t parity, u
 /* Bounded wait. Returns false when the CTA is aborting (this waiter ran out of time, or
    another one did). */
 __device__ __forceinline__ bool MbarWait(uint32_t bar, uint32_t parity, volatile int * abortFlag, int * status,
-                                         uint32_t hintNs = 200)
+                                         uint32_t hintNs = NTB_WAIT_HINT_NS)
 {
+#ifdef NTB_TESTWAIT
+    {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\t"
+                     "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                     "selp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done)
+            return true;
+    }
+#endif
     if (MbarTryWait(bar, parity, hintNs))
         return true;
     const long long t0 = clock64();
@@ -132,6 +154,27 @@ __device__ __forceinline__ void TcMma(uint32_t dTmem, uint64_t aDesc, uint64_t b
         asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
                      :: "r"(dTmem), "l"(aDesc), "l"(bDesc), "r"(iDesc), "r"(accumulate) : "memory");
+    }
+}
+
+/* The same instruction with each shared-memory descriptor given as its two 32-bit halves:
+   inside a main loop only the low word (the start address field) changes from one
+   instruction to the next, a single 32-bit add. */
+template <int MODE>
+__device__ __forceinline__ void TcMmaLH(uint32_t dTmem, uint32_t aLo, uint32_t aHi, uint32_t bLo, uint32_t bHi,
+                                        uint32_t iDesc, uint32_t accumulate)
+{
+    if (MODE == 0) {
+        asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+                     "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+                     "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+                     :: "r"(dTmem), "r"(aLo), "r"(aHi), "r"(bLo), "r"(bHi), "r"(iDesc), "r"(accumulate) : "memory");
+    }
+    else {
+        asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+                     "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+                     "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %5, p;\n\t}"
+                     :: "r"(dTmem), "r"(aLo), "r"(aHi), "r"(bLo), "r"(bHi), "r"(iDesc), "r"(accumulate) : "memory");
     }
 }
 

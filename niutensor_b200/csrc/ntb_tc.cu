@@ -29,6 +29,7 @@
  * leaves its loop; the CTA then lets copies in flight land, frees its TMEM and returns.
  */
 #include "ntb_internal.h"
+#include <cstdio>
 #include "ntb_ptx.cuh"
 #include <cstdlib>
 #include <cmath>
@@ -76,6 +77,7 @@ struct TcParams {
     int group;              /* m-blocks per band of the tile walk */
     FastDiv fdPerProb, fdBand, fdGroup, fdLast, fdQ;   /* tiles per problem, tiles per band, rows of a full / of the last band, Q */
     int epiHint;            /* suspend-time hint (ns) of the epilogue warps' barrier probes */
+    int cPrefetch;          /* wide tiles with beta != 0: 0 no L2 prefetch of old C, 1 boxes through TMA, 2 one request per line */
     float alpha, beta;
     const void * bias;      /* N values of C's type added to every output row, or NULL */
     int act;                /* 1: max(x, 0) applied last */
@@ -91,11 +93,22 @@ __device__ unsigned long long gWaitStats[8];
 /* timeline of CTA 0 of the single-CTA kernel, in SM clocks since kernel entry:
    0 set-up done, 1 first TMA issued, 2 first stage landed, 3 first tile's MMAs committed,
    4 epilogue saw the accumulator, 5 epilogue stores issued, 6 stores complete, 7 kernel end */
-__device__ unsigned long long gTimeline[16];
+__device__ unsigned long long gTimeline[64];
+__device__ int gExp;   /* experiment switches: 1 no MMA instructions, 2 no TMA loads */
+#define NTB_MARKK(row, kb) do { if (blockIdx.x == 0 && (kb) < 16 && tlShared[16 + (row) * 16 + (kb)] == 0) tlShared[16 + (row) * 16 + (kb)] = (unsigned long long)(clock64() - kernelT0) + 1; } while (0)
 #define NTB_MARK(slot) do { if (blockIdx.x == 0 && tlShared[slot] == 0) tlShared[slot] = (unsigned long long)(clock64() - kernelT0) + 1; } while (0)
+#ifdef NTB_CLOCKS
 #define NTB_TIMED(slot, expr) do { long long t0_ = clock64(); expr; wstat[slot] += clock64() - t0_; } while (0)
 #else
+#undef NTB_MARK
+#undef NTB_MARKK
 #define NTB_MARK(slot) do { } while (0)
+#define NTB_MARKK(row, kb) do { } while (0)
+#define NTB_TIMED(slot, expr) do { expr; } while (0)
+#endif
+#else
+#define NTB_MARK(slot) do { } while (0)
+#define NTB_MARKK(row, kb) do { } while (0)
 #define NTB_TIMED(slot, expr) do { expr; } while (0)
 #endif
 
@@ -142,10 +155,14 @@ __device__ __forceinline__ void StoreOne(float * p, float v) { *p = v; }
    row starting at column c0; old values and the bias are read with 16-byte vectors where
    alignment allows it */
 template <typename OutT>
-__device__ __forceinline__ void ScaleRow32(const OutT * cRow, int c0, bool rowOk, float * v, const TcParams & p)
+__device__ __forceinline__ void ScaleRow32(const OutT * cRow, int c0, bool rowOk, float * v, const TcParams & p,
+                                           bool scaled = false)
 {
     constexpr int VN = Vec16<OutT>::N;
-    if (p.beta == 0.f || !rowOk) {
+    if (scaled) {
+        /* the caller has already formed alpha * v + beta * old C */
+    }
+    else if (p.beta == 0.f || !rowOk) {
 #pragma unroll
         for (int e = 0; e < 32; e++)
             v[e] = p.alpha * v[e];
@@ -232,6 +249,14 @@ __device__ __forceinline__ void StoreRow32Direct(OutT * cRow, int c0, const floa
  * store per box: full 128-byte lines, asynchronous, clipped by TMA at the ragged edges of
  * C. Two boxes per warp alternate; before a box is refilled the warp waits until the store
  * that last used it has read it. Otherwise values go out with direct stores.
+ *
+ * With beta != 0 and tiles of at most two boxes per warp (128 half columns) the old values
+ * of C come the same way in the other direction: a TMA load brings each box into the
+ * staging buffer that will hold its result, requested when the tile is announced
+ * (BeginTile), before the accumulator is waited for, so it arrives under the main loop.
+ * One row per lane straight from global memory touches 32 lines per instruction and waits
+ * for each 32-column piece in turn; that is what wider tiles still do, after BeginTile
+ * has asked L2 to fetch the tile.
  */
 constexpr int EPI_BOX_BYTES = 32 * ROW_BYTES;               /* 32 rows x 128 B */
 constexpr int EPI_BYTES = 4 * 2 * EPI_BOX_BYTES;            /* four epilogue warps, two boxes each */
@@ -243,34 +268,208 @@ struct TileWriter {
     uint32_t stage;          /* shared-memory address of this warp's two boxes */
     uint32_t boxes;          /* boxes handed to TMA so far */
     const CUtensorMap * map;
+    uint32_t bars;           /* two mbarriers, one per box buffer, for the loads of old C values */
+    uint32_t phase;          /* bit b: parity of the next wait on buffer b's barrier */
+    volatile int * abortFlag;
+    int * status;
+    /* old-C fetch plan of the current tile: boxes 0 .. fTotal-1, fPerSub per 128-row sub-tile */
+    bool fOn;
+    int fRow0, fRowStep, fCol0, fPerSub, fTotal, fBatch;
 
-    __device__ __forceinline__ void Init(uint32_t epiBase, int sub, const CUtensorMap * m)
+    /* barPair: this warp's two mbarriers (initialised with count 1) */
+    __device__ __forceinline__ void Init(uint32_t epiBase, int sub, const CUtensorMap * m, uint64_t * barPair,
+                                         volatile int * abortPtr, int * statusPtr)
     {
         stage = epiBase + sub * 2 * EPI_BOX_BYTES;
         boxes = 0;
         map = m;
+        bars = SmemAddr(barPair);
+        phase = 0;
+        abortFlag = abortPtr;
+        status = statusPtr;
+        fOn = false;
+        fTotal = 0;
+        oldCurOk = oldNxtOk = false;
+    }
+
+    /* Old C values of wide tiles (beta != 0, half output): every lane keeps the 64 columns
+       of its row that the next chunk needs in registers, requested one chunk ahead (the
+       first chunk of a tile before the accumulator is waited for), so the memory latency
+       of one chunk runs under the work on the chunk before it. */
+    static constexpr bool OLD_REGS = sizeof(OutT) == 2;
+    uint4 oldCur[OLD_REGS ? 8 : 1], oldNxt[OLD_REGS ? 8 : 1];
+    bool oldCurOk, oldNxtOk;
+
+    __device__ __forceinline__ void OldRequest(const TcParams & p, const OutT * cRow, int c0, bool rowOk)
+    {
+        oldNxtOk = false;
+        if (!OLD_REGS)
+            return;
+        oldNxtOk = !fOn && p.beta != 0.f && p.cVec && rowOk && c0 + 64 <= p.N;
+        if (oldNxtOk) {
+#pragma unroll
+            for (int j = 0; j < (OLD_REGS ? 8 : 1); j++)
+                oldNxt[j] = *(const uint4 *)(cRow + c0 + j * 8);
+        }
+    }
+
+    __device__ __forceinline__ void OldAdvance()
+    {
+#pragma unroll
+        for (int j = 0; j < (OLD_REGS ? 8 : 1); j++)
+            oldCur[j] = oldNxt[j];
+        oldCurOk = oldNxtOk;
+        oldNxtOk = false;
+    }
+
+    /* v <- alpha * v + beta * old for the 32 columns whose old values sit in o[0..3] */
+    __device__ __forceinline__ void CombineOld32(const TcParams & p, const uint4 * o, float * v)
+    {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            float2 f;
+            f = __half22float2(*(const __half2 *)&o[j].x);
+            v[j * 8 + 0] = fmaf(p.beta, f.x, p.alpha * v[j * 8 + 0]); v[j * 8 + 1] = fmaf(p.beta, f.y, p.alpha * v[j * 8 + 1]);
+            f = __half22float2(*(const __half2 *)&o[j].y);
+            v[j * 8 + 2] = fmaf(p.beta, f.x, p.alpha * v[j * 8 + 2]); v[j * 8 + 3] = fmaf(p.beta, f.y, p.alpha * v[j * 8 + 3]);
+            f = __half22float2(*(const __half2 *)&o[j].z);
+            v[j * 8 + 4] = fmaf(p.beta, f.x, p.alpha * v[j * 8 + 4]); v[j * 8 + 5] = fmaf(p.beta, f.y, p.alpha * v[j * 8 + 5]);
+            f = __half22float2(*(const __half2 *)&o[j].w);
+            v[j * 8 + 6] = fmaf(p.beta, f.x, p.alpha * v[j * 8 + 6]); v[j * 8 + 7] = fmaf(p.beta, f.y, p.alpha * v[j * 8 + 7]);
+        }
+    }
+
+    /* lane 0: request old C values of box k of the current tile into buffer bufIdx */
+    __device__ __forceinline__ void FetchBox(const TcParams & p, int k, uint32_t bufIdx)
+    {
+        const int sub = k >= fPerSub ? 1 : 0;
+        const int row0 = fRow0 + sub * fRowStep;
+        const int col = fCol0 + (k - sub * fPerSub) * BOX_COLS;
+        if (row0 < p.M) {
+            const uint32_t bar = bars + bufIdx * 8;
+            MbarExpectTx(bar, EPI_BOX_BYTES);
+            TmaLoad3D(stage + bufIdx * EPI_BOX_BYTES, map, bar, col, row0, fBatch);
+        }
+    }
+
+    /* Announces the next tile of this warp: nSub (1 or 2) sub-tiles of 32 rows starting at
+       row0 and row0 + rowStep, columns col0 .. col0 + cols - 1 (col0 on a box boundary),
+       visited sub-tile by sub-tile, left to right; cLane points at column col0 of row
+       row0 + lane. Call it before waiting for the accumulator. */
+    __device__ __forceinline__ void BeginTile(const TcParams & p, const OutT * cLane, int row0, int rowStep, int nSub,
+                                              int col0, int cols, int batch, int lane)
+    {
+        fOn = false;
+        if (!p.cTma || p.beta == 0.f)
+            return;
+        int live = p.N - col0 < cols ? p.N - col0 : cols;
+        fPerSub = live > 0 ? (live + BOX_COLS - 1) / BOX_COLS : 0;
+        fTotal = fPerSub * nSub;
+        fRow0 = row0; fRowStep = rowStep; fCol0 = col0; fBatch = batch;
+        if (fTotal > 2) {
+            /* more boxes than staging buffers: a later box could only be requested after the
+               store two boxes earlier has left its buffer, and that store queues in the TMA
+               unit behind the next tile's operand loads. Such tiles read old C directly;
+               here it is only pulled into L2. */
+            if (p.cPrefetch == 1 && lane == 0) {
+                for (int k = 0; k < fTotal; k++) {
+                    const int sub = k >= fPerSub ? 1 : 0;
+                    if (fRow0 + sub * fRowStep < p.M)
+                        TmaPrefetch3D(map, fCol0 + (k - sub * fPerSub) * BOX_COLS, fRow0 + sub * fRowStep, fBatch);
+                }
+            }
+            if (p.cPrefetch == 2) {
+                /* every lane asks for the lines of its own rows */
+                for (int sub = 0; sub < nSub; sub++) {
+                    if (row0 + sub * rowStep + lane < p.M) {
+                        const char * line = (const char *)(cLane + (long long)sub * rowStep * p.ldc);
+                        for (int b = 0; b < live * (int)sizeof(OutT); b += 128)
+                            asm volatile("prefetch.global.L2 [%0];" :: "l"(line + b));
+                    }
+                }
+            }
+            return;
+        }
+        fOn = true;
+        if (lane == 0 && fTotal > 0) {
+            /* every earlier store has read its buffer */
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            for (int k = 0; k < fTotal; k++)
+                FetchBox(p, k, (boxes + (uint32_t)k) & 1u);
+        }
     }
 
     /* v: raw accumulators of columns c0 .. c0+31 of this lane's row (row = row0 + lane) */
     __device__ __forceinline__ void Put32(const TcParams & p, OutT * cRow, bool rowOk, int row0, int c0,
                                           int batch, float * v, int lane)
     {
-        ScaleRow32(cRow, c0, rowOk, v, p);
+        const bool fromRegs = OLD_REGS && oldCurOk;       /* old values of this chunk are in oldCur */
+        if (fromRegs) {
+            if (c0 & 32)
+                CombineOld32(p, oldCur + (OLD_REGS ? 4 : 0), v);
+            else
+                CombineOld32(p, oldCur, v);
+        }
         if (!p.cTma) {
+            ScaleRow32(cRow, c0, rowOk, v, p, fromRegs);
             if (rowOk)
                 StoreRow32Direct(cRow, c0, v, p);
             return;
         }
         const int colInBox = c0 % BOX_COLS;
-        const uint32_t box = stage + (boxes & 1u) * EPI_BOX_BYTES;
+        const uint32_t bufIdx = boxes & 1u;
+        const uint32_t box = stage + bufIdx * EPI_BOX_BYTES;
+        const bool live = row0 < p.M;             /* uniform across the warp */
         if (colInBox == 0) {
-            /* the store that used this box two boxes ago must have read it */
-            if (lane == 0 && boxes >= 2)
-                asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-            __syncwarp();
+            if (fOn) {
+                /* the old values of this box were requested into this buffer */
+                if (live) {
+                    MbarWait(bars + bufIdx * 8, (phase >> bufIdx) & 1u, abortFlag, status, 20);
+                    phase ^= 1u << bufIdx;
+                }
+                else {
+                    __syncwarp();                 /* lane 0 has waited for the last reader of this buffer */
+                }
+            }
+            else {
+                /* the store that used this box two boxes ago must have read it */
+                if (lane == 0 && boxes >= 2)
+                    asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                __syncwarp();
+            }
         }
         const uint32_t rowAddr = box + lane * ROW_BYTES;
         const int firstChunk = colInBox * (int)sizeof(OutT) / 16;
+        if (fOn && live) {
+            /* alpha * v + beta * old, the old values read from where the result will go */
+#pragma unroll
+            for (int j = 0; j < CHUNKS; j++) {
+                const uint32_t src = rowAddr + (uint32_t)(((firstChunk + j) ^ (lane & 7)) << 4);
+                uint32_t w0, w1, w2, w3;
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3) : "r"(src) : "memory");
+                if (sizeof(OutT) == 2) {
+                    float2 f;
+                    f = __half22float2(*(__half2 *)&w0);
+                    v[j * 8 + 0] = fmaf(p.beta, f.x, p.alpha * v[j * 8 + 0]); v[j * 8 + 1] = fmaf(p.beta, f.y, p.alpha * v[j * 8 + 1]);
+                    f = __half22float2(*(__half2 *)&w1);
+                    v[j * 8 + 2] = fmaf(p.beta, f.x, p.alpha * v[j * 8 + 2]); v[j * 8 + 3] = fmaf(p.beta, f.y, p.alpha * v[j * 8 + 3]);
+                    f = __half22float2(*(__half2 *)&w2);
+                    v[j * 8 + 4] = fmaf(p.beta, f.x, p.alpha * v[j * 8 + 4]); v[j * 8 + 5] = fmaf(p.beta, f.y, p.alpha * v[j * 8 + 5]);
+                    f = __half22float2(*(__half2 *)&w3);
+                    v[j * 8 + 6] = fmaf(p.beta, f.x, p.alpha * v[j * 8 + 6]); v[j * 8 + 7] = fmaf(p.beta, f.y, p.alpha * v[j * 8 + 7]);
+                }
+                else {
+                    v[j * 4 + 0] = fmaf(p.beta, __uint_as_float(w0), p.alpha * v[j * 4 + 0]);
+                    v[j * 4 + 1] = fmaf(p.beta, __uint_as_float(w1), p.alpha * v[j * 4 + 1]);
+                    v[j * 4 + 2] = fmaf(p.beta, __uint_as_float(w2), p.alpha * v[j * 4 + 2]);
+                    v[j * 4 + 3] = fmaf(p.beta, __uint_as_float(w3), p.alpha * v[j * 4 + 3]);
+                }
+            }
+            ScaleRow32(cRow, c0, rowOk, v, p, true);
+        }
+        else {
+            ScaleRow32(cRow, c0, rowOk, v, p, fromRegs);
+        }
 #pragma unroll
         for (int j = 0; j < CHUNKS; j++) {
             const uint32_t dst = rowAddr + (uint32_t)(((firstChunk + j) ^ (lane & 7)) << 4);
@@ -380,10 +579,16 @@ struct TcGroup {
     const int chunkBlocks = MODE == 0 ? kBlocks : FP32_CHUNK_BLOCKS; \
     (void)chunkBlocks
 
-template <int MODE, int BN, int STAGES, typename OutT>
+template <int MODE, int BN, int STAGES, int G, typename OutT>
 __global__ void __launch_bounds__(MODE == 0 ? 192 : 192 + CONV_THREADS, 1)
 GemmTcKernel(const __grid_constant__ TcGroup grp)
 {
+    /* G k-blocks share one full / empty barrier pair: the producer and the MMA thread each
+       pay for a barrier hand-shake (a few hundred clocks of their own time, most of it the
+       MMA thread's shared-memory probe waiting behind the tensor-core instructions it has
+       just issued) once per G k-blocks instead of once per k-block */
+    static_assert(STAGES % G == 0 && (MODE == 0 || G == 1), "k-blocks per hand-shake");
+    constexpr int NSTG = STAGES / G;                    /* barrier pairs in the ring */
     constexpr int ES = MODE == 0 ? 2 : 4;               /* operand element size */
     constexpr int EPR = ROW_BYTES / ES;                 /* elements per 128-byte row = K per stage */
     constexpr int B_TILE_BYTES = BN * ROW_BYTES;
@@ -397,8 +602,9 @@ GemmTcKernel(const __grid_constant__ TcGroup grp)
 
 #ifdef NTB_WAIT_STATS
     const long long kernelT0 = clock64();
-    __shared__ unsigned long long tlShared[16];
-    if (threadIdx.x < 16) tlShared[threadIdx.x] = 0;
+    const int exp = *(volatile int *)&gExp;
+    __shared__ unsigned long long tlShared[64];
+    if (threadIdx.x < 64) tlShared[threadIdx.x] = 0;
     __syncthreads();
 #endif
     extern __shared__ uint8_t smemRaw[];
@@ -407,6 +613,7 @@ GemmTcKernel(const __grid_constant__ TcGroup grp)
     __shared__ __align__(8) uint64_t barConv[STAGES];
     __shared__ __align__(8) uint64_t barTFull[2];
     __shared__ __align__(8) uint64_t barTEmpty[2];
+    __shared__ __align__(8) uint64_t barOldC[8];    /* per epilogue warp and staging box: old C values have landed */
     __shared__ uint32_t tmemBaseSlot;
     __shared__ int abortFlag;
 
@@ -440,6 +647,8 @@ GemmTcKernel(const __grid_constant__ TcGroup grp)
             MbarInit(SmemAddr(&barTFull[b]), 1);
             MbarInit(SmemAddr(&barTEmpty[b]), 4);
         }
+        for (int b = 0; b < 8; b++)
+            MbarInit(SmemAddr(&barOldC[b]), 1);
         abortFlag = 0;
         NTB_MARK(9);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -468,7 +677,7 @@ GemmTcKernel(const __grid_constant__ TcGroup grp)
     }
 
 #ifdef NTB_WAIT_STATS
-    long long wstat[4] = {0, 0, 0, 0};
+    long long wstat[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #endif
     if (threadIdx.x == 0) NTB_MARK(0);
     const int firstTile = blockIdx.x;
@@ -487,55 +696,82 @@ GemmTcKernel(const __grid_constant__ TcGroup grp)
                 const int ba = BatchCoord(p.aSel, tc.prob, p);
                 const int bb = BatchCoord(p.bSel, tc.prob, p);
                 NTB_MARK(12);
-                for (int kb = 0; kb < kBlocks; kb++) {
-                    NTB_TIMED(0, ok = MbarWait(SmemAddr(&barEmpty[s]), ph ^ 1u, abortPtr, p.status));
+                /* everything the k-loop needs, in registers: the loop itself touches no
+                   kernel parameter */
+                const bool aMN = p.aMN != 0, bMN = p.bMN != 0;
+                const int pfDist = p.pfDist, nkb = kBlocks;
+                int * const status = p.status;
+                const CUtensorMap * const mapA = &tmA;
+                const CUtensorMap * const mapB = &tmB;
+#ifdef NTB_WAIT_STATS
+                const long long loopT0 = clock64();
+#endif
+                for (int kb = 0; kb < nkb; kb += G) {
+                    NTB_TIMED(0, ok = MbarWait(SmemAddr(&barEmpty[s]), ph ^ 1u, abortPtr, status));
                     NTB_MARK(13);
                     if (!ok)
                         break;
                     const uint32_t full = SmemAddr(&barFull[s]);
-                    const uint32_t aDst = smemBase + s * STAGE_BYTES;
-                    const uint32_t bDst = aDst + A_TILE_BYTES;
-                    const int k0 = kb * EPR;
-                    MbarExpectTx(full, PLANE_BYTES);
+                    const int nb = G == 1 ? 1 : (nkb - kb < G ? nkb - kb : G);
+#ifdef NTB_WAIT_STATS
+                    if (exp & 2) {
+                        MbarArrive(full);
+                        if (++s == NSTG) { s = 0; ph ^= 1u; }
+                        continue;
+                    }
+#endif
+                    NTB_TIMED(6, MbarExpectTx(full, (uint32_t)nb * PLANE_BYTES));
                     NTB_MARK(14);
-                    if (!p.aMN) {
-                        TmaLoad3D(aDst, &tmA, full, k0, m0, ba);
-                    }
-                    else {
 #pragma unroll
-                        for (int j = 0; j < BM / EPR; j++)
-                            TmaLoad3D(aDst + j * EPR * ROW_BYTES, &tmA, full, m0 + j * EPR, k0, ba);
-                    }
-                    if (!p.bMN) {
-                        TmaLoad3D(bDst, &tmB, full, k0, n0, bb);
-                    }
-                    else {
+                    for (int j = 0; j < G; j++) {
+                        if (j < nb) {
+                            const uint32_t aDst = smemBase + (uint32_t)(s * G + j) * STAGE_BYTES;
+                            const uint32_t bDst = aDst + A_TILE_BYTES;
+                            const int k0 = (kb + j) * EPR;
+                            if (!aMN) {
+                                NTB_TIMED(7, TmaLoad3D(aDst, mapA, full, k0, m0, ba));
+                            }
+                            else {
 #pragma unroll
-                        for (int j = 0; j < BN / EPR; j++)
-                            TmaLoad3D(bDst + j * EPR * ROW_BYTES, &tmB, full, n0 + j * EPR, k0, bb);
-                    }
-                    if (p.pfDist > 0 && kb + p.pfDist < kBlocks) {
-                        const int kp = k0 + p.pfDist * EPR;
-                        if (!p.aMN) {
-                            TmaPrefetch3D(&tmA, kp, m0, ba);
-                        }
-                        else {
+                                for (int i = 0; i < BM / EPR; i++)
+                                    TmaLoad3D(aDst + i * EPR * ROW_BYTES, mapA, full, m0 + i * EPR, k0, ba);
+                            }
+                            if (!bMN) {
+                                NTB_TIMED(5, TmaLoad3D(bDst, mapB, full, k0, n0, bb));
+                            }
+                            else {
 #pragma unroll
-                            for (int j = 0; j < BM / EPR; j++)
-                                TmaPrefetch3D(&tmA, m0 + j * EPR, kp, ba);
-                        }
-                        if (!p.bMN) {
-                            TmaPrefetch3D(&tmB, kp, n0, bb);
-                        }
-                        else {
+                                for (int i = 0; i < BN / EPR; i++)
+                                    TmaLoad3D(bDst + i * EPR * ROW_BYTES, mapB, full, n0 + i * EPR, k0, bb);
+                            }
+                            if (pfDist > 0 && kb + j + pfDist < nkb) {
+                                const int kp = k0 + pfDist * EPR;
+                                if (!aMN) {
+                                    TmaPrefetch3D(mapA, kp, m0, ba);
+                                }
+                                else {
 #pragma unroll
-                            for (int j = 0; j < BN / EPR; j++)
-                                TmaPrefetch3D(&tmB, n0 + j * EPR, kp, bb);
+                                    for (int i = 0; i < BM / EPR; i++)
+                                        TmaPrefetch3D(mapA, m0 + i * EPR, kp, ba);
+                                }
+                                if (!bMN) {
+                                    TmaPrefetch3D(mapB, kp, n0, bb);
+                                }
+                                else {
+#pragma unroll
+                                    for (int i = 0; i < BN / EPR; i++)
+                                        TmaPrefetch3D(mapB, n0 + i * EPR, kp, bb);
+                                }
+                            }
                         }
                     }
                     NTB_MARK(1);
-                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                    NTB_MARKK(0, kb);
+                    if (++s == NSTG) { s = 0; ph ^= 1u; }
                 }
+#ifdef NTB_WAIT_STATS
+                wstat[3] += clock64() - loopT0;
+#endif
             }
         }
     }
@@ -544,8 +780,11 @@ GemmTcKernel(const __grid_constant__ TcGroup grp)
         if (lane == 0) {
             int s = 0;
             uint32_t ph = 0;
+            uint32_t stageOff = 0;                /* s * STAGE_BYTES in 16-byte units */
             uint32_t it = 0;                      /* accumulator hand-overs so far */
             bool ok = true;
+            const uint32_t barFull0 = SmemAddr(MODE == 0 ? &barFull[0] : &barConv[0]);
+            const uint32_t barEmpty0 = SmemAddr(&barEmpty[0]);
             for (int t = firstTile; ok && t < grp.total; t += tileStep) {
                 NTB_SELECT_PROBLEM();
                 (void)tl;
@@ -562,40 +801,67 @@ GemmTcKernel(const __grid_constant__ TcGroup grp)
                    repeats every 4 k-rows (512 B) instead of every 8 */
                 const uint32_t aLay = (MODE != 0 && p.aMN) ? 1u : 2u, bLay = (MODE != 0 && p.bMN) ? 1u : 2u;
                 const uint32_t aSbo = (MODE != 0 && p.aMN) ? 512u : 1024u, bSbo = (MODE != 0 && p.bMN) ? 512u : 1024u;
-                for (int kb0 = 0; ok && kb0 < kBlocks; kb0 += chunkBlocks, ++it) {
+                int * const status = p.status;
+                const int nkb = kBlocks, chunk = chunkBlocks;
+                /* descriptors of stage 0, k-step 0; inside the loop only their start-address
+                   field (bits 0-13 of the low word, in 16-byte units) moves */
+                const uint64_t aD0 = SmemDesc(smemBase, aLbo, aSbo, aLay);
+                const uint64_t bD0 = SmemDesc(smemBase + A_TILE_BYTES, bLbo, bSbo, bLay);
+                const uint32_t aLo0 = (uint32_t)aD0, aHiW = (uint32_t)(aD0 >> 32);
+                const uint32_t bLo0 = (uint32_t)bD0, bHiW = (uint32_t)(bD0 >> 32);
+                const uint32_t aStep4 = aStep >> 4, bStep4 = bStep >> 4;
+                for (int kb0 = 0; ok && kb0 < nkb; kb0 += chunk, ++it) {
                     const uint32_t buf = it & 1u;
-                    NTB_TIMED(2, ok = MbarWait(SmemAddr(&barTEmpty[buf]), ((it >> 1) & 1u) ^ 1u, abortPtr, p.status));
+                    NTB_TIMED(2, ok = MbarWait(SmemAddr(&barTEmpty[buf]), ((it >> 1) & 1u) ^ 1u, abortPtr, status));
                     if (!ok)
                         break;
                     TcFenceAfter();
                     const uint32_t dTmem = tmemBase + buf * BN;
-                    const int kbEnd = min(kBlocks, kb0 + chunkBlocks);
-                    for (int kb = kb0; kb < kbEnd; kb++) {
-                        NTB_TIMED(1, ok = MbarWait(SmemAddr(MODE == 0 ? &barFull[s] : &barConv[s]), ph, abortPtr, p.status));
+                    const int kbEnd = min(nkb, kb0 + chunk);
+                    uint32_t acc = 0u;                /* the first instruction of a chain overwrites */
+                    for (int kb = kb0; kb < kbEnd; kb += G) {
+                        NTB_TIMED(1, ok = MbarWait(barFull0 + (uint32_t)s * 8u, ph, abortPtr, status));
                         if (!ok)
                             break;
                         NTB_MARK(2);
+                        NTB_MARKK(1, kb);
                         TcFenceAfter();
-                        const uint32_t aHi = smemBase + s * STAGE_BYTES;
-                        const uint32_t bHi = aHi + A_TILE_BYTES;
+                        const int nb = G == 1 ? 1 : (kbEnd - kb < G ? kbEnd - kb : G);
 #pragma unroll
-                        for (int k = 0; k < KSTEPS; k++) {
-                            const uint64_t aD = SmemDesc(aHi + k * aStep, aLbo, aSbo, aLay);
-                            const uint64_t bD = SmemDesc(bHi + k * bStep, bLbo, bSbo, bLay);
-                            const uint32_t acc = (kb != kb0 || k != 0) ? 1u : 0u;
-                            if (MODE == 0) {
-                                TcMma<MODE>(dTmem, aD, bD, iDesc, acc);
-                            }
-                            else {
-                                const uint64_t aL = SmemDesc(aHi + PLANE_BYTES + k * aStep, aLbo, aSbo, aLay);
-                                const uint64_t bL = SmemDesc(bHi + PLANE_BYTES + k * bStep, bLbo, bSbo, bLay);
-                                TcMma<MODE>(dTmem, aL, bD, iDesc, acc);
-                                TcMma<MODE>(dTmem, aD, bL, iDesc, 1u);
-                                TcMma<MODE>(dTmem, aD, bD, iDesc, 1u);
+                        for (int j = 0; j < G; j++) {
+                            if (j < nb) {
+                                uint32_t aLo = aLo0 + stageOff + (uint32_t)j * (STAGE_BYTES >> 4);
+                                uint32_t bLo = bLo0 + stageOff + (uint32_t)j * (STAGE_BYTES >> 4);
+#pragma unroll
+                                for (int k = 0; k < KSTEPS; k++) {
+#ifdef NTB_WAIT_STATS
+                                    if (exp & 1)
+                                        continue;
+#endif
+                                    if (MODE == 0) {
+                                        TcMmaLH<MODE>(dTmem, aLo, aHiW, bLo, bHiW, iDesc, acc);
+                                    }
+                                    else {
+                                        constexpr uint32_t PLANE4 = PLANE_BYTES >> 4;
+                                        TcMmaLH<MODE>(dTmem, aLo + PLANE4, aHiW, bLo, bHiW, iDesc, acc);
+                                        TcMmaLH<MODE>(dTmem, aLo, aHiW, bLo + PLANE4, bHiW, iDesc, 1u);
+                                        TcMmaLH<MODE>(dTmem, aLo, aHiW, bLo, bHiW, iDesc, 1u);
+                                    }
+                                    acc = 1u;
+                                    aLo += aStep4;
+                                    bLo += bStep4;
+                                }
                             }
                         }
-                        TcCommit(SmemAddr(&barEmpty[s]));
-                        if (++s == STAGES) { s = 0; ph ^= 1u; }
+#ifdef NTB_WAIT_STATS
+                        if (exp & 8)
+                            MbarArrive(barEmpty0 + (uint32_t)s * 8u);
+                        else
+#endif
+                        TcCommit(barEmpty0 + (uint32_t)s * 8u);
+                        NTB_MARKK(2, kb);
+                        stageOff += (uint32_t)G * (STAGE_BYTES >> 4);
+                        if (++s == NSTG) { s = 0; ph ^= 1u; stageOff = 0; }
                     }
                     if (ok)
                         TcCommit(SmemAddr(&barTFull[buf]));
@@ -610,10 +876,11 @@ GemmTcKernel(const __grid_constant__ TcGroup grp)
         uint32_t it = 0;
         bool ok = true;
         TileWriter<OutT> writer;
-        writer.Init(smemBase + STAGES * STAGE_BYTES, sub, nullptr);
+        writer.Init(smemBase + STAGES * STAGE_BYTES, sub, nullptr, &barOldC[sub * 2], abortPtr, nullptr);
         for (int t = firstTile; ok && t < grp.total; t += tileStep) {
             NTB_SELECT_PROBLEM();
             writer.map = &tmC;
+            writer.status = p.status;
             TileCoord tc = DecodeTile(tl, p);
             const int row0 = tc.mBlk * BM + sub * 32;
             const int row = row0 + lane;
@@ -623,7 +890,9 @@ GemmTcKernel(const __grid_constant__ TcGroup grp)
             const int bc = BatchCoord(p.cSel, tc.prob, p);
             OutT * cRow = (OutT *)p.c + pp * p.sCp + qq * p.sCq + (long long)row * p.ldc;
             const bool rowOk = row < p.M;
+            writer.BeginTile(p, cRow + n0, row0, 0, 1, n0, BN, bc, lane);
             if (MODE == 0) {
+                writer.OldRequest(p, cRow, n0, rowOk);
                 /* one accumulator hand-over per tile: load 32 columns, scale, store */
                 const uint32_t buf = it & 1u;
                 ok = MbarWaitWarp(SmemAddr(&barTFull[buf]), (it >> 1) & 1u, abortPtr, p.status, (uint32_t)p.epiHint);
@@ -637,6 +906,9 @@ GemmTcKernel(const __grid_constant__ TcGroup grp)
                     const int c0 = n0 + ch * 64;
                     if (c0 >= p.N)
                         break;                     /* uniform across the warp */
+                    writer.OldAdvance();
+                    if (ch + 1 < BN / 64 && c0 + 64 < p.N)
+                        writer.OldRequest(p, cRow, c0 + 64, rowOk);
                     float v[64];
                     TmemLoad64(tRow + ch * 64, v);
                     writer.Put32(p, cRow, rowOk, row0, c0, bc, v, lane);
@@ -734,9 +1006,9 @@ GemmTcKernel(const __grid_constant__ TcGroup grp)
     /* ---------------------------------------------------------------- teardown */
 #ifdef NTB_WAIT_STATS
     if (lane == 0 && warp <= 1) {
-        if (warp == 0) { atomicAdd(&gWaitStats[0], (unsigned long long)wstat[0]); atomicAdd(&gWaitStats[5], 1ULL);
+        if (warp == 0) { atomicAdd(&gWaitStats[0], (unsigned long long)wstat[0]); atomicAdd(&gWaitStats[5], 1ULL); atomicAdd(&gWaitStats[6], (unsigned long long)wstat[6]); atomicAdd(&gWaitStats[7], (unsigned long long)wstat[7]); atomicAdd(&gWaitStats[3], (unsigned long long)wstat[3]); atomicAdd(&gWaitStats[2], (unsigned long long)wstat[5]);
                          if (blockIdx.x == 0) atomicAdd(&gWaitStats[4], (unsigned long long)(clock64() - kernelT0)); }
-        if (warp == 1) { atomicAdd(&gWaitStats[1], (unsigned long long)wstat[1]); atomicAdd(&gWaitStats[2], (unsigned long long)wstat[2]); }
+        if (warp == 1) { atomicAdd(&gWaitStats[1], (unsigned long long)wstat[1]); }
     }
 #endif
     __syncwarp();
@@ -755,7 +1027,7 @@ GemmTcKernel(const __grid_constant__ TcGroup grp)
 #ifdef NTB_WAIT_STATS
     if (threadIdx.x == 32) NTB_MARK(7);
     __syncthreads();
-    if (blockIdx.x == 0 && threadIdx.x < 16) gTimeline[threadIdx.x] = tlShared[threadIdx.x];
+    if (blockIdx.x == 0 && threadIdx.x < 64) gTimeline[threadIdx.x] = tlShared[threadIdx.x];
 #endif
 }
 
@@ -795,11 +1067,13 @@ __device__ __forceinline__ void TmaLoad3DPair(uint32_t dst, const CUtensorMap * 
                  :: "r"(dst), "l"(map), "r"(barCluster), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 
-__device__ __forceinline__ void TcMmaPair(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc, uint32_t iDesc, uint32_t accumulate)
+__device__ __forceinline__ void TcMmaPairLH(uint32_t dTmem, uint32_t aLo, uint32_t aHi, uint32_t bLo, uint32_t bHi,
+                                            uint32_t iDesc, uint32_t accumulate)
 {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 :: "r"(dTmem), "l"(aDesc), "l"(bDesc), "r"(iDesc), "r"(accumulate) : "memory");
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+                 "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n\t}"
+                 :: "r"(dTmem), "r"(aLo), "r"(aHi), "r"(bLo), "r"(bHi), "r"(iDesc), "r"(accumulate) : "memory");
 }
 
 /* arrive, once the MMAs issued so far have finished, on the barrier at this offset in
@@ -830,14 +1104,15 @@ __device__ __forceinline__ void TcCommitPair(uint32_t bar)
  * tcgen05.commit; tempty[buf] lives in the leader and collects the eight epilogue warps
  * of the pair. All waits are local and bounded as in the single-CTA kernel.
  */
-template <int MSUB, int STAGES, typename OutT>
+template <int MSUB, int BN, int STAGES, int G, typename OutT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, TcParams p)
 {
     constexpr int ES = 2;
     constexpr int EPR = ROW_BYTES / ES;                 /* 64 halves of K per stage */
-    constexpr int BN = 256;                             /* columns of the pair's tile */
+    constexpr int NSTG = STAGES / G;                    /* barrier pairs: G k-blocks share a hand-shake */
+    static_assert(STAGES % G == 0 && (BN == 256 || BN == 128), "pair tile");
     constexpr int BNH = BN / 2;                         /* columns of B this CTA loads */
     constexpr int PM = 2 * BM * MSUB;                   /* rows of the pair's tile */
     constexpr int NBUF = 2 / MSUB;                      /* accumulator sets that fit in TMEM */
@@ -852,6 +1127,7 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     __shared__ __align__(8) uint64_t barEmpty[STAGES];
     __shared__ __align__(8) uint64_t barTFull[2];
     __shared__ __align__(8) uint64_t barTEmpty[2];
+    __shared__ __align__(8) uint64_t barOldC[8];    /* per epilogue warp and staging box: old C values have landed */
     __shared__ uint32_t tmemBaseSlot;
     __shared__ int abortFlag;
 
@@ -880,6 +1156,8 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             MbarInit(SmemAddr(&barTFull[b]), 1);
             MbarInit(SmemAddr(&barTEmpty[b]), 8);
         }
+        for (int b = 0; b < 8; b++)
+            MbarInit(SmemAddr(&barOldC[b]), 1);
         abortFlag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -913,38 +1191,46 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 const int n0 = tc.nBlk * BN + (int)rank * BNH;
                 const int ba = BatchCoord(p.aSel, tc.prob, p);
                 const int bb = BatchCoord(p.bSel, tc.prob, p);
-                for (int kb = 0; kb < kBlocks; kb++) {
-                    NTB_TIMED(0, ok = MbarWait(SmemAddr(&barEmpty[s]), ph ^ 1u, abortPtr, p.status));
+                const bool aMN = p.aMN != 0, bMN = p.bMN != 0;
+                int * const status = p.status;
+                for (int kb = 0; kb < kBlocks; kb += G) {
+                    NTB_TIMED(0, ok = MbarWait(SmemAddr(&barEmpty[s]), ph ^ 1u, abortPtr, status));
                     if (!ok)
                         break;
                     const uint32_t fullLeader = MapToCta(SmemAddr(&barFull[s]), 0);
-                    const uint32_t aDst = smemBase + s * STAGE_BYTES;
-                    const uint32_t bDst = aDst + MSUB * A_TILE_BYTES;
-                    const int k0 = kb * EPR;
+                    const int nb = G == 1 ? 1 : (kBlocks - kb < G ? kBlocks - kb : G);
                     if (rank == 0)
-                        MbarExpectTx(SmemAddr(&barFull[s]), 2 * STAGE_BYTES);
+                        MbarExpectTx(SmemAddr(&barFull[s]), (uint32_t)nb * 2u * STAGE_BYTES);
 #pragma unroll
-                    for (int sub = 0; sub < MSUB; sub++) {
-                        const int ms = m0 + sub * 2 * BM;
-                        const uint32_t dst = aDst + sub * A_TILE_BYTES;
-                        if (!p.aMN) {
-                            TmaLoad3DPair(dst, &tmA, fullLeader, k0, ms, ba);
+                    for (int j = 0; j < G; j++) {
+                        if (j < nb) {
+                            const uint32_t aDst = smemBase + (uint32_t)(s * G + j) * STAGE_BYTES;
+                            const uint32_t bDst = aDst + MSUB * A_TILE_BYTES;
+                            const int k0 = (kb + j) * EPR;
+#pragma unroll
+                            for (int sub = 0; sub < MSUB; sub++) {
+                                const int ms = m0 + sub * 2 * BM;
+                                const uint32_t dst = aDst + sub * A_TILE_BYTES;
+                                if (!aMN) {
+                                    TmaLoad3DPair(dst, &tmA, fullLeader, k0, ms, ba);
+                                }
+                                else {
+#pragma unroll
+                                    for (int i = 0; i < BM / EPR; i++)
+                                        TmaLoad3DPair(dst + i * EPR * ROW_BYTES, &tmA, fullLeader, ms + i * EPR, k0, ba);
+                                }
+                            }
+                            if (!bMN) {
+                                TmaLoad3DPair(bDst, &tmB, fullLeader, k0, n0, bb);
+                            }
+                            else {
+#pragma unroll
+                                for (int i = 0; i < BNH / EPR; i++)
+                                    TmaLoad3DPair(bDst + i * EPR * ROW_BYTES, &tmB, fullLeader, n0 + i * EPR, k0, bb);
+                            }
                         }
-                        else {
-#pragma unroll
-                            for (int j = 0; j < BM / EPR; j++)
-                                TmaLoad3DPair(dst + j * EPR * ROW_BYTES, &tmA, fullLeader, ms + j * EPR, k0, ba);
-                        }
                     }
-                    if (!p.bMN) {
-                        TmaLoad3DPair(bDst, &tmB, fullLeader, k0, n0, bb);
-                    }
-                    else {
-#pragma unroll
-                        for (int j = 0; j < BNH / EPR; j++)
-                            TmaLoad3DPair(bDst + j * EPR * ROW_BYTES, &tmB, fullLeader, n0 + j * EPR, k0, bb);
-                    }
-                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                    if (++s == NSTG) { s = 0; ph ^= 1u; }
                 }
             }
         }
@@ -961,31 +1247,48 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             uint32_t ph = 0;
             uint32_t it = 0;
             bool ok = true;
+            int * const status = p.status;
+            /* descriptors of slot 0, k-step 0; in the loop only the start-address field moves */
+            const uint64_t aD0 = SmemDesc(smemBase, aLbo, 1024, 2);
+            const uint64_t bD0 = SmemDesc(smemBase + MSUB * A_TILE_BYTES, bLbo, 1024, 2);
+            const uint32_t aLo0 = (uint32_t)aD0, aHiW = (uint32_t)(aD0 >> 32);
+            const uint32_t bLo0 = (uint32_t)bD0, bHiW = (uint32_t)(bD0 >> 32);
+            const uint32_t aStep4 = aStep >> 4, bStep4 = bStep >> 4;
+            const uint32_t barFull0 = SmemAddr(&barFull[0]), barEmpty0 = SmemAddr(&barEmpty[0]);
+            uint32_t stageOff = 0;                /* s * G * STAGE_BYTES in 16-byte units */
             for (int t = firstTile; ok && t < p.totalTiles; t += tileStep, ++it) {
                 const uint32_t buf = it % NBUF;
-                NTB_TIMED(2, ok = MbarWait(SmemAddr(&barTEmpty[buf]), ((it / NBUF) & 1u) ^ 1u, abortPtr, p.status));
+                NTB_TIMED(2, ok = MbarWait(SmemAddr(&barTEmpty[buf]), ((it / NBUF) & 1u) ^ 1u, abortPtr, status));
                 if (!ok)
                     break;
                 TcFenceAfter();
                 const uint32_t dTmem = tmemBase + buf * (MSUB * BN);
-                for (int kb = 0; kb < kBlocks; kb++) {
-                    NTB_TIMED(1, ok = MbarWait(SmemAddr(&barFull[s]), ph, abortPtr, p.status));
+                uint32_t acc = 0u;
+                for (int kb = 0; kb < kBlocks; kb += G) {
+                    NTB_TIMED(1, ok = MbarWait(barFull0 + (uint32_t)s * 8u, ph, abortPtr, status));
                     if (!ok)
                         break;
                     TcFenceAfter();
-                    const uint32_t aT = smemBase + s * STAGE_BYTES;
-                    const uint32_t bT = aT + MSUB * A_TILE_BYTES;
+                    const int nb = G == 1 ? 1 : (kBlocks - kb < G ? kBlocks - kb : G);
 #pragma unroll
-                    for (int k = 0; k < KSTEPS; k++) {
-                        const uint64_t bD = SmemDesc(bT + k * bStep, bLbo, 1024, 2);
+                    for (int j = 0; j < G; j++) {
+                        if (j < nb) {
+                            uint32_t aLo = aLo0 + stageOff + (uint32_t)j * (STAGE_BYTES >> 4);
+                            uint32_t bLo = bLo0 + stageOff + (uint32_t)j * (STAGE_BYTES >> 4);
 #pragma unroll
-                        for (int sub = 0; sub < MSUB; sub++) {
-                            const uint64_t aD = SmemDesc(aT + sub * A_TILE_BYTES + k * aStep, aLbo, 1024, 2);
-                            TcMmaPair(dTmem + sub * BN, aD, bD, iDesc, (kb | k) != 0 ? 1u : 0u);
+                            for (int k = 0; k < KSTEPS; k++) {
+#pragma unroll
+                                for (int sub = 0; sub < MSUB; sub++)
+                                    TcMmaPairLH(dTmem + sub * BN, aLo + (uint32_t)sub * (A_TILE_BYTES >> 4), aHiW, bLo, bHiW, iDesc, acc);
+                                acc = 1u;
+                                aLo += aStep4;
+                                bLo += bStep4;
+                            }
                         }
                     }
-                    TcCommitPair(SmemAddr(&barEmpty[s]));
-                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                    TcCommitPair(barEmpty0 + (uint32_t)s * 8u);
+                    stageOff += (uint32_t)G * (STAGE_BYTES >> 4);
+                    if (++s == NSTG) { s = 0; ph ^= 1u; stageOff = 0; }
                 }
                 if (ok)
                     TcCommitPair(SmemAddr(&barTFull[buf]));
@@ -997,7 +1300,7 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         uint32_t it = 0;
         bool ok = true;
         TileWriter<OutT> writer;
-        writer.Init(smemBase + STAGES * STAGE_BYTES, sub32, &tmC);
+        writer.Init(smemBase + STAGES * STAGE_BYTES, sub32, &tmC, &barOldC[sub32 * 2], abortPtr, p.status);
         for (int t = firstTile; ok && t < p.totalTiles; t += tileStep, ++it) {
             TileCoord tc = DecodeTile(t, p);
             const int n0 = tc.nBlk * BN;
@@ -1006,6 +1309,12 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const int bc = BatchCoord(p.cSel, tc.prob, p);
             OutT * cBase = (OutT *)p.c + pp * p.sCp + qq * p.sCq;
             const uint32_t buf = it % NBUF;
+            writer.BeginTile(p, cBase + (long long)(tc.mBlk * PM + (int)rank * BM + sub32 * 32 + lane) * p.ldc + n0,
+                             tc.mBlk * PM + (int)rank * BM + sub32 * 32, 2 * BM, MSUB, n0, BN, bc, lane);
+            {
+                const int r0 = tc.mBlk * PM + (int)rank * BM + sub32 * 32 + lane;
+                writer.OldRequest(p, cBase + (long long)r0 * p.ldc, n0, r0 < p.M);
+            }
             NTB_TIMED(3, ok = MbarWaitWarp(SmemAddr(&barTFull[buf]), (it / NBUF) & 1u, abortPtr, p.status, (uint32_t)p.epiHint));
             if (!ok)
                 break;
@@ -1022,6 +1331,11 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     const int c0 = n0 + ch * 64;
                     if (c0 >= p.N)
                         break;
+                    writer.OldAdvance();
+                    if (ch + 1 < BN / 64 && c0 + 64 < p.N)
+                        writer.OldRequest(p, cRow, c0 + 64, rowOk);
+                    else if (sub + 1 < MSUB)
+                        writer.OldRequest(p, cRow + (long long)(2 * BM) * p.ldc, n0, row + 2 * BM < p.M);
                     float v[64];
                     TmemLoad64(tRow + ch * 64, v);
                     writer.Put32(p, cRow, rowOk, row0, c0, bc, v, lane);
@@ -1133,6 +1447,7 @@ GemmTcSplitKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     __shared__ __align__(8) uint64_t barEmpty[STAGES];
     __shared__ __align__(8) uint64_t barTFull[2];
     __shared__ __align__(8) uint64_t barTEmpty[2];
+    __shared__ __align__(8) uint64_t barOldC[8];    /* per epilogue warp and staging box: old C values have landed */
     __shared__ __align__(8) uint64_t barRecv[2];
     __shared__ uint32_t tmemBaseSlot;
     __shared__ int abortFlag;
@@ -1160,6 +1475,8 @@ GemmTcSplitKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             MbarInit(SmemAddr(&barTEmpty[b]), 4);
             MbarInit(SmemAddr(&barRecv[b]), (S - 1) * 4);
         }
+        for (int b = 0; b < 8; b++)
+            MbarInit(SmemAddr(&barOldC[b]), 1);
         abortFlag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -1261,7 +1578,7 @@ GemmTcSplitKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         uint32_t it = 0;
         bool ok = true;
         TileWriter<OutT> writer;
-        writer.Init(recvBase + RECV_BYTES, sub, &tmC);
+        writer.Init(recvBase + RECV_BYTES, sub, &tmC, &barOldC[sub * 2], abortPtr, p.status);
         for (int t = firstTile; ok && t < p.totalTiles; t += tileStep, ++it) {
             TileCoord tc = DecodeTile(t, p);
             const uint32_t buf = it & 1u;
@@ -1272,6 +1589,7 @@ GemmTcSplitKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             const int bc = BatchCoord(p.cSel, tc.prob, p);
             OutT * cRow = (OutT *)p.c + pp * p.sCp + qq * p.sCq + (long long)row * p.ldc;
             const bool rowOk = row < p.M;
+            writer.BeginTile(p, cRow + n0 + (int)rank * W, row0, 0, 1, n0 + (int)rank * W, W, bc, lane);
             ok = MbarWaitWarp(SmemAddr(&barTFull[buf]), (it >> 1) & 1u, abortPtr, p.status, (uint32_t)p.epiHint);
             if (!ok)
                 break;
@@ -1362,12 +1680,12 @@ bool BatchSelector(long long sp, long long sq, int P, int Q, int * sel, long lon
     return false;
 }
 
-template <int MODE, int BN, int STAGES, typename OutT>
+template <int MODE, int BN, int STAGES, int G, typename OutT>
 int LaunchOne(const TcGroup & grp, int smCount, cudaStream_t stream)
 {
     constexpr int stage = (A_TILE_BYTES + BN * ROW_BYTES) * (MODE == 0 ? 1 : 2);
     constexpr int smem = stage * STAGES + EPI_BYTES + 1024;
-    auto kern = GemmTcKernel<MODE, BN, STAGES, OutT>;
+    auto kern = GemmTcKernel<MODE, BN, STAGES, G, OutT>;
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1401,28 +1719,50 @@ int LaunchSplit(const CUtensorMap & tmA, const CUtensorMap & tmB, const CUtensor
     return cudaGetLastError() == cudaSuccess ? NTB_OK : NTB_ERR_CUDA;
 }
 
+/* integer tuning knob from the environment, read at every launch */
+int Knob(const char * name, int dflt)
+{
+    const char * v = getenv(name);
+    return v && *v ? atoi(v) : dflt;
+}
+
 /* single-CTA kernel for a group, chosen by operand mode, tile width and output type */
 int LaunchGroup(const TcGroup & grp, int mode, int bn, int dtC, int smCount, cudaStream_t stream)
 {
     if (mode == 0) {
         const bool half = dtC == NTB_X_FLOAT16;
-        if (bn == 256)
-            return half ? LaunchOne<0, 256, 4, __half>(grp, smCount, stream) : LaunchOne<0, 256, 4, float>(grp, smCount, stream);
-        if (bn == 128)
-            return half ? LaunchOne<0, 128, 6, __half>(grp, smCount, stream) : LaunchOne<0, 128, 6, float>(grp, smCount, stream);
-        return half ? LaunchOne<0, 64, 8, __half>(grp, smCount, stream) : LaunchOne<0, 64, 8, float>(grp, smCount, stream);
+        /* k-blocks per barrier hand-shake; the widest tile keeps one (its four MMAs already
+           cover the hand-shake) */
+        const int g = Knob("NTB_GROUP_K", bn == 256 ? 1 : 2);
+        if (bn == 256) {
+            if (g == 2)
+                return half ? LaunchOne<0, 256, 4, 2, __half>(grp, smCount, stream) : LaunchOne<0, 256, 4, 2, float>(grp, smCount, stream);
+            return half ? LaunchOne<0, 256, 4, 1, __half>(grp, smCount, stream) : LaunchOne<0, 256, 4, 1, float>(grp, smCount, stream);
+        }
+        if (bn == 128) {
+            if (g == 1)
+                return half ? LaunchOne<0, 128, 6, 1, __half>(grp, smCount, stream) : LaunchOne<0, 128, 6, 1, float>(grp, smCount, stream);
+            if (g == 3)
+                return half ? LaunchOne<0, 128, 6, 3, __half>(grp, smCount, stream) : LaunchOne<0, 128, 6, 3, float>(grp, smCount, stream);
+            return half ? LaunchOne<0, 128, 6, 2, __half>(grp, smCount, stream) : LaunchOne<0, 128, 6, 2, float>(grp, smCount, stream);
+        }
+        if (g == 1)
+            return half ? LaunchOne<0, 64, 8, 1, __half>(grp, smCount, stream) : LaunchOne<0, 64, 8, 1, float>(grp, smCount, stream);
+        if (g == 4)
+            return half ? LaunchOne<0, 64, 8, 4, __half>(grp, smCount, stream) : LaunchOne<0, 64, 8, 4, float>(grp, smCount, stream);
+        return half ? LaunchOne<0, 64, 8, 2, __half>(grp, smCount, stream) : LaunchOne<0, 64, 8, 2, float>(grp, smCount, stream);
     }
     if (bn == 128)
-        return LaunchOne<1, 128, 3, float>(grp, smCount, stream);
-    return LaunchOne<1, 64, 4, float>(grp, smCount, stream);
+        return LaunchOne<1, 128, 3, 1, float>(grp, smCount, stream);
+    return LaunchOne<1, 64, 4, 1, float>(grp, smCount, stream);
 }
 
-template <int MSUB, int STAGES, typename OutT>
+template <int MSUB, int BN, int STAGES, int G, typename OutT>
 int LaunchPair(const CUtensorMap & tmA, const CUtensorMap & tmB, const CUtensorMap & tmC, const TcParams & tp, int pairs,
                cudaStream_t stream)
 {
-    constexpr int smem = (MSUB * A_TILE_BYTES + 128 * ROW_BYTES) * STAGES + EPI_BYTES + 1024;
-    auto kern = GemmTcPairKernel<MSUB, STAGES, OutT>;
+    constexpr int smem = (MSUB * A_TILE_BYTES + (BN / 2) * ROW_BYTES) * STAGES + EPI_BYTES + 1024;
+    auto kern = GemmTcPairKernel<MSUB, BN, STAGES, G, OutT>;
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1479,25 +1819,35 @@ int EncodeOutput(CUtensorMap * map, int dtC, void * base, int rows, int cols, lo
     return r == CUDA_SUCCESS ? NTB_OK : NTB_ERR_CUDA;
 }
 
-/* integer tuning knob from the environment, read at every launch */
-int Knob(const char * name, int dflt)
+/*
+ * Cost model for the tile shape, in SM clocks: waves x (k-blocks x clocks per k-block +
+ * cost of starting and finishing one tile). A k-block costs the largest of
+ *   - its MMA time;
+ *   - the time its operand bytes take to arrive: an SM takes in about 62 bytes per clock,
+ *     and all SMs together about 5800 (what the L2-to-SM fabric delivered to TMA loads in
+ *     every kernel timed here), so the more CTAs run, the less each one gets;
+ *   - the time of the thread that issues the MMAs: about 47 clocks per instruction plus
+ *     about 400 (500 in a CTA pair) per barrier hand-shake, shared by the k-blocks of a group.
+ * Returns the tile width of the single-CTA kernel; 0 / -1 for the CTA-pair kernel with
+ * 256 x 256 / 512 x 256 tiles, -8 / -9 for pair tiles of 256 x 128 / 512 x 128; -2 / -4 for
+ * the split-K kernel with clusters of 2 / 4 CTAs. Constants were fitted to timings of the
+ * benchmark configurations and of mid-size products on a B200.
+ */
+struct KbCost {
+    double math, bytes, mmas, shake;
+    int g;
+};
+
+double PerKBlock(const KbCost & c, long long activeCtas)
 {
-    const char * v = getenv(name);
-    return v && *v ? atoi(v) : dflt;
+    const double perSm = 62.0, fabric = 5800.0;
+    const double ingest = fmin(perSm, fabric / (double)(activeCtas > 0 ? activeCtas : 1));
+    const double thread = (c.shake + 47.0 * c.mmas * c.g) / c.g;
+    return fmax(c.math, fmax(c.bytes / ingest, thread));
 }
 
-/*
- * Cost model for the tile shape, in SM clocks per CTA: waves x (k-blocks x clocks per
- * k-block + epilogue and hand-over cost of one tile). A k-block costs the larger of its MMA
- * time and the time its operand bytes take to arrive (an SM takes in about 60 bytes per
- * clock here, measured on the large product). Returns the tile width of the single-CTA
- * kernel, 0 / -1 for the CTA-pair kernel with 256 x 256 / 512 x 256 tiles, -2 / -4 for the
- * split-K kernel with clusters of 2 / 4 CTAs. Constants
- * were fitted to timings of the benchmark configurations on a B200.
- */
 int PickBN(const Problem & p, int smCount, int mode)
 {
-    const double ingest = 62.0;                       /* bytes per clock per SM */
     const int es = mode == 0 ? 2 : 4;
     const int kElems = ROW_BYTES / es;
     const double kBlocks = (double)((p.K + kElems - 1) / kElems);
@@ -1509,21 +1859,36 @@ int PickBN(const Problem & p, int smCount, int mode)
         const int bn = cand[i];
         const long long tiles = (long long)((p.M + BM - 1) / BM) * ((p.N + bn - 1) / bn) * p.count;
         const long long waves = (tiles + smCount - 1) / smCount;
-        const double perK = fmax(mmaPerCol * bn, (double)(BM + bn) * ROW_BYTES / ingest);
+        KbCost c;
+        c.math = mmaPerCol * bn;
+        c.bytes = (double)(BM + bn) * ROW_BYTES * (mode == 0 ? 1 : 1);
+        c.mmas = mode == 0 ? 4.0 : 12.0;
+        c.shake = 400.0;
+        c.g = (mode == 0 && bn != 256) ? 2 : 1;
+        const double perK = PerKBlock(c, tiles < smCount ? tiles : smCount);
         const double cost = (double)waves * (kBlocks * perK + 1500.0 + 4.0 * bn);
         if (cost < bestCost) { bestCost = cost; best = bn; }
     }
     if (mode == 0 && smCount >= 2) {
         const long long pairs = smCount / 2;
-        for (int msub = 1; msub <= 2; msub++) {
-            const int pm = 2 * BM * msub;
-            const long long tiles = (long long)((p.M + pm - 1) / pm) * ((p.N + 255) / 256) * p.count;
-            const long long waves = (tiles + pairs - 1) / pairs;
-            const double perK = fmax(512.0 * msub, (double)(msub * BM + 128) * ROW_BYTES / ingest);
-            /* the second accumulator set of the 512-row tile is not double-buffered: its
-               epilogue is exposed; pairs also pay for cluster start-up and hand-shakes */
-            const double cost = (double)waves * (kBlocks * perK + 2524.0 * msub + (msub == 2 ? 6000.0 : 0.0)) + 2000.0;
-            if (cost < bestCost) { bestCost = cost; best = msub == 1 ? 0 : -1; }
+        for (int w = 256; w >= 128; w -= 128) {
+            for (int msub = 1; msub <= 2; msub++) {
+                const int pm = 2 * BM * msub;
+                const long long tiles = (long long)((p.M + pm - 1) / pm) * ((p.N + w - 1) / w) * p.count;
+                const long long waves = (tiles + pairs - 1) / pairs;
+                KbCost c;
+                c.math = 2.0 * w * msub;
+                c.bytes = (double)(msub * BM + w / 2) * ROW_BYTES;
+                c.mmas = 4.0 * msub;
+                c.shake = 500.0;
+                c.g = w == 256 ? 1 : (msub == 1 ? 4 : 2);
+                const double perK = PerKBlock(c, 2 * (tiles < pairs ? tiles : pairs));
+                /* the second accumulator set of the 512-row tile is not double-buffered: its
+                   epilogue is exposed; pairs also pay for cluster start-up and hand-shakes */
+                const double perTile = (w == 256 ? 2524.0 : 1700.0) * msub + (msub == 2 ? (w == 256 ? 6000.0 : 3000.0) : 0.0);
+                const double cost = (double)waves * (kBlocks * perK + perTile) + 2000.0;
+                if (cost < bestCost) { bestCost = cost; best = (msub == 1 ? 0 : -1) - (w == 128 ? 8 : 0); }
+            }
         }
     }
     if (mode == 0) {
@@ -1535,7 +1900,13 @@ int PickBN(const Problem & p, int smCount, int mode)
             const long long tiles = (long long)((p.M + BM - 1) / BM) * ((p.N + 127) / 128) * p.count;
             const long long clusters = smCount / sp;
             const long long waves = (tiles + clusters - 1) / clusters;
-            const double perK = fmax(256.0, (double)(BM + 128) * ROW_BYTES / ingest);
+            KbCost c;
+            c.math = 256.0;
+            c.bytes = (double)(BM + 128) * ROW_BYTES;
+            c.mmas = 4.0;
+            c.shake = 400.0;
+            c.g = 1;
+            const double perK = PerKBlock(c, sp * (tiles < clusters ? tiles : clusters));
             const double cost = (double)waves * (ceil(kBlocks / sp) * perK + 2012.0 + 2500.0) + 2000.0;
             if (cost < bestCost) { bestCost = cost; best = -sp; }
         }
@@ -1597,6 +1968,7 @@ int Prepare(const DeviceCtx & ctx, const Problem & p, int mode, int bn, bool pai
     if (tp.group < 1)
         tp.group = 1;
     tp.epiHint = Knob("NTB_EPI_HINT_NS", 2000);
+    tp.cPrefetch = Knob("NTB_C_PREFETCH", 0);
     tp.fdPerProb.Set((uint32_t)(tp.tilesM * tp.tilesN));
     tp.fdBand.Set((uint32_t)(tp.group * tp.tilesN));
     tp.fdGroup.Set((uint32_t)tp.group);
@@ -1614,7 +1986,7 @@ int Prepare(const DeviceCtx & ctx, const Problem & p, int mode, int bn, bool pai
     int rc = EncodeOperand(&maps[0], mode, p.a, p.aMN, p.aRows, p.aCols, p.lda, stA, extA, BM);
     if (rc != NTB_OK)
         return rc;
-    rc = EncodeOperand(&maps[1], mode, p.b, p.bMN, p.bRows, p.bCols, p.ldb, stB, extB, pair ? 128 : bn);
+    rc = EncodeOperand(&maps[1], mode, p.b, p.bMN, p.bRows, p.bCols, p.ldb, stB, extB, pair ? bn / 2 : bn);
     if (rc != NTB_OK)
         return rc;
 
@@ -1647,23 +2019,33 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
     const int knobSplit = Knob("NTB_SPLIT_K", -1);  /* tuning: 0 forbids, 2 / 4 force the split-K kernel */
     if (mode == 0 && (knobSplit == 2 || knobSplit == 4) && (p.K + 63) / 64 >= knobSplit && ctx.smCount >= knobSplit)
         bn = -knobSplit;
-    if (bn <= -2 && (knobSplit == 0 || forced == NTB_ROUTE_TC_F16_PAIR)) {
+    const bool isSplit = bn == -2 || bn == -4;
+    if (isSplit && (knobSplit == 0 || forced == NTB_ROUTE_TC_F16_PAIR)) {
         Problem q = p;
         q.K = 64;                                   /* too short to split: re-ask the model */
         bn = PickBN(q, ctx.smCount, mode);
     }
     if (mode == 0 && forced == NTB_ROUTE_TC_F16_PAIR && ctx.smCount >= 2 && bn > 0)
         bn = Knob("NTB_PAIR_MSUB", 2) == 1 ? 0 : -1;
-    if (bn <= 0 && bn >= -1 && forced == NTB_ROUTE_TC_F16)
+    if ((bn == 0 || bn == -1 || bn == -8 || bn == -9) && forced == NTB_ROUTE_TC_F16)
         bn = 256;
-    const int split = bn <= -2 ? -bn : 0;
+    /* tuning: width of the pair tile (the model's choice otherwise) */
+    const int knobPairBN = Knob("NTB_PAIR_BN", 0);
+    if (knobPairBN == 128 && (bn == 0 || bn == -1))
+        bn -= 8;
+    if (knobPairBN == 256 && (bn == -8 || bn == -9))
+        bn += 8;
+    const int split = (bn == -2 || bn == -4) ? -bn : 0;
     if (split)
         bn = 128;
     const bool pair = bn <= 0;
-    const int msub = bn == -1 ? 2 : 1;
+    const int msub = (bn == -1 || bn == -9) ? 2 : 1;
     if (pair)
-        bn = 256;
+        bn = bn <= -8 ? 128 : 256;
     *route = mode != 0 ? NTB_ROUTE_TC_3XTF32 : pair ? NTB_ROUTE_TC_F16_PAIR : NTB_ROUTE_TC_F16;
+    if (Knob("NTB_DEBUG_CHOICE", 0))
+        fprintf(stderr, "ntb: M %d N %d K %d count %d -> %s width %d msub %d split %d\n", p.M, p.N, p.K, p.count,
+                pair ? "pair" : split ? "split-K" : "single", bn, msub, split);
 
     TcGroup grp;
     grp.n = 1;
@@ -1691,11 +2073,22 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
     if (pair) {
         const TcParams & tp = grp.p[0];
         const int pairs = (int)(tp.totalTiles < ctx.smCount / 2 ? tp.totalTiles : ctx.smCount / 2);
+        const bool half = p.dtC == NTB_X_FLOAT16;
+        /* k-blocks per barrier hand-shake: enough MMAs between two hand-shakes to cover one */
+        int g = Knob("NTB_PAIR_G", 0);
+        if (g == 0 && bn == 128 && msub == 1)
+            g = (p.K + 63) / 64 > 64 ? 2 : 4;     /* long K: keep four barrier stages in flight */
+#define NTB_PAIR(MS, W, ST, GG) (half ? LaunchPair<MS, W, ST, GG, __half>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, pairs, stream) \
+                                      : LaunchPair<MS, W, ST, GG, float>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, pairs, stream))
+        if (bn == 256) {
+            if (msub == 2)
+                return g == 2 ? NTB_PAIR(2, 256, 4, 2) : NTB_PAIR(2, 256, 4, 1);
+            return g == 2 ? NTB_PAIR(1, 256, 6, 2) : g == 3 ? NTB_PAIR(1, 256, 6, 3) : NTB_PAIR(1, 256, 6, 1);
+        }
         if (msub == 2)
-            return p.dtC == NTB_X_FLOAT16 ? LaunchPair<2, 4, __half>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, pairs, stream)
-                                          : LaunchPair<2, 4, float>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, pairs, stream);
-        return p.dtC == NTB_X_FLOAT16 ? LaunchPair<1, 6, __half>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, pairs, stream)
-                                      : LaunchPair<1, 6, float>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, pairs, stream);
+            return g == 1 ? NTB_PAIR(2, 128, 4, 1) : NTB_PAIR(2, 128, 4, 2);
+        return g == 1 ? NTB_PAIR(1, 128, 8, 1) : g == 2 ? NTB_PAIR(1, 128, 8, 2) : NTB_PAIR(1, 128, 8, 4);
+#undef NTB_PAIR
     }
     return LaunchGroup(grp, mode, bn, p.dtC, ctx.smCount, stream);
 }
@@ -1755,11 +2148,16 @@ extern "C" void ntb_debug_wait_stats(unsigned long long * out)
     cudaMemcpyToSymbol(gWaitStats, zero, sizeof(zero));
 }
 
+extern "C" void ntb_debug_set_exp(int v)
+{
+    cudaMemcpyToSymbol(gExp, &v, sizeof(int));
+}
+
 extern "C" void ntb_debug_timeline(unsigned long long * out)
 {
     cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out, gTimeline, sizeof(unsigned long long) * 16);
-    unsigned long long zero[16] = {0};
+    cudaMemcpyFromSymbol(out, gTimeline, sizeof(unsigned long long) * 64);
+    unsigned long long zero[64] = {0};
     cudaMemcpyToSymbol(gTimeline, zero, sizeof(zero));
 }
 #endif
