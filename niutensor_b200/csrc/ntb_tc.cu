@@ -261,7 +261,9 @@ __device__ __forceinline__ void StoreRow32Direct(OutT * cRow, int c0, const floa
 constexpr int EPI_BOX_BYTES = 32 * ROW_BYTES;               /* 32 rows x 128 B */
 constexpr int EPI_BYTES = 4 * 2 * EPI_BOX_BYTES;            /* four epilogue warps, two boxes each */
 
-template <typename OutT>
+/* OLDC: the kernel was built for products that read the old C (beta != 0); without it all
+   of that support compiles away, which keeps the epilogue of beta == 0 products short */
+template <typename OutT, bool OLDC>
 struct TileWriter {
     static constexpr int BOX_COLS = ROW_BYTES / (int)sizeof(OutT);   /* 64 halves / 32 floats */
     static constexpr int CHUNKS = 32 * (int)sizeof(OutT) / 16;      /* 16-byte chunks per 32 columns */
@@ -296,7 +298,7 @@ struct TileWriter {
        of its row that the next chunk needs in registers, requested one chunk ahead (the
        first chunk of a tile before the accumulator is waited for), so the memory latency
        of one chunk runs under the work on the chunk before it. */
-    static constexpr bool OLD_REGS = sizeof(OutT) == 2;
+    static constexpr bool OLD_REGS = OLDC && sizeof(OutT) == 2;
     uint4 oldCur[OLD_REGS ? 8 : 1], oldNxt[OLD_REGS ? 8 : 1];
     bool oldCurOk, oldNxtOk;
 
@@ -360,7 +362,7 @@ struct TileWriter {
                                               int col0, int cols, int batch, int lane)
     {
         fOn = false;
-        if (!p.cTma || p.beta == 0.f)
+        if (!OLDC || !p.cTma || p.beta == 0.f)
             return;
         int live = p.N - col0 < cols ? p.N - col0 : cols;
         fPerSub = live > 0 ? (live + BOX_COLS - 1) / BOX_COLS : 0;
@@ -579,7 +581,7 @@ struct TcGroup {
     const int chunkBlocks = MODE == 0 ? kBlocks : FP32_CHUNK_BLOCKS; \
     (void)chunkBlocks
 
-template <int MODE, int BN, int STAGES, int G, typename OutT>
+template <int MODE, int BN, int STAGES, int G, typename OutT, bool OLDC>
 __global__ void __launch_bounds__(MODE == 0 ? 192 : 192 + CONV_THREADS, 1)
 GemmTcKernel(const __grid_constant__ TcGroup grp)
 {
@@ -875,7 +877,7 @@ GemmTcKernel(const __grid_constant__ TcGroup grp)
         const int sub = warp & 3;                 /* TMEM sub-partition this warp may read */
         uint32_t it = 0;
         bool ok = true;
-        TileWriter<OutT> writer;
+        TileWriter<OutT, OLDC> writer;
         writer.Init(smemBase + STAGES * STAGE_BYTES, sub, nullptr, &barOldC[sub * 2], abortPtr, nullptr);
         for (int t = firstTile; ok && t < grp.total; t += tileStep) {
             NTB_SELECT_PROBLEM();
@@ -1104,7 +1106,7 @@ __device__ __forceinline__ void TcCommitPair(uint32_t bar)
  * tcgen05.commit; tempty[buf] lives in the leader and collects the eight epilogue warps
  * of the pair. All waits are local and bounded as in the single-CTA kernel.
  */
-template <int MSUB, int BN, int STAGES, int G, typename OutT>
+template <int MSUB, int BN, int STAGES, int G, typename OutT, bool OLDC>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, TcParams p)
@@ -1299,7 +1301,7 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int sub32 = warp & 3;
         uint32_t it = 0;
         bool ok = true;
-        TileWriter<OutT> writer;
+        TileWriter<OutT, OLDC> writer;
         writer.Init(smemBase + STAGES * STAGE_BYTES, sub32, &tmC, &barOldC[sub32 * 2], abortPtr, p.status);
         for (int t = firstTile; ok && t < p.totalTiles; t += tileStep, ++it) {
             TileCoord tc = DecodeTile(t, p);
@@ -1425,7 +1427,7 @@ __device__ __forceinline__ bool MbarWaitClusterWarp(uint32_t bar, uint32_t parit
  * receiver, because its own wait for tile i+1 needs the receiver's partials of tile i+1,
  * which the receiver's warp sends only after it has consumed tile i.
  */
-template <int S, int STAGES, typename OutT>
+template <int S, int STAGES, typename OutT, bool OLDC>
 __global__ void __cluster_dims__(S, 1, 1) __launch_bounds__(192, 1)
 GemmTcSplitKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmC, TcParams p)
@@ -1577,7 +1579,7 @@ GemmTcSplitKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const int rowInTile = sub * 32 + lane;
         uint32_t it = 0;
         bool ok = true;
-        TileWriter<OutT> writer;
+        TileWriter<OutT, OLDC> writer;
         writer.Init(recvBase + RECV_BYTES, sub, &tmC, &barOldC[sub * 2], abortPtr, p.status);
         for (int t = firstTile; ok && t < p.totalTiles; t += tileStep, ++it) {
             TileCoord tc = DecodeTile(t, p);
@@ -1680,12 +1682,12 @@ bool BatchSelector(long long sp, long long sq, int P, int Q, int * sel, long lon
     return false;
 }
 
-template <int MODE, int BN, int STAGES, int G, typename OutT>
+template <int MODE, int BN, int STAGES, int G, typename OutT, bool OLDC>
 int LaunchOne(const TcGroup & grp, int smCount, cudaStream_t stream)
 {
     constexpr int stage = (A_TILE_BYTES + BN * ROW_BYTES) * (MODE == 0 ? 1 : 2);
     constexpr int smem = stage * STAGES + EPI_BYTES + 1024;
-    auto kern = GemmTcKernel<MODE, BN, STAGES, G, OutT>;
+    auto kern = GemmTcKernel<MODE, BN, STAGES, G, OutT, OLDC>;
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1700,12 +1702,12 @@ int LaunchOne(const TcGroup & grp, int smCount, cudaStream_t stream)
     return cudaGetLastError() == cudaSuccess ? NTB_OK : NTB_ERR_CUDA;
 }
 
-template <int S, int STAGES, typename OutT>
+template <int S, int STAGES, typename OutT, bool OLDC>
 int LaunchSplit(const CUtensorMap & tmA, const CUtensorMap & tmB, const CUtensorMap & tmC, const TcParams & tp, int clusters,
                 cudaStream_t stream)
 {
     constexpr int smem = (A_TILE_BYTES + 128 * ROW_BYTES) * STAGES + 2 * (S - 1) * (BM * (128 / S) * 4) + EPI_BYTES + 1024;
-    auto kern = GemmTcSplitKernel<S, STAGES, OutT>;
+    auto kern = GemmTcSplitKernel<S, STAGES, OutT, OLDC>;
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1729,40 +1731,38 @@ int Knob(const char * name, int dflt)
 /* single-CTA kernel for a group, chosen by operand mode, tile width and output type */
 int LaunchGroup(const TcGroup & grp, int mode, int bn, int dtC, int smCount, cudaStream_t stream)
 {
+    /* kernels built with support for reading the old C only where a product asks for it */
+    const bool oldc = grp.p[0].beta != 0.f || (grp.n > 1 && grp.p[1].beta != 0.f);
+#define NTB_ONE(MD, W, ST, GG, T) (oldc ? LaunchOne<MD, W, ST, GG, T, true>(grp, smCount, stream) \
+                                        : LaunchOne<MD, W, ST, GG, T, false>(grp, smCount, stream))
     if (mode == 0) {
         const bool half = dtC == NTB_X_FLOAT16;
-        /* k-blocks per barrier hand-shake; the widest tile keeps one (its four MMAs already
-           cover the hand-shake) */
-        const int g = Knob("NTB_GROUP_K", bn == 256 ? 1 : 2);
-        if (bn == 256) {
-            if (g == 2)
-                return half ? LaunchOne<0, 256, 4, 2, __half>(grp, smCount, stream) : LaunchOne<0, 256, 4, 2, float>(grp, smCount, stream);
-            return half ? LaunchOne<0, 256, 4, 1, __half>(grp, smCount, stream) : LaunchOne<0, 256, 4, 1, float>(grp, smCount, stream);
-        }
+        /* k-blocks per barrier hand-shake: two, except for the widest tile, whose four MMAs
+           already cover a hand-shake (NTB_GROUP_K = 1 asks for one everywhere) */
+        const int g = Knob("NTB_GROUP_K", 0);
+        if (bn == 256)
+            return half ? NTB_ONE(0, 256, 4, 1, __half) : NTB_ONE(0, 256, 4, 1, float);
         if (bn == 128) {
             if (g == 1)
-                return half ? LaunchOne<0, 128, 6, 1, __half>(grp, smCount, stream) : LaunchOne<0, 128, 6, 1, float>(grp, smCount, stream);
-            if (g == 3)
-                return half ? LaunchOne<0, 128, 6, 3, __half>(grp, smCount, stream) : LaunchOne<0, 128, 6, 3, float>(grp, smCount, stream);
-            return half ? LaunchOne<0, 128, 6, 2, __half>(grp, smCount, stream) : LaunchOne<0, 128, 6, 2, float>(grp, smCount, stream);
+                return half ? NTB_ONE(0, 128, 6, 1, __half) : NTB_ONE(0, 128, 6, 1, float);
+            return half ? NTB_ONE(0, 128, 6, 2, __half) : NTB_ONE(0, 128, 6, 2, float);
         }
         if (g == 1)
-            return half ? LaunchOne<0, 64, 8, 1, __half>(grp, smCount, stream) : LaunchOne<0, 64, 8, 1, float>(grp, smCount, stream);
-        if (g == 4)
-            return half ? LaunchOne<0, 64, 8, 4, __half>(grp, smCount, stream) : LaunchOne<0, 64, 8, 4, float>(grp, smCount, stream);
-        return half ? LaunchOne<0, 64, 8, 2, __half>(grp, smCount, stream) : LaunchOne<0, 64, 8, 2, float>(grp, smCount, stream);
+            return half ? NTB_ONE(0, 64, 8, 1, __half) : NTB_ONE(0, 64, 8, 1, float);
+        return half ? NTB_ONE(0, 64, 8, 2, __half) : NTB_ONE(0, 64, 8, 2, float);
     }
     if (bn == 128)
-        return LaunchOne<1, 128, 3, 1, float>(grp, smCount, stream);
-    return LaunchOne<1, 64, 4, 1, float>(grp, smCount, stream);
+        return NTB_ONE(1, 128, 3, 1, float);
+    return NTB_ONE(1, 64, 4, 1, float);
+#undef NTB_ONE
 }
 
-template <int MSUB, int BN, int STAGES, int G, typename OutT>
+template <int MSUB, int BN, int STAGES, int G, typename OutT, bool OLDC>
 int LaunchPair(const CUtensorMap & tmA, const CUtensorMap & tmB, const CUtensorMap & tmC, const TcParams & tp, int pairs,
                cudaStream_t stream)
 {
     constexpr int smem = (MSUB * A_TILE_BYTES + (BN / 2) * ROW_BYTES) * STAGES + EPI_BYTES + 1024;
-    auto kern = GemmTcPairKernel<MSUB, BN, STAGES, G, OutT>;
+    auto kern = GemmTcPairKernel<MSUB, BN, STAGES, G, OutT, OLDC>;
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -2064,11 +2064,13 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
         const TcParams & tp = grp.p[0];
         const int clusters = (int)(tp.totalTiles < ctx.smCount / split ? tp.totalTiles : ctx.smCount / split);
         const bool half = p.dtC == NTB_X_FLOAT16;
+        const bool oldc = tp.beta != 0.f;
+#define NTB_SPLIT(SS, ST, T) (oldc ? LaunchSplit<SS, ST, T, true>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, clusters, stream) \
+                                   : LaunchSplit<SS, ST, T, false>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, clusters, stream))
         if (split == 2)
-            return half ? LaunchSplit<2, 4, __half>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, clusters, stream)
-                        : LaunchSplit<2, 4, float>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, clusters, stream);
-        return half ? LaunchSplit<4, 3, __half>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, clusters, stream)
-                    : LaunchSplit<4, 3, float>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, clusters, stream);
+            return half ? NTB_SPLIT(2, 4, __half) : NTB_SPLIT(2, 4, float);
+        return half ? NTB_SPLIT(4, 3, __half) : NTB_SPLIT(4, 3, float);
+#undef NTB_SPLIT
     }
     if (pair) {
         const TcParams & tp = grp.p[0];
@@ -2078,16 +2080,16 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
         int g = Knob("NTB_PAIR_G", 0);
         if (g == 0 && bn == 128 && msub == 1)
             g = (p.K + 63) / 64 > 64 ? 2 : 4;     /* long K: keep four barrier stages in flight */
-#define NTB_PAIR(MS, W, ST, GG) (half ? LaunchPair<MS, W, ST, GG, __half>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, pairs, stream) \
-                                      : LaunchPair<MS, W, ST, GG, float>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, pairs, stream))
-        if (bn == 256) {
-            if (msub == 2)
-                return g == 2 ? NTB_PAIR(2, 256, 4, 2) : NTB_PAIR(2, 256, 4, 1);
-            return g == 2 ? NTB_PAIR(1, 256, 6, 2) : g == 3 ? NTB_PAIR(1, 256, 6, 3) : NTB_PAIR(1, 256, 6, 1);
-        }
+        const bool oldc = tp.beta != 0.f;
+#define NTB_PAIR2(MS, W, ST, GG, T) (oldc ? LaunchPair<MS, W, ST, GG, T, true>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, pairs, stream) \
+                                          : LaunchPair<MS, W, ST, GG, T, false>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, pairs, stream))
+#define NTB_PAIR(MS, W, ST, GG) (half ? NTB_PAIR2(MS, W, ST, GG, __half) : NTB_PAIR2(MS, W, ST, GG, float))
+        if (bn == 256)
+            return msub == 2 ? NTB_PAIR(2, 256, 4, 1) : NTB_PAIR(1, 256, 6, 1);
         if (msub == 2)
-            return g == 1 ? NTB_PAIR(2, 128, 4, 1) : NTB_PAIR(2, 128, 4, 2);
-        return g == 1 ? NTB_PAIR(1, 128, 8, 1) : g == 2 ? NTB_PAIR(1, 128, 8, 2) : NTB_PAIR(1, 128, 8, 4);
+            return NTB_PAIR(2, 128, 4, 2);
+        return g == 2 ? NTB_PAIR(1, 128, 8, 2) : NTB_PAIR(1, 128, 8, 4);
+#undef NTB_PAIR2
 #undef NTB_PAIR
     }
     return LaunchGroup(grp, mode, bn, p.dtC, ctx.smCount, stream);
