@@ -42,8 +42,8 @@ FLOPS_PER_RANK = 2.0 * N_DIM * N_DIM * N_DIM
 # algorithmic bytes of one launch: read A, B and C0 once, write C once (fp16)
 BYTES_PER_RANK = 4.0 * N_DIM * N_DIM * 2
 # DRAM traffic of one launch measured by ncu (dram__bytes_read.sum + dram__bytes_write.sum),
-# profiles/gemm_f16_8192_ncu.md (CTA-pair kernel 256 x 256, this shape; the 512 x 256 variant moves 1.091e9)
-NCU_TRAFFIC_BYTES = 1.326e9
+# profiles/gemm_f16_8192_ncu.md (CTA-pair kernel with 512 x 256 tiles, the one this shape runs on)
+NCU_TRAFFIC_BYTES = 1.075e9
 
 
 def load_peaks():
