@@ -228,12 +228,19 @@ def main():
     ap.add_argument("--iters", type=int, default=60)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--cublas", action="store_true")
+    ap.add_argument("--shapes", default="",
+                    help="extra fp16 products M x N x K (a row-major, b stored N x K, beta 0), e.g. 4096x512x2048,2048x1024x4096")
     args = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("no CUDA device; this path has no CPU implementation")
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    for name in args.configs.split(","):
+    names = [n for n in args.configs.split(",") if n]
+    for shape in [x for x in args.shapes.split(",") if x]:
+        M, N, K = (int(v) for v in shape.lower().split("x"))
+        CONFIGS[shape] = (torch.float16, 1, M, N, K, X_NOTRANS, X_TRANS, 1.0, 0.0, "tensor", "fp16 " + shape)
+        names.append(shape)
+    for name in names:
         if name == "4lsm":
             print(json.dumps(run_output_layer(args.iters, not args.no_graph, args.cublas, dev)), flush=True)
             continue
