@@ -3,17 +3,24 @@
  * tcgen05.mma with accumulators in tensor memory (TMEM) and operands brought into
  * 128-byte-swizzled shared memory by TMA (cp.async.bulk.tensor, no cluster multicast).
  *
- *   warp 0      TMA producer: one lane arms full[s] with the stage's byte count and
- *               issues the A and B boxes of k-block kb into stage s.
+ *   warp 0      TMA producer: one lane arms full[s] with the byte count of a group of
+ *               G k-blocks and issues their A and B boxes into the G slots of stage s.
  *   warp 1      owns TMEM (tcgen05.alloc / dealloc); one lane issues the tcgen05.mma
- *               instructions of a stage and commits them to empty[s]; after the last
- *               k-block of a tile it commits to tfull[buf].
+ *               instructions of the group and commits them to empty[s]; after the last
+ *               k-block of a tile it commits to tfull[buf]. G > 1 because this lane
+ *               waits about 200 clocks for the answer to a barrier probe issued behind
+ *               tensor-core instructions: per hand-shake it spends 300-400 clocks that
+ *               only enough MMAs between two hand-shakes can cover. Its loop touches no
+ *               kernel parameter and moves each shared-memory descriptor with one add.
  *   warps 2-5   epilogue: tcgen05.ld of the finished accumulator (each warp reads the 32
  *               TMEM lanes of its sub-partition), alpha / beta / bias / rectifier in
  *               fp32, cast, staging in swizzled shared memory and TMA stores to C (direct
  *               stores when C is not 16-byte aligned), then release of the accumulator
  *               through tempty[buf]. Two accumulators alternate, so the epilogue of tile
- *               i overlaps the main loop of tile i+1.
+ *               i overlaps the main loop of tile i+1. Old values of C (beta != 0) come by
+ *               TMA load into the staging boxes (narrow tiles) or are requested one
+ *               64-column chunk ahead into registers (wide tiles); kernels for
+ *               beta == 0 are instantiated without any of that.
  *   warps 6-9   (fp32 inputs only) split every fp32 operand value x in shared memory
  *               into hi = tf32(x) and lo = x - hi; the MMA lane then issues three
  *               kind::tf32 products per k-step, lo*hi + hi*lo + hi*hi, small terms first.
@@ -1427,7 +1434,7 @@ __device__ __forceinline__ bool MbarWaitClusterWarp(uint32_t bar, uint32_t parit
  * receiver, because its own wait for tile i+1 needs the receiver's partials of tile i+1,
  * which the receiver's warp sends only after it has consumed tile i.
  */
-template <int S, int STAGES, typename OutT, bool OLDC>
+template <int S, int STAGES, int G, typename OutT, bool OLDC>
 __global__ void __cluster_dims__(S, 1, 1) __launch_bounds__(192, 1)
 GemmTcSplitKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmC, TcParams p)
@@ -1442,7 +1449,8 @@ GemmTcSplitKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     constexpr int KSTEPS = ROW_BYTES / UMMA_K_BYTES;
     constexpr int SLOT_BYTES = BM * W * 4;              /* one sender's slice: 128 rows x W floats */
     constexpr int RECV_BYTES = 2 * (S - 1) * SLOT_BYTES;
-    static_assert(S == 2 || S == 4, "cluster size");
+    constexpr int NSTG = STAGES / G;                    /* barrier pairs: G k-blocks share a hand-shake */
+    static_assert((S == 2 || S == 4) && STAGES % G == 0, "cluster size, k-blocks per hand-shake");
 
     extern __shared__ uint8_t smemRaw[];
     __shared__ __align__(8) uint64_t barFull[STAGES];
@@ -1508,32 +1516,40 @@ GemmTcSplitKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 const int m0 = tc.mBlk * BM, n0 = tc.nBlk * BN;
                 const int ba = BatchCoord(p.aSel, tc.prob, p);
                 const int bb = BatchCoord(p.bSel, tc.prob, p);
-                for (int kb = kbLo; kb < kbHi; kb++) {
-                    ok = MbarWait(SmemAddr(&barEmpty[s]), ph ^ 1u, abortPtr, p.status);
+                const bool aMN = p.aMN != 0, bMN = p.bMN != 0;
+                int * const status = p.status;
+                for (int kb = kbLo; kb < kbHi; kb += G) {
+                    ok = MbarWait(SmemAddr(&barEmpty[s]), ph ^ 1u, abortPtr, status);
                     if (!ok)
                         break;
                     const uint32_t full = SmemAddr(&barFull[s]);
-                    const uint32_t aDst = smemBase + s * STAGE_BYTES;
-                    const uint32_t bDst = aDst + A_TILE_BYTES;
-                    const int k0 = kb * EPR;
-                    MbarExpectTx(full, STAGE_BYTES);
-                    if (!p.aMN) {
-                        TmaLoad3D(aDst, &tmA, full, k0, m0, ba);
-                    }
-                    else {
+                    const int nb = G == 1 ? 1 : (kbHi - kb < G ? kbHi - kb : G);
+                    MbarExpectTx(full, (uint32_t)nb * STAGE_BYTES);
 #pragma unroll
-                        for (int j = 0; j < BM / EPR; j++)
-                            TmaLoad3D(aDst + j * EPR * ROW_BYTES, &tmA, full, m0 + j * EPR, k0, ba);
-                    }
-                    if (!p.bMN) {
-                        TmaLoad3D(bDst, &tmB, full, k0, n0, bb);
-                    }
-                    else {
+                    for (int j = 0; j < G; j++) {
+                        if (j < nb) {
+                            const uint32_t aDst = smemBase + (uint32_t)(s * G + j) * STAGE_BYTES;
+                            const uint32_t bDst = aDst + A_TILE_BYTES;
+                            const int k0 = (kb + j) * EPR;
+                            if (!aMN) {
+                                TmaLoad3D(aDst, &tmA, full, k0, m0, ba);
+                            }
+                            else {
 #pragma unroll
-                        for (int j = 0; j < BN / EPR; j++)
-                            TmaLoad3D(bDst + j * EPR * ROW_BYTES, &tmB, full, n0 + j * EPR, k0, bb);
+                                for (int i = 0; i < BM / EPR; i++)
+                                    TmaLoad3D(aDst + i * EPR * ROW_BYTES, &tmA, full, m0 + i * EPR, k0, ba);
+                            }
+                            if (!bMN) {
+                                TmaLoad3D(bDst, &tmB, full, k0, n0, bb);
+                            }
+                            else {
+#pragma unroll
+                                for (int i = 0; i < BN / EPR; i++)
+                                    TmaLoad3D(bDst + i * EPR * ROW_BYTES, &tmB, full, n0 + i * EPR, k0, bb);
+                            }
+                        }
                     }
-                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                    if (++s == NSTG) { s = 0; ph ^= 1u; }
                 }
             }
         }
@@ -1548,26 +1564,45 @@ GemmTcSplitKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             int s = 0;
             uint32_t ph = 0, it = 0;
             bool ok = true;
+            int * const status = p.status;
+            const uint64_t aD0 = SmemDesc(smemBase, aLbo, 1024, 2);
+            const uint64_t bD0 = SmemDesc(smemBase + A_TILE_BYTES, bLbo, 1024, 2);
+            const uint32_t aLo0 = (uint32_t)aD0, aHiW = (uint32_t)(aD0 >> 32);
+            const uint32_t bLo0 = (uint32_t)bD0, bHiW = (uint32_t)(bD0 >> 32);
+            const uint32_t aStep4 = aStep >> 4, bStep4 = bStep >> 4;
+            const uint32_t barFull0 = SmemAddr(&barFull[0]), barEmpty0 = SmemAddr(&barEmpty[0]);
+            uint32_t stageOff = 0;
             for (int t = firstTile; ok && t < p.totalTiles; t += tileStep, ++it) {
                 const uint32_t buf = it & 1u;
-                ok = MbarWait(SmemAddr(&barTEmpty[buf]), ((it >> 1) & 1u) ^ 1u, abortPtr, p.status);
+                ok = MbarWait(SmemAddr(&barTEmpty[buf]), ((it >> 1) & 1u) ^ 1u, abortPtr, status);
                 if (!ok)
                     break;
                 TcFenceAfter();
                 const uint32_t dTmem = tmemBase + buf * BN;
-                for (int kb = kbLo; kb < kbHi; kb++) {
-                    ok = MbarWait(SmemAddr(&barFull[s]), ph, abortPtr, p.status);
+                uint32_t acc = 0u;
+                for (int kb = kbLo; kb < kbHi; kb += G) {
+                    ok = MbarWait(barFull0 + (uint32_t)s * 8u, ph, abortPtr, status);
                     if (!ok)
                         break;
                     TcFenceAfter();
-                    const uint32_t aT = smemBase + s * STAGE_BYTES;
-                    const uint32_t bT = aT + A_TILE_BYTES;
+                    const int nb = G == 1 ? 1 : (kbHi - kb < G ? kbHi - kb : G);
 #pragma unroll
-                    for (int k = 0; k < KSTEPS; k++)
-                        TcMma<0>(dTmem, SmemDesc(aT + k * aStep, aLbo, 1024, 2), SmemDesc(bT + k * bStep, bLbo, 1024, 2),
-                                 iDesc, (kb != kbLo || k != 0) ? 1u : 0u);
-                    TcCommit(SmemAddr(&barEmpty[s]));
-                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                    for (int j = 0; j < G; j++) {
+                        if (j < nb) {
+                            uint32_t aLo = aLo0 + stageOff + (uint32_t)j * (STAGE_BYTES >> 4);
+                            uint32_t bLo = bLo0 + stageOff + (uint32_t)j * (STAGE_BYTES >> 4);
+#pragma unroll
+                            for (int k = 0; k < KSTEPS; k++) {
+                                TcMmaLH<0>(dTmem, aLo, aHiW, bLo, bHiW, iDesc, acc);
+                                acc = 1u;
+                                aLo += aStep4;
+                                bLo += bStep4;
+                            }
+                        }
+                    }
+                    TcCommit(barEmpty0 + (uint32_t)s * 8u);
+                    stageOff += (uint32_t)G * (STAGE_BYTES >> 4);
+                    if (++s == NSTG) { s = 0; ph ^= 1u; stageOff = 0; }
                 }
                 if (ok)
                     TcCommit(SmemAddr(&barTFull[buf]));
@@ -1702,12 +1737,12 @@ int LaunchOne(const TcGroup & grp, int smCount, cudaStream_t stream)
     return cudaGetLastError() == cudaSuccess ? NTB_OK : NTB_ERR_CUDA;
 }
 
-template <int S, int STAGES, typename OutT, bool OLDC>
+template <int S, int STAGES, int G, typename OutT, bool OLDC>
 int LaunchSplit(const CUtensorMap & tmA, const CUtensorMap & tmB, const CUtensorMap & tmC, const TcParams & tp, int clusters,
                 cudaStream_t stream)
 {
     constexpr int smem = (A_TILE_BYTES + 128 * ROW_BYTES) * STAGES + 2 * (S - 1) * (BM * (128 / S) * 4) + EPI_BYTES + 1024;
-    auto kern = GemmTcSplitKernel<S, STAGES, OutT, OLDC>;
+    auto kern = GemmTcSplitKernel<S, STAGES, G, OutT, OLDC>;
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1791,10 +1826,12 @@ int EncodeOperand(CUtensorMap * map, int mode, const void * base, int mnMajor, i
        MN-major: the stored row is M (or N) -> box = 128 bytes of MN x one stage of K rows. */
     cuuint32_t box[3] = { (cuuint32_t)epr, (cuuint32_t)(mnMajor ? epr : tileRows), 1 };
     cuuint32_t estr[3] = { 1, 1, 1 };
+    const int promo = Knob("NTB_L2_PROMOTION", 3);   /* tuning: L2 fetch granularity of operand loads */
     CUresult r = enc(map, mode == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
                      3, (void *)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      (mode != 0 && mnMajor) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
-                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     promo == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE : promo == 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+                     : promo == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B : CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? NTB_OK : NTB_ERR_CUDA;
 }
@@ -1881,7 +1918,7 @@ int PickBN(const Problem & p, int smCount, int mode)
                 c.bytes = (double)(msub * BM + w / 2) * ROW_BYTES;
                 c.mmas = 4.0 * msub;
                 c.shake = 500.0;
-                c.g = w == 256 ? 1 : (msub == 1 ? 4 : 2);
+                c.g = w == 256 ? 1 : 2;
                 const double perK = PerKBlock(c, 2 * (tiles < pairs ? tiles : pairs));
                 /* the second accumulator set of the 512-row tile is not double-buffered: its
                    epilogue is exposed; pairs also pay for cluster start-up and hand-shakes */
@@ -2065,11 +2102,15 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
         const int clusters = (int)(tp.totalTiles < ctx.smCount / split ? tp.totalTiles : ctx.smCount / split);
         const bool half = p.dtC == NTB_X_FLOAT16;
         const bool oldc = tp.beta != 0.f;
-#define NTB_SPLIT(SS, ST, T) (oldc ? LaunchSplit<SS, ST, T, true>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, clusters, stream) \
-                                   : LaunchSplit<SS, ST, T, false>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, clusters, stream))
-        if (split == 2)
-            return half ? NTB_SPLIT(2, 4, __half) : NTB_SPLIT(2, 4, float);
-        return half ? NTB_SPLIT(4, 3, __half) : NTB_SPLIT(4, 3, float);
+#define NTB_SPLIT(SS, ST, GG, T) (oldc ? LaunchSplit<SS, ST, GG, T, true>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, clusters, stream) \
+                                       : LaunchSplit<SS, ST, GG, T, false>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, clusters, stream))
+        const int sg = Knob("NTB_SPLIT_G", 2);
+        if (split == 2) {
+            if (sg == 1)
+                return half ? NTB_SPLIT(2, 4, 1, __half) : NTB_SPLIT(2, 4, 1, float);
+            return half ? NTB_SPLIT(2, 4, 2, __half) : NTB_SPLIT(2, 4, 2, float);
+        }
+        return half ? NTB_SPLIT(4, 3, 1, __half) : NTB_SPLIT(4, 3, 1, float);
 #undef NTB_SPLIT
     }
     if (pair) {
@@ -2077,9 +2118,9 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
         const int pairs = (int)(tp.totalTiles < ctx.smCount / 2 ? tp.totalTiles : ctx.smCount / 2);
         const bool half = p.dtC == NTB_X_FLOAT16;
         /* k-blocks per barrier hand-shake: enough MMAs between two hand-shakes to cover one */
-        int g = Knob("NTB_PAIR_G", 0);
-        if (g == 0 && bn == 128 && msub == 1)
-            g = (p.K + 63) / 64 > 64 ? 2 : 4;     /* long K: keep four barrier stages in flight */
+        /* 256 x 128 tiles: two k-blocks per hand-shake keep four barrier stages in flight;
+           four (NTB_PAIR_G = 4) gain a few per cent on short K and lose more on long K */
+        const int g = Knob("NTB_PAIR_G", 2);
         const bool oldc = tp.beta != 0.f;
 #define NTB_PAIR2(MS, W, ST, GG, T) (oldc ? LaunchPair<MS, W, ST, GG, T, true>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, pairs, stream) \
                                           : LaunchPair<MS, W, ST, GG, T, false>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, pairs, stream))
@@ -2088,7 +2129,7 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
             return msub == 2 ? NTB_PAIR(2, 256, 4, 1) : NTB_PAIR(1, 256, 6, 1);
         if (msub == 2)
             return NTB_PAIR(2, 128, 4, 2);
-        return g == 2 ? NTB_PAIR(1, 128, 8, 2) : NTB_PAIR(1, 128, 8, 4);
+        return g == 4 ? NTB_PAIR(1, 128, 8, 4) : NTB_PAIR(1, 128, 8, 2);
 #undef NTB_PAIR2
 #undef NTB_PAIR
     }
