@@ -212,16 +212,23 @@ def test_forced_ffma_route_matches_tensor_core_route(oracle):
     status_ok()
 
 
-@pytest.mark.parametrize("msub", ["1", "2"])
-def test_cta_pair_route(msub, oracle):
-    """The cta_group::2 kernel, forced on shapes the cost model would give to one CTA:
-    ragged edges in M, N and K, every transposition, batches, alpha/beta, fp32 output."""
-    rng = np.random.default_rng(300 + int(msub))
+@pytest.mark.parametrize("variant", ["256/1", "256/2", "128/1/2", "128/1/4", "128/2"])
+def test_cta_pair_route(variant, oracle):
+    """The cta_group::2 kernels (pair tile width / A sub-tiles per CTA / k-blocks per barrier
+    hand-shake), forced on shapes the cost model would give to one CTA: ragged edges in M, N
+    and K (K tails shorter than a hand-shake group), every transposition, batches, alpha/beta
+    (old C by TMA load for the narrow tile, from registers for the wide one), fp32 output."""
+    parts = variant.split("/")
+    width, msub = parts[0], parts[1]
+    rng = np.random.default_rng(300 + int(msub) + int(width))
     L = capi.lib()
     os.environ["NTB_PAIR_MSUB"] = msub
+    os.environ["NTB_PAIR_BN"] = width
+    if len(parts) > 2:
+        os.environ["NTB_PAIR_G"] = parts[2]
     assert L.ntb_set_route(capi.ROUTE_TC_F16_PAIR) == capi.OK
     try:
-        shapes = [(256, 256, 64), (520, 264, 136), (136, 304, 72), (1024, 512, 320), (8, 8, 8)]
+        shapes = [(256, 256, 64), (520, 264, 136), (136, 304, 72), (1024, 512, 320), (8, 8, 8), (304, 200, 1096)]
         n = 0
         for tA in (X_TRANS, X_NOTRANS):
             for tB in (X_TRANS, X_NOTRANS):
@@ -240,15 +247,54 @@ def test_cta_pair_route(msub, oracle):
                     assert err <= 2e-3, (M, N, K, tA, tB, alpha, beta, err)
     finally:
         L.ntb_set_route(0)
-        os.environ.pop("NTB_PAIR_MSUB", None)
+        for k in ("NTB_PAIR_MSUB", "NTB_PAIR_BN", "NTB_PAIR_G"):
+            os.environ.pop(k, None)
     status_ok()
 
 
-@pytest.mark.parametrize("split", ["2", "4"])
+@pytest.mark.parametrize("bn", ["64", "128", "256"])
+@pytest.mark.parametrize("group", ["1", "2"])
+def test_single_cta_tile_widths_and_hand_shake_groups(bn, group, oracle):
+    """Every tile width of the single-CTA fp16 kernel with one and two k-blocks per barrier
+    hand-shake: K that ends inside a group, ragged M and N, transpositions, batches,
+    alpha/beta with half and float outputs."""
+    rng = np.random.default_rng(900 + int(bn) + int(group))
+    L = capi.lib()
+    os.environ.update({"NTB_BN": bn, "NTB_GROUP_K": group, "NTB_SPLIT_K": "0"})
+    assert L.ntb_set_route(capi.ROUTE_TC_F16) == capi.OK
+    try:
+        shapes = [(128, 64, 64), (200, 136, 72), (72, 264, 192), (384, 320, 1096), (8, 520, 136)]
+        n = 0
+        for tA in (X_TRANS, X_NOTRANS):
+            for tB in (X_TRANS, X_NOTRANS):
+                for (M, N, K) in shapes:
+                    alpha, beta = AB[n % len(AB)]
+                    n += 1
+                    cnt = 1 + n % 3
+                    a = round_to_half(stored(rng, (cnt,), M, K, tA))
+                    b = round_to_half(stored(rng, (cnt,), K, N, tB))
+                    c0 = round_to_half(rng.normal(size=(cnt, M, N)).astype(np.float32))
+                    out_dtype = torch.float32 if n % 4 == 0 else torch.float16
+                    c = to_dev(c0, out_dtype)
+                    ops._MatrixMulBatched(to_dev(a, torch.float16), tA, to_dev(b, torch.float16), tB, c, alpha, beta)
+                    assert L.ntb_last_route() == capi.ROUTE_TC_F16
+                    err = rel_fro(c.float().cpu().numpy(), oracle.matmul_batched(a, tA, b, tB, alpha, beta, c0))
+                    assert err <= 2e-3, (M, N, K, tA, tB, alpha, beta, err)
+    finally:
+        L.ntb_set_route(0)
+        for k in ("NTB_BN", "NTB_GROUP_K", "NTB_SPLIT_K"):
+            os.environ.pop(k, None)
+    status_ok()
+
+
+@pytest.mark.parametrize("split", ["2", "2/1", "4"])
 def test_split_k_cluster_route(split, oracle):
     """Clusters of 2 / 4 CTAs share a tile and a part of K each and exchange partial sums
     through distributed shared memory; forced here on shapes with ragged edges, a K that
     does not divide evenly, batches, every transposition, alpha/beta and fp32 output."""
+    if "/" in split:
+        split, group = split.split("/")
+        os.environ["NTB_SPLIT_G"] = group           # one k-block per barrier hand-shake
     rng = np.random.default_rng(600 + int(split))
     L = capi.lib()
     os.environ["NTB_SPLIT_K"] = split
@@ -273,6 +319,7 @@ def test_split_k_cluster_route(split, oracle):
                     assert err <= 2e-3, (M, N, K, tA, tB, alpha, beta, err)
     finally:
         os.environ.pop("NTB_SPLIT_K", None)
+        os.environ.pop("NTB_SPLIT_G", None)
     status_ok()
 
 
