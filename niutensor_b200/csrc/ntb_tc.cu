@@ -608,6 +608,7 @@ GemmTcKernel(const __grid_constant__ TcGroup grp)
     constexpr int TMEM_COLS = TMEM_NEED <= 128 ? 128 : TMEM_NEED <= 256 ? 256 : 512;
     constexpr int KSTEPS = ROW_BYTES / UMMA_K_BYTES;                 /* 4 */
     static_assert(BN == 64 || BN == 128 || BN == 256, "tile width");
+    static_assert(STAGES <= 8, "barrier initialisation assigns lanes 0-7 to the stages");
 
 #ifdef NTB_WAIT_STATS
     const long long kernelT0 = clock64();
@@ -631,38 +632,49 @@ GemmTcKernel(const __grid_constant__ TcGroup grp)
     const uint32_t smemBase = (SmemAddr(smemRaw) + 1023u) & ~1023u;
     volatile int * abortPtr = &abortFlag;
 
-    if (threadIdx.x == 64) {
-        /* an idle epilogue lane pulls the kernel parameters and the tensor maps towards the SM
-           while the other warps set up, so the producer's first use of them does not stall */
+    if (threadIdx.x == 128 || threadIdx.x == 160) {
+        /* Idle epilogue lanes pull the kernel parameters (and one of them the tensor maps)
+           towards the SM while the other warps set up. Warps 4 and 5 share their scheduler
+           partition, and with it the first-level constant cache, with the producer warp and
+           the MMA warp: a constant load that misses stalls its warp for the whole miss,
+           one line after the other, and the producer reads half a dozen lines before its
+           first copy. */
         int touch = grp.total + grp.split;
         for (int gi = 0; gi < grp.n; gi++) {
             const TcParams & p = grp.p[gi];
-            PrefetchTensorMap(&grp.tm[gi][0]);
-            PrefetchTensorMap(&grp.tm[gi][1]);
-            if (p.cTma)
-                PrefetchTensorMap(&grp.tm[gi][2]);
-            touch += p.tilesM + p.tilesN + p.K + p.Q + p.group + p.aSel + p.bSel + p.aMN + p.bMN;
+            if (threadIdx.x == 128) {
+                PrefetchTensorMap(&grp.tm[gi][0]);
+                PrefetchTensorMap(&grp.tm[gi][1]);
+                if (p.cTma)
+                    PrefetchTensorMap(&grp.tm[gi][2]);
+            }
+            const int * words = (const int *)&p;
+            for (int w = 0; w < (int)(sizeof(TcParams) / sizeof(int)); w += 8)
+                touch += words[w];
         }
         asm volatile("" :: "r"(touch));
     }
-    if (threadIdx.x == 0) {
-        NTB_MARK(8);
-        for (int s = 0; s < STAGES; s++) {
-            MbarInit(SmemAddr(&barFull[s]), 1);
-            MbarInit(SmemAddr(&barEmpty[s]), 1);
-            MbarInit(SmemAddr(&barConv[s]), CONV_THREADS);
+    if (warp == 0) {
+        /* one barrier per lane: thirty-odd initialisations one after the other cost the
+           producer, which goes first, several hundred clocks */
+        if (lane == 0) NTB_MARK(8);
+        if (lane < STAGES) {
+            MbarInit(SmemAddr(&barFull[lane]), 1);
+            MbarInit(SmemAddr(&barEmpty[lane]), 1);
+            MbarInit(SmemAddr(&barConv[lane]), CONV_THREADS);
         }
-        for (int b = 0; b < 2; b++) {
-            MbarInit(SmemAddr(&barTFull[b]), 1);
-            MbarInit(SmemAddr(&barTEmpty[b]), 4);
+        else if (lane >= 8 && lane < 10) {
+            MbarInit(SmemAddr(&barTFull[lane - 8]), 1);
+            MbarInit(SmemAddr(&barTEmpty[lane - 8]), 4);
         }
-        for (int b = 0; b < 8; b++)
-            MbarInit(SmemAddr(&barOldC[b]), 1);
-        abortFlag = 0;
-        NTB_MARK(9);
+        else if (OLDC && lane >= 16 && lane < 24) {
+            MbarInit(SmemAddr(&barOldC[lane - 16]), 1);
+        }
+        if (lane == 0)
+            abortFlag = 0;
+        if (lane == 0) NTB_MARK(9);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        NTB_MARK(10);
+        if (lane == 0) NTB_MARK(10);
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -1146,30 +1158,37 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t smemBase = (SmemAddr(smemRaw) + 1023u) & ~1023u;
     volatile int * abortPtr = &abortFlag;
 
-    if (threadIdx.x == 64) {
-        /* an idle epilogue lane pulls the kernel parameters and the tensor maps towards the SM
-           while the other warps set up, so the producer's first use of them does not stall */
-        PrefetchTensorMap(&tmA);
-        PrefetchTensorMap(&tmB);
-        if (p.cTma)
-            PrefetchTensorMap(&tmC);
-        int touch = p.totalTiles + p.tilesM + p.tilesN + p.K + p.Q + p.group + p.aSel + p.bSel + p.aMN + p.bMN;
+    if (threadIdx.x == 128 || threadIdx.x == 160) {
+        /* idle epilogue lanes in the scheduler partitions of the producer warp and of the
+           MMA warp pull the kernel parameters (one of them also the tensor maps) towards
+           their constant caches while the other warps set up */
+        if (threadIdx.x == 128) {
+            PrefetchTensorMap(&tmA);
+            PrefetchTensorMap(&tmB);
+            if (p.cTma)
+                PrefetchTensorMap(&tmC);
+        }
+        int touch = 0;
+        const int * words = (const int *)&p;
+        for (int w = 0; w < (int)(sizeof(TcParams) / sizeof(int)); w += 8)
+            touch += words[w];
         asm volatile("" :: "r"(touch));
     }
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; s++) {
-            MbarInit(SmemAddr(&barFull[s]), 1);
-            MbarInit(SmemAddr(&barEmpty[s]), 1);
+    if (warp == 0) {
+        if (lane < STAGES) {
+            MbarInit(SmemAddr(&barFull[lane]), 1);
+            MbarInit(SmemAddr(&barEmpty[lane]), 1);
         }
-        for (int b = 0; b < 2; b++) {
-            MbarInit(SmemAddr(&barTFull[b]), 1);
-            MbarInit(SmemAddr(&barTEmpty[b]), 8);
+        else if (lane >= 8 && lane < 10) {
+            MbarInit(SmemAddr(&barTFull[lane - 8]), 1);
+            MbarInit(SmemAddr(&barTEmpty[lane - 8]), 8);
         }
-        for (int b = 0; b < 8; b++)
-            MbarInit(SmemAddr(&barOldC[b]), 1);
-        abortFlag = 0;
+        else if (OLDC && lane >= 16 && lane < 24) {
+            MbarInit(SmemAddr(&barOldC[lane - 16]), 1);
+        }
+        if (lane == 0)
+            abortFlag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -1469,27 +1488,38 @@ GemmTcSplitKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const uint32_t recvBase = smemBase + STAGES * STAGE_BYTES;
     volatile int * abortPtr = &abortFlag;
 
-    if (threadIdx.x == 64) {
-        PrefetchTensorMap(&tmA);
-        PrefetchTensorMap(&tmB);
-        if (p.cTma)
-            PrefetchTensorMap(&tmC);
+    if (threadIdx.x == 128 || threadIdx.x == 160) {
+        /* idle epilogue lanes in the scheduler partitions of the producer warp and of the
+           MMA warp pull the kernel parameters (one of them also the tensor maps) towards
+           their constant caches while the other warps set up */
+        if (threadIdx.x == 128) {
+            PrefetchTensorMap(&tmA);
+            PrefetchTensorMap(&tmB);
+            if (p.cTma)
+                PrefetchTensorMap(&tmC);
+        }
+        int touch = 0;
+        const int * words = (const int *)&p;
+        for (int w = 0; w < (int)(sizeof(TcParams) / sizeof(int)); w += 8)
+            touch += words[w];
+        asm volatile("" :: "r"(touch));
     }
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; s++) {
-            MbarInit(SmemAddr(&barFull[s]), 1);
-            MbarInit(SmemAddr(&barEmpty[s]), 1);
+    if (warp == 0) {
+        if (lane < STAGES) {
+            MbarInit(SmemAddr(&barFull[lane]), 1);
+            MbarInit(SmemAddr(&barEmpty[lane]), 1);
         }
-        for (int b = 0; b < 2; b++) {
-            MbarInit(SmemAddr(&barTFull[b]), 1);
-            MbarInit(SmemAddr(&barTEmpty[b]), 4);
-            MbarInit(SmemAddr(&barRecv[b]), (S - 1) * 4);
+        else if (lane >= 8 && lane < 10) {
+            MbarInit(SmemAddr(&barTFull[lane - 8]), 1);
+            MbarInit(SmemAddr(&barTEmpty[lane - 8]), 4);
+            MbarInit(SmemAddr(&barRecv[lane - 8]), (S - 1) * 4);
         }
-        for (int b = 0; b < 8; b++)
-            MbarInit(SmemAddr(&barOldC[b]), 1);
-        abortFlag = 0;
+        else if (OLDC && lane >= 16 && lane < 24) {
+            MbarInit(SmemAddr(&barOldC[lane - 16]), 1);
+        }
+        if (lane == 0)
+            abortFlag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
