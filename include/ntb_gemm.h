@@ -211,6 +211,29 @@ int ntb_gemm_list(int devID, void * stream,
                   float alpha, float beta);
 
 /*
+ * One 2-D product whose result is also written, tile by tile from the epilogue, to the
+ * same rows and columns of up to NTB_MAX_PEERS further buffers of the shape and pitch of c:
+ * the copies of C that other GPUs hold (their memory mapped into this process) or other
+ * buffers of this GPU. With the columns of C sharded over GPUs, every rank passes its column
+ * block of every other rank's full C and the all-gather of C is done by the products
+ * themselves, with plain 16-byte stores of full 128-byte lines over NVLink; no rank reads
+ * another's memory. The reference gathers tensors across devices with a device-to-device
+ * cudaMemcpy of the whole tensor after the operator (source/tensor/XUtility.cpp:196-201,
+ * source/train/XWorkerCollect.cpp:59-78); it has no fused form. c and the peers must allow
+ * the staged store path (16-byte aligned bases and pitches), else NTB_ERR_ARG; old values
+ * (beta != 0) are read from c only. The caller makes the writes visible to the other ranks
+ * by synchronising its stream and then the ranks (a host barrier), as after any copy.
+ */
+#define NTB_MAX_PEERS 8
+int ntb_gemm_peers(int devID, void * stream,
+                   const void * a, int transA, const void * b, int transB, void * c,
+                   void * const * peers, int nPeers,
+                   int dtypeAB, int dtypeC,
+                   int na, int ma, int nb, int mb, int nc, int mc,
+                   long long lda, long long ldb, long long ldc,
+                   float alpha, float beta);
+
+/*
  * Host-buffer form: a, b and c are HOST memory (pinned or pageable). Copies the
  * operands (and c when beta != 0) to staging buffers owned by the device context, runs
  * the strided-batched GEMM, copies c back and synchronises the stream. This is what a

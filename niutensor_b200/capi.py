@@ -13,6 +13,7 @@ X_INT, X_INT8, X_FLOAT, X_FLOAT16, X_DOUBLE = 0, 1, 2, 3, 4
 X_TRANS, X_NOTRANS = 0, 1
 ROUTE_NONE, ROUTE_TC_F16, ROUTE_TC_3XTF32, ROUTE_SIMT, ROUTE_TC_F16_PAIR = 0, 1, 2, 3, 4
 OK, ERR_ARG, ERR_SHAPE, ERR_DTYPE, ERR_CUDA, ERR_DEVICE_WAIT, ERR_LIMIT = range(7)
+MAX_PEERS = 8
 NOALLOC_MAX_BYTES = 16 << 20
 ACT_NONE, ACT_RECTIFY = 0, 1
 
@@ -31,6 +32,7 @@ PROTOTYPES = {
     "ntb_gemm_grad": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f]),
     "ntb_gemm_strided_batched": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _i, _i] + [_i] * 6 + [_ll] * 6 + [_i, _f, _f]),
     "ntb_gemm_broadcast": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _i, _i] + [_i] * 6 + [_i, _i, _f, _f]),
+    "ntb_gemm_peers": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, ctypes.POINTER(_vp), _i, _i, _i] + [_i] * 6 + [_ll] * 3 + [_f, _f]),
     "ntb_gemm_list": (_i, [_i, _vp, ctypes.POINTER(_vp), _i, ctypes.POINTER(_vp), _i, ctypes.POINTER(_vp),
                            _i, _i, _i] + [_i] * 6 + [_f, _f]),
     "ntb_gemm_host": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _i, _i] + [_i] * 6 + [_ll] * 3 + [_i, _f, _f]),

@@ -111,6 +111,8 @@ int Dispatch(int devID, cudaStream_t stream, Problem & p)
         return NTB_ERR_CUDA;
     const int forced = ForcedRoute();
     const bool tc = forced != NTB_ROUTE_SIMT && TcEligible(p);
+    if (p.nPeers > 0 && !tc)
+        return NTB_ERR_ARG;                         /* only the tensor-core kernels store to peers */
     int rc;
     if (tc) {
         int route = NTB_ROUTE_NONE;
@@ -364,6 +366,45 @@ int ntb_gemm(int devID, void * stream,
 {
     return ntb_gemm_strided_batched(devID, stream, a, transA, b, transB, c, dtypeAB, dtypeC,
                                     na, ma, nb, mb, nc, mc, lda, ldb, ldc, 0, 0, 0, 1, alpha, beta);
+}
+
+int ntb_gemm_peers(int devID, void * stream,
+                   const void * a, int transA, const void * b, int transB, void * c,
+                   void * const * peers, int nPeers,
+                   int dtypeAB, int dtypeC,
+                   int na, int ma, int nb, int mb, int nc, int mc,
+                   long long lda, long long ldb, long long ldc,
+                   float alpha, float beta)
+{
+    Problem p;
+    memset(&p, 0, sizeof(p));
+    int rc = CheckDtypes(dtypeAB, dtypeC);
+    if (rc != NTB_OK)
+        return rc;
+    rc = SetShape(p, transA, transB, na, ma, nb, mb, nc, mc);
+    if (rc != NTB_OK)
+        return rc;
+    if (lda < ma || ldb < mb || ldc < mc || nPeers < 0 || (nPeers > 0 && !peers))
+        return NTB_ERR_ARG;
+    if (nPeers > NTB_MAX_PEERS)
+        return NTB_ERR_LIMIT;
+    const long long ces = ElemSize(dtypeC);
+    for (int i = 0; i < nPeers; i++) {
+        if (!peers[i] || ((uintptr_t)peers[i] & 15) || (ldc * ces) % 16)
+            return NTB_ERR_ARG;
+        p.peers[i] = peers[i];
+    }
+    p.nPeers = nPeers;
+    p.a = a; p.b = b; p.c = c;
+    p.dtAB = dtypeAB; p.dtC = dtypeC;
+    p.lda = lda; p.ldb = ldb; p.ldc = ldc;
+    p.count = 1; p.Q = 1;
+    p.alpha = alpha; p.beta = beta;
+    if (nPeers > 0 && p.K == 0)
+        return NTB_ERR_ARG;                         /* K == 0 takes the FFMA kernel, which has no peer stores */
+    if (nPeers > 0 && !TcEligible(p))
+        return NTB_ERR_ARG;
+    return Dispatch(devID, (cudaStream_t)stream, p);
 }
 
 int ntb_gemm_broadcast(int devID, void * stream,

@@ -29,6 +29,10 @@ struct Problem {
     float alpha, beta;
     const void * bias;      /* optional row vector of N values (type of c) added to every row of every problem */
     int act;                /* NTB_ACT_NONE / NTB_ACT_RECTIFY, applied last */
+    /* further destinations of the result, same shape and pitch as c (other GPUs' copies of C
+       mapped into this process, or other buffers of this GPU) */
+    void * peers[NTB_MAX_PEERS];
+    int nPeers;
 };
 
 struct DeviceCtx {

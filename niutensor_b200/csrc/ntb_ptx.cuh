@@ -72,17 +72,6 @@ __device__ __forceinline__ uint32_t MbarTryWait(uint32_t bar, uint32_t parity, u
 __device__ __forceinline__ bool MbarWait(uint32_t bar, uint32_t parity, volatile int * abortFlag, int * status,
                                          uint32_t hintNs = NTB_WAIT_HINT_NS)
 {
-#ifdef NTB_TESTWAIT
-    {
-        uint32_t done;
-        asm volatile("{\n\t.reg .pred p;\n\t"
-                     "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                     "selp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-        if (done)
-            return true;
-    }
-#endif
     if (MbarTryWait(bar, parity, hintNs))
         return true;
     const long long t0 = clock64();

@@ -84,6 +84,8 @@ struct TcParams {
     int group;              /* m-blocks per band of the tile walk */
     FastDiv fdPerProb, fdBand, fdGroup, fdLast, fdQ;   /* tiles per problem, tiles per band, rows of a full / of the last band, Q */
     int epiHint;            /* suspend-time hint (ns) of the epilogue warps' barrier probes */
+    void * peers[NTB_MAX_PEERS];   /* further destinations of every result tile (peer GPUs' C), or none */
+    int nPeers;
     int cPrefetch;          /* wide tiles with beta != 0: 0 no L2 prefetch of old C, 1 boxes through TMA, 2 one request per line */
     float alpha, beta;
     const void * bias;      /* N values of C's type added to every output row, or NULL */
@@ -101,7 +103,6 @@ __device__ unsigned long long gWaitStats[8];
    0 set-up done, 1 first TMA issued, 2 first stage landed, 3 first tile's MMAs committed,
    4 epilogue saw the accumulator, 5 epilogue stores issued, 6 stores complete, 7 kernel end */
 __device__ unsigned long long gTimeline[64];
-__device__ int gExp;   /* experiment switches: 1 no MMA instructions, 2 no TMA loads */
 #define NTB_MARKK(row, kb) do { if (blockIdx.x == 0 && (kb) < 16 && tlShared[16 + (row) * 16 + (kb)] == 0) tlShared[16 + (row) * 16 + (kb)] = (unsigned long long)(clock64() - kernelT0) + 1; } while (0)
 #define NTB_MARK(slot) do { if (blockIdx.x == 0 && tlShared[slot] == 0) tlShared[slot] = (unsigned long long)(clock64() - kernelT0) + 1; } while (0)
 #ifdef NTB_CLOCKS
@@ -268,8 +269,9 @@ __device__ __forceinline__ void StoreRow32Direct(OutT * cRow, int c0, const floa
 constexpr int EPI_BOX_BYTES = 32 * ROW_BYTES;               /* 32 rows x 128 B */
 constexpr int EPI_BYTES = 4 * 2 * EPI_BOX_BYTES;            /* four epilogue warps, two boxes each */
 
-/* OLDC: the kernel was built for products that read the old C (beta != 0); without it all
-   of that support compiles away, which keeps the epilogue of beta == 0 products short */
+/* OLDC: the kernel was built for products that read the old C (beta != 0) or that also
+   store their result to peer buffers; without it all of that support compiles away, which
+   keeps the epilogue of the plain beta == 0 product short */
 template <typename OutT, bool OLDC>
 struct TileWriter {
     static constexpr int BOX_COLS = ROW_BYTES / (int)sizeof(OutT);   /* 64 halves / 32 floats */
@@ -504,7 +506,44 @@ struct TileWriter {
                              :: "l"(map), "r"(c0 - colInBox), "r"(row0), "r"(batch), "r"(box) : "memory");
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
+            if (OLDC && p.nPeers > 0 && live)
+                BoxToPeers(p, cRow - (long long)lane * p.ldc, box, row0, c0 - colInBox, lane);
             boxes++;
+        }
+    }
+
+    /* The finished box (32 rows x 128 bytes, swizzled in shared memory) goes to the same
+       place of every peer buffer with plain 16-byte stores: eight lanes cover the 128 bytes
+       of one row, so a warp instruction writes four full lines. cBox0 points at row row0,
+       column 0 of this problem's C. */
+    __device__ __forceinline__ void BoxToPeers(const TcParams & p, const OutT * cBox0, uint32_t box, int row0, int col0,
+                                               int lane)
+    {
+        constexpr int VN = Vec16<OutT>::N;
+        const long long base = cBox0 - (const OutT *)p.c;          /* element offset of (row0, 0) in C */
+        const int chunk = lane & 7;
+        const int col = col0 + chunk * VN;
+#pragma unroll
+        for (int r = 0; r < 8; r++) {
+            const int rr = r * 4 + (lane >> 3);
+            uint32_t w0, w1, w2, w3;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3)
+                         : "r"(box + (uint32_t)rr * ROW_BYTES + (uint32_t)((chunk ^ (rr & 7)) << 4)) : "memory");
+            if (row0 + rr < p.M && col + VN <= p.N) {
+                const long long off = base + (long long)rr * p.ldc + col;
+                for (int k = 0; k < p.nPeers; k++)
+                    *(uint4 *)((OutT *)p.peers[k] + off) = make_uint4(w0, w1, w2, w3);
+            }
+            else if (row0 + rr < p.M) {
+                const uint32_t w[4] = { w0, w1, w2, w3 };          /* ragged right edge: element by element */
+                const OutT * e = (const OutT *)w;
+                for (int j = 0; j < VN; j++)
+                    if (col + j < p.N) {
+                        const long long off = base + (long long)rr * p.ldc + col + j;
+                        for (int k = 0; k < p.nPeers; k++)
+                            ((OutT *)p.peers[k])[off] = e[j];
+                    }
+            }
         }
     }
 
@@ -612,7 +651,6 @@ GemmTcKernel(const __grid_constant__ TcGroup grp)
 
 #ifdef NTB_WAIT_STATS
     const long long kernelT0 = clock64();
-    const int exp = *(volatile int *)&gExp;
     __shared__ unsigned long long tlShared[64];
     if (threadIdx.x < 64) tlShared[threadIdx.x] = 0;
     __syncthreads();
@@ -734,13 +772,6 @@ GemmTcKernel(const __grid_constant__ TcGroup grp)
                         break;
                     const uint32_t full = SmemAddr(&barFull[s]);
                     const int nb = G == 1 ? 1 : (nkb - kb < G ? nkb - kb : G);
-#ifdef NTB_WAIT_STATS
-                    if (exp & 2) {
-                        MbarArrive(full);
-                        if (++s == NSTG) { s = 0; ph ^= 1u; }
-                        continue;
-                    }
-#endif
                     NTB_TIMED(6, MbarExpectTx(full, (uint32_t)nb * PLANE_BYTES));
                     NTB_MARK(14);
 #pragma unroll
@@ -855,10 +886,6 @@ GemmTcKernel(const __grid_constant__ TcGroup grp)
                                 uint32_t bLo = bLo0 + stageOff + (uint32_t)j * (STAGE_BYTES >> 4);
 #pragma unroll
                                 for (int k = 0; k < KSTEPS; k++) {
-#ifdef NTB_WAIT_STATS
-                                    if (exp & 1)
-                                        continue;
-#endif
                                     if (MODE == 0) {
                                         TcMmaLH<MODE>(dTmem, aLo, aHiW, bLo, bHiW, iDesc, acc);
                                     }
@@ -874,11 +901,6 @@ GemmTcKernel(const __grid_constant__ TcGroup grp)
                                 }
                             }
                         }
-#ifdef NTB_WAIT_STATS
-                        if (exp & 8)
-                            MbarArrive(barEmpty0 + (uint32_t)s * 8u);
-                        else
-#endif
                         TcCommit(barEmpty0 + (uint32_t)s * 8u);
                         NTB_MARKK(2, kb);
                         stageOff += (uint32_t)G * (STAGE_BYTES >> 4);
@@ -1797,7 +1819,7 @@ int Knob(const char * name, int dflt)
 int LaunchGroup(const TcGroup & grp, int mode, int bn, int dtC, int smCount, cudaStream_t stream)
 {
     /* kernels built with support for reading the old C only where a product asks for it */
-    const bool oldc = grp.p[0].beta != 0.f || (grp.n > 1 && grp.p[1].beta != 0.f);
+    const bool oldc = grp.p[0].beta != 0.f || grp.p[0].nPeers > 0 || (grp.n > 1 && (grp.p[1].beta != 0.f || grp.p[1].nPeers > 0));
 #define NTB_ONE(MD, W, ST, GG, T) (oldc ? LaunchOne<MD, W, ST, GG, T, true>(grp, smCount, stream) \
                                         : LaunchOne<MD, W, ST, GG, T, false>(grp, smCount, stream))
     if (mode == 0) {
@@ -2029,6 +2051,9 @@ int Prepare(const DeviceCtx & ctx, const Problem & p, int mode, int bn, bool pai
     tp.totalTiles = (int)tiles64;
     tp.alpha = p.alpha; tp.beta = p.beta;
     tp.bias = p.bias; tp.act = p.act;
+    tp.nPeers = p.nPeers;
+    for (int i = 0; i < NTB_MAX_PEERS; i++)
+        tp.peers[i] = i < p.nPeers ? p.peers[i] : nullptr;
     tp.status = ctx.status;
     tp.pfDist = Knob("NTB_PREFETCH_DIST", 0);
     tp.group = Knob("NTB_TILE_GROUP", 8);
@@ -2102,7 +2127,9 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
         bn -= 8;
     if (knobPairBN == 256 && (bn == -8 || bn == -9))
         bn += 8;
-    const int split = (bn == -2 || bn == -4) ? -bn : 0;
+    int split = (bn == -2 || bn == -4) ? -bn : 0;
+    if (split == 4 && p.nPeers > 0 && p.dtC == NTB_X_FLOAT16)
+        split = 2;                                  /* the 4-way split of a half tile stores directly */
     if (split)
         bn = 128;
     const bool pair = bn <= 0;
@@ -2124,6 +2151,8 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
         grp.tm[1][i] = grp.tm[0][i];
     grp.split = grp.total = grp.p[0].totalTiles;
 
+    if (p.nPeers > 0 && !grp.p[0].cTma)
+        return NTB_ERR_ARG;                         /* peer copies are made from the staged boxes */
     if (split) {
         /* a 32-column slice of half values is half a store box: direct stores instead */
         if (split == 4 && p.dtC == NTB_X_FLOAT16)
@@ -2131,7 +2160,7 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
         const TcParams & tp = grp.p[0];
         const int clusters = (int)(tp.totalTiles < ctx.smCount / split ? tp.totalTiles : ctx.smCount / split);
         const bool half = p.dtC == NTB_X_FLOAT16;
-        const bool oldc = tp.beta != 0.f;
+        const bool oldc = tp.beta != 0.f || tp.nPeers > 0;
 #define NTB_SPLIT(SS, ST, GG, T) (oldc ? LaunchSplit<SS, ST, GG, T, true>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, clusters, stream) \
                                        : LaunchSplit<SS, ST, GG, T, false>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, clusters, stream))
         const int sg = Knob("NTB_SPLIT_G", 2);
@@ -2151,7 +2180,7 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
         /* 256 x 128 tiles: two k-blocks per hand-shake keep four barrier stages in flight;
            four (NTB_PAIR_G = 4) gain a few per cent on short K and lose more on long K */
         const int g = Knob("NTB_PAIR_G", 2);
-        const bool oldc = tp.beta != 0.f;
+        const bool oldc = tp.beta != 0.f || tp.nPeers > 0;
 #define NTB_PAIR2(MS, W, ST, GG, T) (oldc ? LaunchPair<MS, W, ST, GG, T, true>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, pairs, stream) \
                                           : LaunchPair<MS, W, ST, GG, T, false>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, pairs, stream))
 #define NTB_PAIR(MS, W, ST, GG) (half ? NTB_PAIR2(MS, W, ST, GG, __half) : NTB_PAIR2(MS, W, ST, GG, float))
@@ -2219,11 +2248,6 @@ extern "C" void ntb_debug_wait_stats(unsigned long long * out)
     cudaMemcpyFromSymbol(out, gWaitStats, sizeof(unsigned long long) * 8);
     unsigned long long zero[8] = {0};
     cudaMemcpyToSymbol(gWaitStats, zero, sizeof(zero));
-}
-
-extern "C" void ntb_debug_set_exp(int v)
-{
-    cudaMemcpyToSymbol(gExp, &v, sizeof(int));
 }
 
 extern "C" void ntb_debug_timeline(unsigned long long * out)

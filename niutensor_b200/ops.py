@@ -12,6 +12,8 @@ Names, argument meaning and shape rules follow the reference:
 Transposition flags are the reference's enum values: X_TRANS = 0, X_NOTRANS = 1.
 Where the reference prints an error and terminates, these raise NtError.
 """
+import ctypes
+
 import torch
 
 from . import capi
@@ -268,3 +270,26 @@ def GradMatrixMul(a, transposedA, b, transposedB, dedc, deda, dedb, alpha=1.0):
                                   None if dedb is None else dedb.data_ptr(), _dtype_code(a),
                                   a.shape[-2], a.shape[-1], b.shape[-2], b.shape[-1], count, alpha)
     _raise_rc(rc, "GradMatrixMul")
+
+
+def MatrixMul2DToPeers(a, transposedA, b, transposedB, c_full, col0, peer_bases, alpha=1.0, beta=0.0):
+    """c_full[:, col0:col0+n] = alpha * op(a) * op(b) + beta * c_full[:, col0:col0+n], and the same
+    block written to the same place of every buffer in peer_bases (device addresses of
+    matrices with the shape and pitch of c_full: other GPUs' copies of C mapped into this
+    process, or other buffers of this GPU). The stores to the peers are issued by the
+    epilogue of the product (ntb_gemm_peers); no separate gather pass runs."""
+    _common_checks(a, b, c_full)
+    _check(a.dim() == 2 and b.dim() == 2 and c_full.dim() == 2, "Input tensors must have a order = 2!")
+    an, am = (a.shape[1], a.shape[0]) if transposedA == X_TRANS else (a.shape[0], a.shape[1])
+    bn, bm = (b.shape[1], b.shape[0]) if transposedB == X_TRANS else (b.shape[0], b.shape[1])
+    _check(am == bn and an == c_full.shape[0] and 0 <= col0 and col0 + bm <= c_full.shape[1],
+           "Unmatched tensors in multiplication!")
+    _check(len(peer_bases) <= capi.MAX_PEERS, "too many peers")
+    es = c_full.element_size()
+    ptrs = (ctypes.c_void_p * max(1, len(peer_bases)))(*[int(x) + col0 * es for x in peer_bases])
+    rc = capi.lib().ntb_gemm_peers(a.device.index, _stream(a), a.data_ptr(), transposedA, b.data_ptr(), transposedB,
+                                   c_full.data_ptr() + col0 * es, ptrs, len(peer_bases),
+                                   _dtype_code(a), _dtype_code(c_full),
+                                   a.shape[0], a.shape[1], b.shape[0], b.shape[1], an, bm,
+                                   a.shape[1], b.shape[1], c_full.shape[1], alpha, beta)
+    _raise_rc(rc, "MatrixMul2DToPeers")

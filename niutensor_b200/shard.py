@@ -53,6 +53,40 @@ def matmul_column_shard(a, transposedA, b_local, transposedB, alpha=1.0, beta=0.
     return ops.MatrixMul(a, transposedA, b_local, transposedB, alpha, beta, c=c_local)
 
 
+def symmetric_matrix(rows, cols, dtype, device, group=None):
+    """A [rows, cols] matrix allocated on every rank of the group in symmetric memory, and
+    the device addresses under which this process can write the other ranks' copies (NVLink
+    peer mappings; plain stores, no multicast: TORCH_SYMM_MEM_DISABLE_MULTICAST is set unless
+    the caller chose otherwise). Returns (tensor, {rank: address})."""
+    import os
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+    import torch.distributed._symmetric_memory as symm
+    group = group if group is not None else dist.group.WORLD
+    t = symm.empty((rows, cols), dtype=dtype, device=device)
+    hdl = symm.rendezvous(t, group)
+    me = dist.get_rank(group)
+    peers = {r: int(hdl.buffer_ptrs[r]) for r in range(dist.get_world_size(group)) if r != me}
+    return t, peers
+
+
+def matmul_column_shard_to_all(a, transposedA, b_local, transposedB, c_sym, peer_addrs, n_cols, group=None,
+                               alpha=1.0, beta=0.0):
+    """Every rank computes its column block of C from its packed shard of B and its epilogue
+    writes the block into its own c_sym and into every other rank's (ntb_gemm_peers): after
+    the closing barrier all ranks hold the full C. Replaces product + all-gather + the
+    re-interleaving pass of gather_columns."""
+    from . import ops
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    lo, hi = column_shard(n_cols, world, rank)
+    if not b_local.is_contiguous():
+        b_local = b_local.contiguous()
+    ops.MatrixMul2DToPeers(a, transposedA, b_local, transposedB, c_sym, lo, [peer_addrs[r] for r in sorted(peer_addrs)],
+                           alpha, beta)
+    torch.cuda.current_stream(c_sym.device).synchronize()
+    dist.barrier(group)
+    return c_sym
+
+
 def gather_columns(c_local, n_cols, group=None):
     """All ranks receive the full [..., M, n_cols] matrix from the per-rank column shards."""
     world = dist.get_world_size(group)

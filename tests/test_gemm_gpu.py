@@ -342,6 +342,59 @@ def test_split_k_is_chosen_for_weight_gradient_shapes_and_is_deterministic(oracl
     status_ok()
 
 
+@pytest.mark.parametrize("variant", ["auto", "single64", "single256", "pair128", "pair256", "split2"])
+def test_result_also_stored_to_peer_buffers(variant, oracle):
+    """ntb_gemm_peers: the epilogue writes each finished tile to the column block of C and to
+    the same block of further buffers (here other buffers of this GPU stand in for the other
+    ranks' copies of C). Every destination must hold exactly the block, nothing outside it
+    may change, beta reads only the local C; ragged rows, a block narrower than a store
+    box, every kernel family."""
+    env = {"auto": {}, "single64": {"NTB_ROUTE": "1", "NTB_BN": "64", "NTB_SPLIT_K": "0"},
+           "single256": {"NTB_ROUTE": "1", "NTB_BN": "256", "NTB_SPLIT_K": "0"},
+           "pair128": {"NTB_ROUTE": "4", "NTB_PAIR_BN": "128", "NTB_PAIR_MSUB": "1"},
+           "pair256": {"NTB_ROUTE": "4", "NTB_PAIR_BN": "256", "NTB_PAIR_MSUB": "2"},
+           "split2": {"NTB_SPLIT_K": "2"}}[variant]
+    rng = np.random.default_rng(1200 + len(variant))
+    os.environ.update(env)
+    try:
+        for (M, N, K, full_cols, col0, dtype, beta) in [(256, 256, 512, 640, 128, torch.float16, 0.0),
+                                                         (200, 136, 320, 512, 64, torch.float16, 0.5),
+                                                         (72, 40, 1032, 96, 8, torch.float32, 1.0),
+                                                         (520, 264, 264, 272, 8, torch.float16, 0.0)]:
+            a = round_to_half(rng.uniform(-1, 1, (M, K)).astype(np.float32))
+            b = round_to_half(rng.uniform(-1, 1, (N, K)).astype(np.float32))
+            c0 = round_to_half(rng.normal(size=(M, full_cols)).astype(np.float32))
+            local = to_dev(c0, dtype)
+            peers = [torch.full((M, full_cols), float(7 + i), device=DEV, dtype=dtype) for i in range(3)]
+            ops.MatrixMul2DToPeers(to_dev(a, torch.float16), X_NOTRANS, to_dev(b, torch.float16), X_TRANS,
+                                   local, col0, [t.data_ptr() for t in peers], 0.25, beta)
+            want = oracle.matmul2d(a, X_NOTRANS, b, X_TRANS, 0.25, beta, c0[:, col0:col0 + N])
+            got = local.float().cpu().numpy()
+            assert rel_fro(got[:, col0:col0 + N], want) <= 2e-3, (variant, M, N, K)
+            keep = np.ones(full_cols, bool)
+            keep[col0:col0 + N] = False
+            assert np.array_equal(got[:, keep], to_dev(c0, dtype).float().cpu().numpy()[:, keep])
+            for i, t in enumerate(peers):
+                pt = t.float().cpu().numpy()
+                assert np.array_equal(pt[:, col0:col0 + N], got[:, col0:col0 + N]), (variant, M, N, K, i)
+                assert np.all(pt[:, keep] == float(7 + i))
+    finally:
+        for k in env:
+            os.environ.pop(k, None)
+    status_ok()
+
+
+def test_peer_stores_are_refused_where_no_kernel_makes_them():
+    a = torch.zeros(64, 64, device=DEV, dtype=torch.float16)
+    c = torch.zeros(64, 72, device=DEV, dtype=torch.float16)
+    other = torch.zeros(64, 72, device=DEV, dtype=torch.float16)
+    with pytest.raises(ops.NtError):        # column offset 4 -> destination not 16-byte aligned
+        ops.MatrixMul2DToPeers(a, X_NOTRANS, a, X_TRANS, c, 4, [other.data_ptr()])
+    with pytest.raises(ops.NtError):
+        ops.MatrixMul2DToPeers(a, X_NOTRANS, a, X_TRANS, c, 0, [other.data_ptr()] * 9)
+    status_ok()
+
+
 # --------------------------------------------------------------- semantics corners
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
