@@ -275,6 +275,35 @@ def main_ours(args):
         dist.all_reduce(g, op=dist.ReduceOp.MAX)
         gather_ms = float(g.item())
 
+    # optional: the same gather done by the product's own epilogue (peer stores), for comparison
+    fused = None
+    if world > 1 and args.fused_gather:
+        try:
+            from niutensor_b200 import ops as nops
+            c_sym, peers = shard.symmetric_matrix(N_DIM, N_DIM * world, torch.float16, dev)
+            c_sym.zero_()
+            plist = [peers[r] for r in sorted(peers)]
+            torch.cuda.synchronize()
+            barrier()
+
+            def fused_step():
+                nops.MatrixMul2DToPeers(a, capi.X_NOTRANS, b, capi.X_NOTRANS, c_sym, rank * N_DIM, plist, ALPHA, 0.0)
+
+            fused_step()
+            barrier()
+            e0.record()
+            for _ in range(3):
+                fused_step()
+            e1.record()
+            barrier()
+            g = torch.tensor([e0.elapsed_time(e1) / 3], device=dev, dtype=torch.float64)
+            dist.all_reduce(g, op=dist.ReduceOp.MAX)
+            fused = {"ms": float(g.item()),
+                     "note": "product (beta = 0) whose epilogue stores its column block into every rank's C; "
+                             "compare with ms_per_step + allgather_of_c.ms"}
+        except Exception as exc:              # an extra must never sink the benchmark line
+            fused = {"ms": None, "note": "failed: %r" % (exc,)}
+
     if args.kernel_only:
         if rank == 0:
             print(json.dumps({"metric": "MatrixMul TFLOP/s", "value": tflops, "unit": "TFLOP/s",
@@ -341,6 +370,8 @@ def main_ours(args):
                                       "gb_per_s_per_gpu": (world - 1) * mat_bytes / (gather_ms * 1e-3) / 1e9,
                                       "note": "NCCL all_gather + local re-interleave; only for callers that "
                                               "need the full C on every rank; not part of value"}
+        if fused is not None:
+            line["fused_gather_of_c"] = fused
         if world == 1:
             try:
                 line["cpu_baseline"] = {k: v for k, v in time_cpu(2, 1).items() if k != "ms_per_step"}
@@ -360,6 +391,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--fused-gather", action="store_true",
+                    help="N > 1: also time the product whose epilogue writes its block of C to every rank (symmetric memory)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end and CPU-baseline legs (short runs under a profiler)")
     args = ap.parse_args()
