@@ -86,6 +86,7 @@ struct TcParams {
     int epiHint;            /* suspend-time hint (ns) of the epilogue warps' barrier probes */
     void * peers[NTB_MAX_PEERS];   /* further destinations of every result tile (peer GPUs' C), or none */
     int nPeers;
+    int l2Hint;             /* pair kernel: L2 eviction policy of the A loads (bits 0-1) and B loads (bits 2-3): 0 none, 1 keep, 2 stream */
     int cPrefetch;          /* wide tiles with beta != 0: 0 no L2 prefetch of old C, 1 boxes through TMA, 2 one request per line */
     float alpha, beta;
     const void * bias;      /* N values of C's type added to every output row, or NULL */
@@ -1102,6 +1103,26 @@ __device__ __forceinline__ void ClusterSync()
     asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
 }
 
+/* L2 eviction policy for a stream of loads: 1 keep (evict last), 2 stream (evict first) */
+__device__ __forceinline__ uint64_t L2Policy(int kind)
+{
+    uint64_t pol = 0;
+    if (kind == 1)
+        asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    else if (kind == 2)
+        asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+
+/* the pair load with an L2 eviction policy */
+__device__ __forceinline__ void TmaLoad3DPairHint(uint32_t dst, const CUtensorMap * map, uint32_t barCluster, int c0, int c1,
+                                                  int c2, uint64_t policy)
+{
+    asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+                 " [%0], [%1, {%3, %4, %5}], [%2], %6;"
+                 :: "r"(dst), "l"(map), "r"(barCluster), "r"(c0), "r"(c1), "r"(c2), "l"(policy) : "memory");
+}
+
 /* TMA load whose completion bytes are counted on a barrier of the pair's leader CTA */
 __device__ __forceinline__ void TmaLoad3DPair(uint32_t dst, const CUtensorMap * map, uint32_t barCluster, int c0, int c1, int c2)
 {
@@ -1243,6 +1264,8 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 const int bb = BatchCoord(p.bSel, tc.prob, p);
                 const bool aMN = p.aMN != 0, bMN = p.bMN != 0;
                 int * const status = p.status;
+                const int hint = p.l2Hint;
+                const uint64_t polA = L2Policy(hint & 3), polB = L2Policy((hint >> 2) & 3);
                 for (int kb = 0; kb < kBlocks; kb += G) {
                     NTB_TIMED(0, ok = MbarWait(SmemAddr(&barEmpty[s]), ph ^ 1u, abortPtr, status));
                     if (!ok)
@@ -1262,7 +1285,10 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                 const int ms = m0 + sub * 2 * BM;
                                 const uint32_t dst = aDst + sub * A_TILE_BYTES;
                                 if (!aMN) {
-                                    TmaLoad3DPair(dst, &tmA, fullLeader, k0, ms, ba);
+                                    if (hint & 3)
+                                        TmaLoad3DPairHint(dst, &tmA, fullLeader, k0, ms, ba, polA);
+                                    else
+                                        TmaLoad3DPair(dst, &tmA, fullLeader, k0, ms, ba);
                                 }
                                 else {
 #pragma unroll
@@ -1271,12 +1297,19 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                 }
                             }
                             if (!bMN) {
-                                TmaLoad3DPair(bDst, &tmB, fullLeader, k0, n0, bb);
+                                if (hint >> 2)
+                                    TmaLoad3DPairHint(bDst, &tmB, fullLeader, k0, n0, bb, polB);
+                                else
+                                    TmaLoad3DPair(bDst, &tmB, fullLeader, k0, n0, bb);
                             }
                             else {
 #pragma unroll
-                                for (int i = 0; i < BNH / EPR; i++)
-                                    TmaLoad3DPair(bDst + i * EPR * ROW_BYTES, &tmB, fullLeader, n0 + i * EPR, k0, bb);
+                                for (int i = 0; i < BNH / EPR; i++) {
+                                    if (hint >> 2)
+                                        TmaLoad3DPairHint(bDst + i * EPR * ROW_BYTES, &tmB, fullLeader, n0 + i * EPR, k0, bb, polB);
+                                    else
+                                        TmaLoad3DPair(bDst + i * EPR * ROW_BYTES, &tmB, fullLeader, n0 + i * EPR, k0, bb);
+                                }
                             }
                         }
                     }
@@ -2061,6 +2094,7 @@ int Prepare(const DeviceCtx & ctx, const Problem & p, int mode, int bn, bool pai
         tp.group = 1;
     tp.epiHint = Knob("NTB_EPI_HINT_NS", 2000);
     tp.cPrefetch = Knob("NTB_C_PREFETCH", 0);
+    tp.l2Hint = Knob("NTB_L2_HINT", 0);
     tp.fdPerProb.Set((uint32_t)(tp.tilesM * tp.tilesN));
     tp.fdBand.Set((uint32_t)(tp.group * tp.tilesN));
     tp.fdGroup.Set((uint32_t)tp.group);

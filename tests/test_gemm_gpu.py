@@ -395,6 +395,39 @@ def test_peer_stores_are_refused_where_no_kernel_makes_them():
     status_ok()
 
 
+def test_seeded_random_shapes_against_the_oracle(oracle):
+    """120 seeded random products: extents 1..700 (multiples of 8 or not, so both the
+    tensor-core kernels and the FFMA kernel are reached), every transposition, batch counts
+    1..5 in the strided and the general (p, q) form, alpha/beta drawn from a small set, half
+    and float tensors, whatever kernel the cost model picks."""
+    rng = np.random.default_rng(20240)
+    routes = set()
+    for case in range(120):
+        dtype = torch.float16 if case % 3 else torch.float32
+        aligned = case % 4 != 0
+        def extent(hi):
+            v = int(rng.integers(1, hi))
+            return max(8, v // 8 * 8) if aligned else v
+        M, N, K = extent(700), extent(700), extent(1400 if case % 5 == 0 else 400)
+        tA = X_TRANS if rng.integers(2) else X_NOTRANS
+        tB = X_TRANS if rng.integers(2) else X_NOTRANS
+        alpha = float(rng.choice([1.0, 0.5, -0.125, 2.0]))
+        beta = float(rng.choice([0.0, 0.0, 1.0, 0.5]))
+        cnt = int(rng.integers(1, 6)) if case % 2 else 1
+        a = stored(rng, (cnt,), M, K, tA)
+        b = stored(rng, (cnt,), K, N, tB)
+        c0 = rng.normal(size=(cnt, M, N)).astype(np.float32)
+        if dtype == torch.float16:
+            a, b, c0 = round_to_half(a), round_to_half(b), round_to_half(c0)
+        c = to_dev(c0, dtype)
+        ops._MatrixMulBatched(to_dev(a, dtype), tA, to_dev(b, dtype), tB, c, alpha, beta)
+        routes.add(capi.lib().ntb_last_route())
+        err = rel_fro(c.float().cpu().numpy(), oracle.matmul_batched(a, tA, b, tB, alpha, beta, c0))
+        assert err <= TOL[dtype], (case, M, N, K, tA, tB, cnt, alpha, beta, dtype, err)
+    assert capi.ROUTE_SIMT in routes and capi.ROUTE_TC_F16 in routes and capi.ROUTE_TC_3XTF32 in routes
+    status_ok()
+
+
 # --------------------------------------------------------------- semantics corners
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
