@@ -289,6 +289,22 @@ int ntb_set_route(int route);
  */
 int ntb_device_status(int devID);
 
+/*
+ * The kernel the tile cost model picks for `count` fp16 (NTB_X_FLOAT16) or fp32 products
+ * of M x N x K on a device with smCount SMs, without launching anything (no CUDA call):
+ * the tile width 64 / 128 / 256 of the single-CTA kernel, or NTB_PLAN_PAIR_* /
+ * NTB_PLAN_SPLIT_* for the cluster kernels. An inspection aid for tuning and for tests of
+ * the model; it has no counterpart in the reference, whose cuBLAS calls choose internally.
+ * Environment knobs that override the model at launch are not applied here.
+ */
+#define NTB_PLAN_PAIR_256X256   0
+#define NTB_PLAN_PAIR_512X256  (-1)
+#define NTB_PLAN_SPLIT_K2      (-2)
+#define NTB_PLAN_SPLIT_K4      (-4)
+#define NTB_PLAN_PAIR_256X128  (-8)
+#define NTB_PLAN_PAIR_512X128  (-9)
+int ntb_plan(int dtypeAB, int M, int N, int K, int count, int smCount);
+
 /* Number of kernels this library has launched in the process so far. */
 long long ntb_launch_count(void);
 

@@ -14,6 +14,7 @@ X_TRANS, X_NOTRANS = 0, 1
 ROUTE_NONE, ROUTE_TC_F16, ROUTE_TC_3XTF32, ROUTE_SIMT, ROUTE_TC_F16_PAIR = 0, 1, 2, 3, 4
 OK, ERR_ARG, ERR_SHAPE, ERR_DTYPE, ERR_CUDA, ERR_DEVICE_WAIT, ERR_LIMIT = range(7)
 MAX_PEERS = 8
+PLAN_PAIR_256X256, PLAN_PAIR_512X256, PLAN_SPLIT_K2, PLAN_SPLIT_K4, PLAN_PAIR_256X128, PLAN_PAIR_512X128 = 0, -1, -2, -4, -8, -9
 NOALLOC_MAX_BYTES = 16 << 20
 ACT_NONE, ACT_RECTIFY = 0, 1
 
@@ -40,6 +41,7 @@ PROTOTYPES = {
     "ntb_last_route": (_i, []),
     "ntb_set_route": (_i, [_i]),
     "ntb_device_status": (_i, [_i]),
+    "ntb_plan": (_i, [_i] * 6),
     "ntb_launch_count": (_ll, []),
     "ntb_release": (None, []),
     "ntb_strerror": (ctypes.c_char_p, [_i]),

@@ -648,6 +648,22 @@ int ntb_device_status(int devID)
     return v;
 }
 
+int ntb_plan(int dtypeAB, int M, int N, int K, int count, int smCount)
+{
+    if ((dtypeAB != NTB_X_FLOAT16 && dtypeAB != NTB_X_FLOAT) || M <= 0 || N <= 0 || K <= 0 || count <= 0 || smCount <= 0)
+        return NTB_PLAN_PAIR_256X256 - 100;         /* no plan: bad argument */
+    Problem p;
+    memset(&p, 0, sizeof(p));
+    p.dtAB = dtypeAB;
+    p.dtC = dtypeAB;
+    p.M = M; p.N = N; p.K = K;
+    p.count = count; p.Q = 1;
+    DeviceCtx ctx;
+    memset(&ctx, 0, sizeof(ctx));
+    ctx.smCount = smCount;
+    return TcTileChoice(ctx, p);
+}
+
 long long ntb_launch_count(void)
 {
     return gLaunches.load();
