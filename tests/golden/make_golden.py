@@ -1,5 +1,5 @@
 """Regenerates the golden fixtures of this folder. Needs the NiuTensor sources
-(REF, default /root/reference) and the compiled reference CPU library
+(their folder in the environment variable REF) and the compiled reference CPU library
 (`make -C oracle ref`); the fixtures themselves are committed so the tests run
 without either.
 
