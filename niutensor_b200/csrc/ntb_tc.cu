@@ -1955,14 +1955,17 @@ int EncodeOutput(CUtensorMap * map, int dtC, void * base, int rows, int cols, lo
  *     and all SMs together about 5800 (what the L2-to-SM fabric delivered to TMA loads in
  *     every kernel timed here), so the more CTAs run, the less each one gets;
  *   - the time of the thread that issues the MMAs: about 47 clocks per instruction plus
- *     about 400 (500 in a CTA pair) per barrier hand-shake, shared by the k-blocks of a group.
+ *     about 400 (500 in a CTA pair) per barrier hand-shake, shared by the k-blocks of a group;
+ *   - its shared-memory traffic at 128 bytes per clock: the bytes TMA writes plus the operand
+ *     bytes every MMA reads back (a 128 x 128 tile reads 8 KB per 64 clocks of math and is
+ *     bound by this at half the MMA rate).
  * Returns the tile width of the single-CTA kernel; 0 / -1 for the CTA-pair kernel with
  * 256 x 256 / 512 x 256 tiles, -8 / -9 for pair tiles of 256 x 128 / 512 x 128; -2 / -4 for
  * the split-K kernel with clusters of 2 / 4 CTAs. Constants were fitted to timings of the
  * benchmark configurations and of mid-size products on a B200.
  */
 struct KbCost {
-    double math, bytes, mmas, shake;
+    double math, bytes, reads, mmas, shake;   /* reads: operand bytes the MMAs fetch from shared memory */
     int g;
 };
 
@@ -1971,7 +1974,8 @@ double PerKBlock(const KbCost & c, long long activeCtas)
     const double perSm = 62.0, fabric = 5800.0;
     const double ingest = fmin(perSm, fabric / (double)(activeCtas > 0 ? activeCtas : 1));
     const double thread = (c.shake + 47.0 * c.mmas * c.g) / c.g;
-    return fmax(c.math, fmax(c.bytes / ingest, thread));
+    const double smem = (c.bytes + c.reads) / 128.0;  /* TMA writes and operand reads share 128 bytes per clock */
+    return fmax(fmax(c.math, smem), fmax(c.bytes / ingest, thread));
 }
 
 int PickBN(const Problem & p, int smCount, int mode)
@@ -1989,7 +1993,9 @@ int PickBN(const Problem & p, int smCount, int mode)
         const long long waves = (tiles + smCount - 1) / smCount;
         KbCost c;
         c.math = mmaPerCol * bn;
-        c.bytes = (double)(BM + bn) * ROW_BYTES * (mode == 0 ? 1 : 1);
+        c.bytes = (double)(BM + bn) * ROW_BYTES;
+        /* fp32: three MMAs per k-step read both planes, and the splitter reads and writes a plane */
+        c.reads = mode == 0 ? c.bytes : 5.0 * c.bytes;
         c.mmas = mode == 0 ? 4.0 : 12.0;
         c.shake = 400.0;
         c.g = (mode == 0 && bn != 256) ? 2 : 1;
@@ -2007,6 +2013,7 @@ int PickBN(const Problem & p, int smCount, int mode)
                 KbCost c;
                 c.math = 2.0 * w * msub;
                 c.bytes = (double)(msub * BM + w / 2) * ROW_BYTES;
+                c.reads = (double)msub * (BM + w / 2) * ROW_BYTES;
                 c.mmas = 4.0 * msub;
                 c.shake = 500.0;
                 c.g = w == 256 ? 1 : 2;
@@ -2031,6 +2038,7 @@ int PickBN(const Problem & p, int smCount, int mode)
             KbCost c;
             c.math = 256.0;
             c.bytes = (double)(BM + 128) * ROW_BYTES;
+            c.reads = c.bytes;
             c.mmas = 4.0;
             c.shake = 400.0;
             c.g = 1;
