@@ -1157,17 +1157,20 @@ __device__ __forceinline__ void TcCommitPair(uint32_t bar)
 
 /*
  * fp16 GEMM on pairs of CTAs (a cluster of two SMs, tcgen05 cta_group::2). A pair owns a
- * (256 * MSUB) x 256 output tile. CTA r of the pair loads, per k-block, MSUB sub-tiles of
- * 128 rows of A (rows j*256 + r*128.. of the tile) and columns r*128.. of the B tile into
- * its own shared memory; the leader (rank 0) issues, per k-step, MSUB 256 x 256 x 16 MMAs
- * that read both CTAs' shared memory, and each CTA's TMEM receives its 128 rows of each
- * accumulator. Every CTA fetches half as much of B per flop as a lone 128 x 256 CTA
- * (MSUB = 1), and with MSUB = 2 half as much again: the rate at which an SM can take in
- * operand tiles, not the tensor pipe, is what bounds the smaller tiles on large products.
+ * (256 * MSUB) x BN output tile, BN = 256 or 128. CTA r of the pair loads, per k-block, MSUB
+ * sub-tiles of 128 rows of A (rows j*256 + r*128.. of the tile) and columns r*BN/2.. of the
+ * B tile into its own shared memory; the leader (rank 0) issues, per k-step, MSUB
+ * 256 x BN x 16 MMAs that read both CTAs' shared memory, and each CTA's TMEM receives its
+ * 128 rows of each accumulator. Every CTA fetches half as much of B per flop as a lone CTA
+ * with the same accumulator, and with MSUB = 2 half as much again: the rate at which
+ * operand tiles reach the SMs, not the tensor pipe, bounds the smaller tiles. The narrow
+ * tile gives mid-size products (a few hundred 128 x 128 blocks of output) twice as many
+ * CTAs at three quarters of the single-CTA kernel's traffic.
  *
- * MSUB = 1 keeps two 256-column accumulators, so the epilogue of a tile overlaps the main
- * loop of the next; MSUB = 2 fills all 512 TMEM columns with one tile and the epilogue runs
- * between main loops while the producer already refills the pipeline.
+ * MSUB = 1 keeps two accumulator sets, so the epilogue of a tile overlaps the main loop of
+ * the next; MSUB = 2 with BN = 256 fills all 512 TMEM columns with one tile and the
+ * epilogue runs between main loops while the producer already refills the pipeline.
+ * G k-blocks share a barrier hand-shake as in the single-CTA kernel.
  *
  * Barriers: full[s] lives in the leader and counts the bytes of both CTAs' loads;
  * empty[s] and tfull[buf] exist in both CTAs and are signalled together by the leader's
