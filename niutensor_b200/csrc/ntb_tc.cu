@@ -672,6 +672,8 @@ GemmTcKernel(const __grid_constant__ TcGroup grp)
     const int lane = threadIdx.x & 31;
     const uint32_t smemBase = (SmemAddr(smemRaw) + 1023u) & ~1023u;
     volatile int * abortPtr = &abortFlag;
+    /* a kernel launched behind this one with programmatic serialisation may start setting up */
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (threadIdx.x == 128 || threadIdx.x == 160) {
         /* Idle epilogue lanes pull the kernel parameters (and one of them the tensor maps)
@@ -742,6 +744,9 @@ GemmTcKernel(const __grid_constant__ TcGroup grp)
     long long wstat[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #endif
     if (threadIdx.x == 0) NTB_MARK(0);
+    /* set-up is done; nothing before this point touched global memory. A kernel launched
+       with programmatic serialisation waits here for the kernels before it in the stream. */
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int firstTile = blockIdx.x;
     const int tileStep = gridDim.x;
 
@@ -1209,6 +1214,8 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t rank = ClusterCtaRank();
     const uint32_t smemBase = (SmemAddr(smemRaw) + 1023u) & ~1023u;
     volatile int * abortPtr = &abortFlag;
+    /* a kernel launched behind this one with programmatic serialisation may start setting up */
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (threadIdx.x == 128 || threadIdx.x == 160) {
         /* idle epilogue lanes in the scheduler partitions of the producer warp and of the
@@ -1257,6 +1264,9 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const long long kernelT0 = clock64();
 #endif
     const int kBlocks = (p.K + EPR - 1) / EPR;
+    /* set-up is done; nothing before this point touched global memory. A kernel launched
+       with programmatic serialisation waits here for the kernels before it in the stream. */
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int firstTile = blockIdx.x >> 1;
     const int tileStep = gridDim.x >> 1;
 
@@ -1551,6 +1561,8 @@ GemmTcSplitKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const uint32_t smemBase = (SmemAddr(smemRaw) + 1023u) & ~1023u;
     const uint32_t recvBase = smemBase + STAGES * STAGE_BYTES;
     volatile int * abortPtr = &abortFlag;
+    /* a kernel launched behind this one with programmatic serialisation may start setting up */
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (threadIdx.x == 128 || threadIdx.x == 160) {
         /* idle epilogue lanes in the scheduler partitions of the producer warp and of the
@@ -1597,6 +1609,9 @@ GemmTcSplitKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
     const int kBlocks = (p.K + EPR - 1) / EPR;
     const int kbLo = (int)((long long)kBlocks * rank / S), kbHi = (int)((long long)kBlocks * (rank + 1) / S);
+    /* set-up is done; nothing before this point touched global memory. A kernel launched
+       with programmatic serialisation waits here for the kernels before it in the stream. */
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int firstTile = blockIdx.x / S;
     const int tileStep = gridDim.x / S;
 
@@ -1811,6 +1826,34 @@ bool BatchSelector(long long sp, long long sq, int P, int Q, int * sel, long lon
     return false;
 }
 
+/* integer tuning knob from the environment, read at every launch */
+int Knob(const char * name, int dflt)
+{
+    const char * v = getenv(name);
+    return v && *v ? atoi(v) : dflt;
+}
+
+/* Launch with programmatic stream serialisation: the next kernel of the stream that was
+   launched the same way may start its set-up (barrier initialisation, TMEM allocation,
+   descriptor fetch) while this one drains; it waits (griddepcontrol.wait) before its first
+   access to global memory. Kernels launched any other way are ordered as always.
+   NTB_PDL=0 turns it off. */
+template <typename... Params, typename... Args>
+cudaError_t LaunchPdl(void (*kern)(Params...), int grid, int block, int smem, cudaStream_t stream, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid, 1, 1);
+    cfg.blockDim = dim3((unsigned)block, 1, 1);
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = Knob("NTB_PDL", 1) != 0 ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
 template <int MODE, int BN, int STAGES, int G, typename OutT, bool OLDC>
 int LaunchOne(const TcGroup & grp, int smCount, cudaStream_t stream)
 {
@@ -1826,9 +1869,9 @@ int LaunchOne(const TcGroup & grp, int smCount, cudaStream_t stream)
         configured[dev] = true;
     }
     const int grid = grp.total < smCount ? grp.total : smCount;
-    kern<<<grid, MODE == 0 ? 192 : 192 + CONV_THREADS, smem, stream>>>(grp);
+    const cudaError_t err = LaunchPdl(kern, grid, MODE == 0 ? 192 : 192 + CONV_THREADS, smem, stream, grp);
     CountLaunch();
-    return cudaGetLastError() == cudaSuccess ? NTB_OK : NTB_ERR_CUDA;
+    return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? NTB_OK : NTB_ERR_CUDA;
 }
 
 template <int S, int STAGES, int G, typename OutT, bool OLDC>
@@ -1845,17 +1888,11 @@ int LaunchSplit(const CUtensorMap & tmA, const CUtensorMap & tmB, const CUtensor
             return NTB_ERR_CUDA;
         configured[dev] = true;
     }
-    kern<<<S * clusters, 192, smem, stream>>>(tmA, tmB, tmC, tp);
+    const cudaError_t err = LaunchPdl(kern, S * clusters, 192, smem, stream, tmA, tmB, tmC, tp);
     CountLaunch();
-    return cudaGetLastError() == cudaSuccess ? NTB_OK : NTB_ERR_CUDA;
+    return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? NTB_OK : NTB_ERR_CUDA;
 }
 
-/* integer tuning knob from the environment, read at every launch */
-int Knob(const char * name, int dflt)
-{
-    const char * v = getenv(name);
-    return v && *v ? atoi(v) : dflt;
-}
 
 /* single-CTA kernel for a group, chosen by operand mode, tile width and output type */
 int LaunchGroup(const TcGroup & grp, int mode, int bn, int dtC, int smCount, cudaStream_t stream)
@@ -1900,9 +1937,9 @@ int LaunchPair(const CUtensorMap & tmA, const CUtensorMap & tmB, const CUtensorM
             return NTB_ERR_CUDA;
         configured[dev] = true;
     }
-    kern<<<2 * pairs, 192, smem, stream>>>(tmA, tmB, tmC, tp);
+    const cudaError_t err = LaunchPdl(kern, 2 * pairs, 192, smem, stream, tmA, tmB, tmC, tp);
     CountLaunch();
-    return cudaGetLastError() == cudaSuccess ? NTB_OK : NTB_ERR_CUDA;
+    return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? NTB_OK : NTB_ERR_CUDA;
 }
 
 int EncodeOperand(CUtensorMap * map, int mode, const void * base, int mnMajor, int rows, int cols,

@@ -428,6 +428,37 @@ def test_seeded_random_shapes_against_the_oracle(oracle):
     status_ok()
 
 
+def test_chains_of_dependent_products_need_no_synchronisation():
+    """Kernels are launched with programmatic stream serialisation (the next one sets up while
+    the previous one drains and waits on the device before touching memory): a chain in
+    which every product reads the previous result, and one that accumulates into the same C,
+    must give bit-for-bit what the same chain gives with a device synchronisation after
+    every call. Shapes small enough for several kernels to be resident at once."""
+    g = torch.Generator(device=DEV)
+    g.manual_seed(77)
+    for (M, K, dtype) in [(128, 128, torch.float16), (256, 512, torch.float16), (192, 128, torch.float32)]:
+        w = (torch.randn(K, K, device=DEV, generator=g) / K ** 0.5).to(dtype)
+        x0 = torch.randn(M, K, device=DEV, generator=g).to(dtype)
+
+        def chain(sync):
+            bufs = [x0.clone(), torch.empty_like(x0)]
+            acc = torch.zeros(M, K, device=DEV, dtype=dtype)
+            for i in range(40):
+                src, dst = bufs[i & 1], bufs[(i + 1) & 1]
+                ops._MatrixMul2D(src, X_NOTRANS, w, X_NOTRANS, dst, 1.0, 0.0)
+                ops._MatrixMul2D(dst, X_NOTRANS, w, X_TRANS, acc, 0.5, 1.0)
+                if sync:
+                    torch.cuda.synchronize()
+            torch.cuda.synchronize()
+            return bufs[0].clone(), acc.clone()
+
+        x_sync, acc_sync = chain(True)
+        for _ in range(3):
+            x_free, acc_free = chain(False)
+            assert torch.equal(x_sync, x_free) and torch.equal(acc_sync, acc_free), (M, K, dtype)
+    status_ok()
+
+
 # --------------------------------------------------------------- semantics corners
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
