@@ -75,6 +75,8 @@ AttentionKernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t smemBase = (SmemAddr(smemRaw) + 1023u) & ~1023u;
     const uint32_t qS = smemBase, kS = qS + Q_BYTES, vS = kS + K_BYTES, pS = vS + V_BYTES, oS = pS + P_BYTES;
     volatile int * abortPtr = &abortFlag;
+    /* a kernel launched behind this one with programmatic serialisation may start setting up */
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (threadIdx.x == 64) {
         PrefetchTensorMap(&tmQ);
@@ -103,6 +105,8 @@ AttentionKernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     TcFenceAfter();
     const uint32_t tmemBase = *(volatile uint32_t *)&tmemBaseSlot;
     const int kBoxes = p.kPad / 64;
+    /* set-up touched no global memory; wait here for the kernels before this one in the stream */
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp == 0) {
         if (lane == 0) {
@@ -393,9 +397,9 @@ extern "C" int ntb_attention(int devID, void * stream,
             configured[devID] = true;
         }
         const int grid = p.totalItems < ctx->smCount ? p.totalItems : ctx->smCount;
-        AttentionKernel<<<grid, 192, ATTN_SMEM, (cudaStream_t)stream>>>(tmQ, tmK, tmV, tmO, p);
+        const cudaError_t err = LaunchPdl(AttentionKernel, grid, 192, ATTN_SMEM, (cudaStream_t)stream, tmQ, tmK, tmV, tmO, p);
         CountLaunch();
-        rc = cudaGetLastError() == cudaSuccess ? NTB_OK : NTB_ERR_CUDA;
+        rc = (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? NTB_OK : NTB_ERR_CUDA;
     } while (0);
     if (rc == NTB_ERR_CUDA)
         cudaGetLastError();

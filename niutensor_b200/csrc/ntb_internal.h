@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <cuda.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include "../../include/ntb_gemm.h"
 
 namespace ntb {
@@ -58,6 +59,34 @@ bool TcEligible(const Problem & p);
 /* *route receives the NTB_ROUTE_* code of the kernel launched */
 int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int * route);
 int LaunchSimt(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream);
+/* NTB_PDL=0 in the environment turns programmatic stream serialisation off */
+inline bool PdlEnabled()
+{
+    const char * v = getenv("NTB_PDL");
+    return !(v && *v && atoi(v) == 0);
+}
+
+/* Launch with programmatic stream serialisation: the next kernel of the stream that was
+   launched the same way may start its set-up (barrier initialisation, TMEM allocation,
+   descriptor fetch) while this one drains; it waits (griddepcontrol.wait) before its first
+   access to global memory. Kernels launched any other way are ordered as always.
+   NTB_PDL=0 turns it off. */
+template <typename... Params, typename... Args>
+cudaError_t LaunchPdl(void (*kern)(Params...), int grid, int block, int smem, cudaStream_t stream, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid, 1, 1);
+    cfg.blockDim = dim3((unsigned)block, 1, 1);
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = PdlEnabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
 /* tile choice of the cost model for p alone: > 0 single-CTA width, <= 0 a cluster kernel (pair or split-K) */
 int TcTileChoice(const DeviceCtx & ctx, const Problem & p);
 /* two tensor-core-eligible problems of equal operand and output types in one launch */

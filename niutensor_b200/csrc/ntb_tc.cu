@@ -1833,27 +1833,6 @@ int Knob(const char * name, int dflt)
     return v && *v ? atoi(v) : dflt;
 }
 
-/* Launch with programmatic stream serialisation: the next kernel of the stream that was
-   launched the same way may start its set-up (barrier initialisation, TMEM allocation,
-   descriptor fetch) while this one drains; it waits (griddepcontrol.wait) before its first
-   access to global memory. Kernels launched any other way are ordered as always.
-   NTB_PDL=0 turns it off. */
-template <typename... Params, typename... Args>
-cudaError_t LaunchPdl(void (*kern)(Params...), int grid, int block, int smem, cudaStream_t stream, Args... args)
-{
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid, 1, 1);
-    cfg.blockDim = dim3((unsigned)block, 1, 1);
-    cfg.dynamicSmemBytes = (size_t)smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = Knob("NTB_PDL", 1) != 0 ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kern, args...);
-}
-
 template <int MODE, int BN, int STAGES, int G, typename OutT, bool OLDC>
 int LaunchOne(const TcGroup & grp, int smCount, cudaStream_t stream)
 {
