@@ -84,6 +84,8 @@ template <typename T>
 __global__ void __launch_bounds__(LS_THREADS) RowStatsKernel(const T * x, int cols, long long ld, bool vec,
                                                              float * rowMax, float * rowSum)
 {
+    /* a product launched behind this kernel with programmatic serialisation may start setting up */
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr int PN = Pack<T>::N;
     const T * row = x + (long long)blockIdx.x * ld;
     float m = -INFINITY, s = 0.f;
@@ -129,6 +131,8 @@ template <typename T>
 __global__ void __launch_bounds__(LS_THREADS) LogSoftmaxApplyKernel(const T * x, T * y, int cols, long long ldx, long long ldy,
                                                                    bool vec, const float * rowMax, const float * rowSum)
 {
+    /* a product launched behind this kernel with programmatic serialisation may start setting up */
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr int PN = Pack<T>::N;
     const T * in = x + (long long)blockIdx.y * ldx;
     T * out = y + (long long)blockIdx.y * ldy;

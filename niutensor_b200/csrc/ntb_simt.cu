@@ -38,6 +38,8 @@ template <> __device__ __forceinline__ __half FromF<__half>(float x) { return __
 template <typename TIn, typename TOut>
 __global__ void __launch_bounds__(NTHREADS) GemmSimtKernel(SimtParams p)
 {
+    /* a product launched behind this kernel with programmatic serialisation may start setting up */
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __shared__ float As[TK][TM + 4];
     __shared__ float Bs[TK][TN + 4];
 
