@@ -459,6 +459,24 @@ def test_chains_of_dependent_products_need_no_synchronisation():
     status_ok()
 
 
+def test_plain_launch_path_without_programmatic_serialisation(oracle):
+    """NTB_PDL=0 launches the same kernels the plain way."""
+    rng = np.random.default_rng(31)
+    a = round_to_half(stored(rng, (), 264, 520, X_NOTRANS))
+    b = round_to_half(stored(rng, (), 520, 136, X_NOTRANS))
+    os.environ["NTB_PDL"] = "0"
+    try:
+        for dtype in (torch.float16, torch.float32):
+            c = torch.zeros(264, 136, device=DEV, dtype=dtype)
+            for _ in range(3):
+                ops._MatrixMul2D(to_dev(a, dtype), X_NOTRANS, to_dev(b, dtype), X_NOTRANS, c, 1.0, 0.0)
+            err = rel_fro(c.float().cpu().numpy(), oracle.matmul2d(a, X_NOTRANS, b, X_NOTRANS, 1.0, 0.0))
+            assert err <= TOL[dtype]
+    finally:
+        os.environ.pop("NTB_PDL", None)
+    status_ok()
+
+
 # --------------------------------------------------------------- semantics corners
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
