@@ -261,8 +261,13 @@ int ntb_gemm_host(int devID, void * stream,
  * a, b, c and the status word -- is a fixed array inside the library, so the staged
  * operands (each rounded up to 256 bytes) must fit in NTB_NOALLOC_MAX_BYTES; a larger
  * problem returns NTB_ERR_LIMIT. Calls on one device share that array: do not overlap
- * them. The first call on a device looks up the array's address; make it before any
- * stream capture begins. The call returns after the result is back in c.
+ * them. The first call on a device looks up the array's address, and with CUDA's default
+ * lazy module loading that look-up is also when the runtime reserves the array's 16 MiB on
+ * the device: make that first call (any tiny product) early -- before the host's pools take
+ * the rest of the GPU's memory and before the process begins any stream capture -- or run
+ * with CUDA_MODULE_LOADING=EAGER; from then on no call allocates anything. The call returns
+ * after the result is back in c; after an error it still waits for copies it had queued.
+ * ntb_set_route() applies as everywhere else.
  */
 #define NTB_NOALLOC_MAX_BYTES (16u << 20)
 int ntb_gemm_host_noalloc(int devID, void * stream,

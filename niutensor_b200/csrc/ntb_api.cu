@@ -176,6 +176,11 @@ void CountLaunch()
     gLaunches.fetch_add(1);
 }
 
+void SetLastRoute(int route)
+{
+    tLastRoute = route;
+}
+
 int ForcedRoute()
 {
     const int r = gForcedRoute.load();

@@ -388,13 +388,10 @@ extern "C" int ntb_attention(int devID, void * stream,
         p.kPad = (lenK + 63) / 64 * 64;
         p.scale = scale;
         p.status = ctx->status;
-        static bool configured[64] = { false };
-        if (devID < 64 && !configured[devID]) {
-            if (cudaFuncSetAttribute(AttentionKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATTN_SMEM) != cudaSuccess) {
-                rc = NTB_ERR_CUDA;
-                break;
-            }
-            configured[devID] = true;
+        static SmemOptIn optIn;
+        if (!optIn.Ensure((const void *)AttentionKernel, ATTN_SMEM)) {
+            rc = NTB_ERR_CUDA;
+            break;
         }
         const int grid = p.totalItems < ctx->smCount ? p.totalItems : ctx->smCount;
         const cudaError_t err = LaunchPdl(AttentionKernel, grid, 192, ATTN_SMEM, (cudaStream_t)stream, tmQ, tmK, tmV, tmO, p);

@@ -6,6 +6,8 @@
 #include <cuda.h>
 #include <stdint.h>
 #include <stdlib.h>
+#include <atomic>
+#include <mutex>
 #include "../../include/ntb_gemm.h"
 
 namespace ntb {
@@ -97,6 +99,33 @@ DeviceCtx * CtxFor(int dev);
 
 void CountLaunch();
 int ForcedRoute();           /* value of the last ntb_set_route() */
+void SetLastRoute(int route); /* what ntb_last_route() reports for the calling thread */
+
+/* The opt-in to more than 48 KB of dynamic shared memory is per kernel and per device. One
+   object per kernel instantiation; threads that share a device may launch concurrently, so
+   the flag is only published after the attribute call has returned. */
+struct SmemOptIn {
+    std::atomic<int> done[64];
+    std::mutex lock;
+    SmemOptIn() { for (int i = 0; i < 64; i++) done[i].store(0); }
+    bool Ensure(const void * kern, int smem)
+    {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess)
+            return false;
+        const bool tracked = dev >= 0 && dev < 64;
+        if (tracked && done[dev].load(std::memory_order_acquire))
+            return true;
+        std::lock_guard<std::mutex> g(lock);
+        if (tracked && done[dev].load(std::memory_order_relaxed))
+            return true;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return false;
+        if (tracked)
+            done[dev].store(1, std::memory_order_release);
+        return true;
+    }
+};
 
 static inline size_t ElemSize(int dt) { return dt == NTB_X_FLOAT16 ? 2 : 4; }
 

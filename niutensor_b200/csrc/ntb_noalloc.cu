@@ -22,7 +22,15 @@
  * threads, or on two streams -- race on the array; callers serialise them.
  *
  * Set-up: the first call on a device resolves the array's device address (with that device
- * current) and caches it; make that first call before starting any stream capture.
+ * current) and caches it. With CUDA's default lazy module loading that look-up is also the
+ * moment the runtime loads the module holding the array and reserves its 16 MiB on the
+ * device, so the promise "no allocation" holds from the second call on: make the first call
+ * (a tiny warm-up product will do) early -- before the host's memory pools take what is left
+ * of the GPU, and before the process begins any stream capture -- or start the process with
+ * CUDA_MODULE_LOADING=EAGER, which reserves the array when the library is loaded.
+ *
+ * Routing follows ntb_set_route() / NTB_ROUTE like every other entry point, and
+ * ntb_last_route() reports the kernel family used.
  */
 #include "ntb_internal.h"
 #include <mutex>
@@ -108,6 +116,7 @@ extern "C" int ntb_gemm_host_noalloc(int devID, void * stream,
     }
     int rc = NTB_OK;
     int hostStatus = 0;
+    bool queued = false, drained = false;     /* work was put on the stream / the stream was synchronised */
     do {
         unsigned char * scratch = nullptr;
         DeviceCtx ctx;
@@ -126,6 +135,7 @@ extern "C" int ntb_gemm_host_noalloc(int devID, void * stream,
         /* the array still holds the previous call's status word: clear it */
         if (cudaMemsetAsync(scratch, 0, HEADER_BYTES, st) != cudaSuccess)
             break;
+        queued = true;
         if (aBytes && cudaMemcpyAsync(dA, a, aBytes, cudaMemcpyHostToDevice, st) != cudaSuccess)
             break;
         if (bBytes && cudaMemcpyAsync(dB, b, bBytes, cudaMemcpyHostToDevice, st) != cudaSuccess)
@@ -145,16 +155,33 @@ extern "C" int ntb_gemm_host_noalloc(int devID, void * stream,
         p.count = 1; p.Q = 1;
         p.alpha = alpha; p.beta = beta;
         int route = NTB_ROUTE_NONE;
-        rc = TcEligible(p) ? LaunchTc(ctx, p, st, &route) : LaunchSimt(ctx, p, st);
+        const int forced = ForcedRoute();
+        if (forced != NTB_ROUTE_SIMT && TcEligible(p)) {
+            rc = LaunchTc(ctx, p, st, &route);
+        }
+        else if (forced == NTB_ROUTE_TC_F16 || forced == NTB_ROUTE_TC_3XTF32 || forced == NTB_ROUTE_TC_F16_PAIR) {
+            rc = NTB_ERR_ARG;                       /* a tensor-core route was demanded and cannot address this */
+        }
+        else {
+            rc = LaunchSimt(ctx, p, st);
+            route = NTB_ROUTE_SIMT;
+        }
         if (rc != NTB_OK)
             break;
+        SetLastRoute(route);
         rc = NTB_ERR_CUDA;
         if (cudaMemcpyAsync(c, dC, cBytes, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
             cudaMemcpyAsync(&hostStatus, scratch, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess ||
             cudaStreamSynchronize(st) != cudaSuccess)
             break;
+        drained = true;
         rc = hostStatus == 0 ? NTB_OK : NTB_ERR_DEVICE_WAIT;
     } while (0);
+    /* After a failure part-way, copies already queued may still read a / b or write the
+       shared array: let them finish, so that the caller's buffers are free on return and the
+       next (serialised) call does not race with this one's leftovers. */
+    if (queued && !drained)
+        cudaStreamSynchronize((cudaStream_t)stream);
     if (rc == NTB_ERR_CUDA)
         cudaGetLastError();
     if (prev >= 0 && prev != devID)

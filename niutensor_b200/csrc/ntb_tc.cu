@@ -37,574 +37,16 @@
  * CTA's abort flag, records NTB_ERR_DEVICE_WAIT in the device status word, and every role
  * leaves its loop; the CTA then lets copies in flight land, frees its TMEM and returns.
  */
-#include "ntb_internal.h"
+#include "ntb_tc_common.cuh"
 #include <cstdio>
-#include "ntb_ptx.cuh"
 #include <cstdlib>
 #include <cmath>
+#include <atomic>
+#include <mutex>
 
 namespace ntb {
 
 namespace {
-
-/* fp32 route: threads that split operands into hi/lo planes (warps 6 and up) */
-#ifndef NTB_CONV_THREADS
-#define NTB_CONV_THREADS 128
-#endif
-constexpr int CONV_THREADS = NTB_CONV_THREADS;
-constexpr int FP32_CHUNK_BLOCKS = 8;  /* fp32 route: 8 k-blocks = 256 of K per TMEM accumulation chain */
-
-/* Division of a 31-bit unsigned number by a run-time constant as multiply-high, add and
-   shift: the tile walk and the batch indices need several divisions per tile, and a
-   hardware-emulated integer division costs about two hundred clocks of latency each. */
-struct FastDiv {
-    uint32_t d, m, s;
-    __host__ void Set(uint32_t div)
-    {
-        d = div ? div : 1;
-        s = 0;
-        while ((1ull << s) < d)
-            s++;
-        m = (uint32_t)((((1ull << 32) * ((1ull << s) - d)) / d) + 1);
-    }
-    __device__ __forceinline__ uint32_t Div(uint32_t n) const { return (__umulhi(n, m) + n) >> s; }
-    __device__ __forceinline__ void DivMod(uint32_t n, uint32_t & q, uint32_t & r) const { q = Div(n); r = n - q * d; }
-};
-
-struct TcParams {
-    void * c;
-    long long ldc, sCp, sCq;
-    int M, N, K, count, Q;
-    int aSel, bSel;         /* which index walks the operand's batch dimension: 0 none, 1 p, 2 q, 3 i */
-    int aMN, bMN;
-    int tilesM, tilesN;
-    int totalTiles;
-    int cVec;               /* C rows can be accessed with 16-byte vectors */
-    int cTma;               /* C is written with TMA stores from swizzled staging boxes */
-    int cSel;               /* index that walks C's batch dimension in its tensor map (as aSel) */
-    int pfDist;             /* producer asks L2 for the boxes of k-block kb + pfDist while loading kb; 0 = off */
-    int group;              /* m-blocks per band of the tile walk */
-    FastDiv fdPerProb, fdBand, fdGroup, fdLast, fdQ;   /* tiles per problem, tiles per band, rows of a full / of the last band, Q */
-    int epiHint;            /* suspend-time hint (ns) of the epilogue warps' barrier probes */
-    void * peers[NTB_MAX_PEERS];   /* further destinations of every result tile (peer GPUs' C), or none */
-    int nPeers;
-    int l2Hint;             /* pair kernel: L2 eviction policy of the A loads (bits 0-1) and B loads (bits 2-3): 0 none, 1 keep, 2 stream */
-    int cPrefetch;          /* wide tiles with beta != 0: 0 no L2 prefetch of old C, 1 boxes through TMA, 2 one request per line */
-    float alpha, beta;
-    const void * bias;      /* N values of C's type added to every output row, or NULL */
-    int act;                /* 1: max(x, 0) applied last */
-    int * status;
-};
-
-/* Optional wait accounting (compile with -DNTB_WAIT_STATS): cycles each role of the
-   CTA-pair kernel spends blocked on its barriers, summed over CTAs.
-   0 producer on empty, 1 MMA on full, 2 MMA on tempty, 3 epilogue warp 2 on tfull,
-   4 kernel cycles of CTA 0's producer lane, 5 CTAs counted */
-#ifdef NTB_WAIT_STATS
-__device__ unsigned long long gWaitStats[8];
-/* timeline of CTA 0 of the single-CTA kernel, in SM clocks since kernel entry:
-   0 set-up done, 1 first TMA issued, 2 first stage landed, 3 first tile's MMAs committed,
-   4 epilogue saw the accumulator, 5 epilogue stores issued, 6 stores complete, 7 kernel end */
-__device__ unsigned long long gTimeline[64];
-#define NTB_MARKK(row, kb) do { if (blockIdx.x == 0 && (kb) < 16 && tlShared[16 + (row) * 16 + (kb)] == 0) tlShared[16 + (row) * 16 + (kb)] = (unsigned long long)(clock64() - kernelT0) + 1; } while (0)
-#define NTB_MARK(slot) do { if (blockIdx.x == 0 && tlShared[slot] == 0) tlShared[slot] = (unsigned long long)(clock64() - kernelT0) + 1; } while (0)
-#ifdef NTB_CLOCKS
-#define NTB_TIMED(slot, expr) do { long long t0_ = clock64(); expr; wstat[slot] += clock64() - t0_; } while (0)
-#else
-#undef NTB_MARK
-#undef NTB_MARKK
-#define NTB_MARK(slot) do { } while (0)
-#define NTB_MARKK(row, kb) do { } while (0)
-#define NTB_TIMED(slot, expr) do { expr; } while (0)
-#endif
-#else
-#define NTB_MARK(slot) do { } while (0)
-#define NTB_MARKK(row, kb) do { } while (0)
-#define NTB_TIMED(slot, expr) do { expr; } while (0)
-#endif
-
-/* ---------------------------------------------------------------- epilogue helpers */
-
-template <typename OutT> struct Vec16;
-template <> struct Vec16<__half> { static constexpr int N = 8; };
-template <> struct Vec16<float>  { static constexpr int N = 4; };
-
-__device__ __forceinline__ void StoreVec(__half * dst, const float * v)
-{
-    uint4 u;
-    __half2 h0 = __floats2half2_rn(v[0], v[1]);
-    __half2 h1 = __floats2half2_rn(v[2], v[3]);
-    __half2 h2 = __floats2half2_rn(v[4], v[5]);
-    __half2 h3 = __floats2half2_rn(v[6], v[7]);
-    u.x = *(uint32_t *)&h0; u.y = *(uint32_t *)&h1; u.z = *(uint32_t *)&h2; u.w = *(uint32_t *)&h3;
-    *(uint4 *)dst = u;
-}
-__device__ __forceinline__ void StoreVec(float * dst, const float * v)
-{
-    *(float4 *)dst = make_float4(v[0], v[1], v[2], v[3]);
-}
-__device__ __forceinline__ void LoadVec(const __half * src, float * v)
-{
-    uint4 u = *(const uint4 *)src;
-    float2 f;
-    f = __half22float2(*(__half2 *)&u.x); v[0] = f.x; v[1] = f.y;
-    f = __half22float2(*(__half2 *)&u.y); v[2] = f.x; v[3] = f.y;
-    f = __half22float2(*(__half2 *)&u.z); v[4] = f.x; v[5] = f.y;
-    f = __half22float2(*(__half2 *)&u.w); v[6] = f.x; v[7] = f.y;
-}
-__device__ __forceinline__ void LoadVec(const float * src, float * v)
-{
-    float4 f = *(const float4 *)src;
-    v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
-}
-__device__ __forceinline__ float LoadOne(const __half * p) { return __half2float(*p); }
-__device__ __forceinline__ float LoadOne(const float * p) { return *p; }
-__device__ __forceinline__ void StoreOne(__half * p, float v) { *p = __float2half_rn(v); }
-__device__ __forceinline__ void StoreOne(float * p, float v) { *p = v; }
-
-/* v <- act(alpha * v (+ beta * old C) (+ bias)) for 32 consecutive columns of one output
-   row starting at column c0; old values and the bias are read with 16-byte vectors where
-   alignment allows it */
-template <typename OutT>
-__device__ __forceinline__ void ScaleRow32(const OutT * cRow, int c0, bool rowOk, float * v, const TcParams & p,
-                                           bool scaled = false)
-{
-    constexpr int VN = Vec16<OutT>::N;
-    if (scaled) {
-        /* the caller has already formed alpha * v + beta * old C */
-    }
-    else if (p.beta == 0.f || !rowOk) {
-#pragma unroll
-        for (int e = 0; e < 32; e++)
-            v[e] = p.alpha * v[e];
-    }
-    else {
-#pragma unroll
-        for (int g = 0; g < 32 / VN; g++) {
-            const int c = c0 + g * VN;
-            float * vv = v + g * VN;
-            if (p.cVec && c + VN <= p.N) {
-                float old[VN];
-                LoadVec(cRow + c, old);
-#pragma unroll
-                for (int e = 0; e < VN; e++)
-                    vv[e] = fmaf(p.beta, old[e], p.alpha * vv[e]);
-            }
-            else {
-#pragma unroll
-                for (int e = 0; e < VN; e++) {
-                    float x = p.alpha * vv[e];
-                    if (c + e < p.N)
-                        x = fmaf(p.beta, LoadOne(cRow + c + e), x);
-                    vv[e] = x;
-                }
-            }
-        }
-    }
-    if (p.bias != nullptr) {
-        const OutT * bias = (const OutT *)p.bias;
-        const bool vec = (((uintptr_t)bias) & 15) == 0;
-#pragma unroll
-        for (int g = 0; g < 32 / VN; g++) {
-            const int c = c0 + g * VN;
-            float * vv = v + g * VN;
-            if (vec && c + VN <= p.N) {
-                float bv[VN];
-                LoadVec(bias + c, bv);
-#pragma unroll
-                for (int e = 0; e < VN; e++)
-                    vv[e] += bv[e];
-            }
-            else {
-#pragma unroll
-                for (int e = 0; e < VN; e++)
-                    if (c + e < p.N)
-                        vv[e] += LoadOne(bias + c + e);
-            }
-        }
-    }
-    if (p.act == NTB_ACT_RECTIFY) {
-#pragma unroll
-        for (int e = 0; e < 32; e++)
-            v[e] = fmaxf(v[e], 0.f);
-    }
-}
-
-/* final values of 32 consecutive columns of one row, straight from registers: 16-byte
-   vectors where the row allows it, element by element at a ragged edge or for rows that
-   are not 16-byte aligned */
-template <typename OutT>
-__device__ __forceinline__ void StoreRow32Direct(OutT * cRow, int c0, const float * v, const TcParams & p)
-{
-    constexpr int VN = Vec16<OutT>::N;
-#pragma unroll
-    for (int g = 0; g < 32 / VN; g++) {
-        const int c = c0 + g * VN;
-        const float * vv = v + g * VN;
-        if (p.cVec && c + VN <= p.N) {
-            StoreVec(cRow + c, vv);
-        }
-        else {
-#pragma unroll
-            for (int e = 0; e < VN; e++)
-                if (c + e < p.N)
-                    StoreOne(cRow + c + e, vv[e]);
-        }
-    }
-}
-
-/*
- * Per-warp writer of output tiles. When C allows it (16-byte aligned base and pitches)
- * the 32 rows x 128 bytes a warp produces are staged in shared memory in the 128-byte
- * swizzled layout (conflict-free for one-row-per-lane writes) and sent to HBM by one TMA
- * store per box: full 128-byte lines, asynchronous, clipped by TMA at the ragged edges of
- * C. Two boxes per warp alternate; before a box is refilled the warp waits until the store
- * that last used it has read it. Otherwise values go out with direct stores.
- *
- * With beta != 0 and tiles of at most two boxes per warp (128 half columns) the old values
- * of C come the same way in the other direction: a TMA load brings each box into the
- * staging buffer that will hold its result, requested when the tile is announced
- * (BeginTile), before the accumulator is waited for, so it arrives under the main loop.
- * One row per lane straight from global memory touches 32 lines per instruction and waits
- * for each 32-column piece in turn; that is what wider tiles still do, after BeginTile
- * has asked L2 to fetch the tile.
- */
-constexpr int EPI_BOX_BYTES = 32 * ROW_BYTES;               /* 32 rows x 128 B */
-constexpr int EPI_BYTES = 4 * 2 * EPI_BOX_BYTES;            /* four epilogue warps, two boxes each */
-
-/* OLDC: the kernel was built for products that read the old C (beta != 0) or that also
-   store their result to peer buffers; without it all of that support compiles away, which
-   keeps the epilogue of the plain beta == 0 product short */
-template <typename OutT, bool OLDC>
-struct TileWriter {
-    static constexpr int BOX_COLS = ROW_BYTES / (int)sizeof(OutT);   /* 64 halves / 32 floats */
-    static constexpr int CHUNKS = 32 * (int)sizeof(OutT) / 16;      /* 16-byte chunks per 32 columns */
-    uint32_t stage;          /* shared-memory address of this warp's two boxes */
-    uint32_t boxes;          /* boxes handed to TMA so far */
-    const CUtensorMap * map;
-    uint32_t bars;           /* two mbarriers, one per box buffer, for the loads of old C values */
-    uint32_t phase;          /* bit b: parity of the next wait on buffer b's barrier */
-    volatile int * abortFlag;
-    int * status;
-    /* old-C fetch plan of the current tile: boxes 0 .. fTotal-1, fPerSub per 128-row sub-tile */
-    bool fOn;
-    int fRow0, fRowStep, fCol0, fPerSub, fTotal, fBatch;
-
-    /* barPair: this warp's two mbarriers (initialised with count 1) */
-    __device__ __forceinline__ void Init(uint32_t epiBase, int sub, const CUtensorMap * m, uint64_t * barPair,
-                                         volatile int * abortPtr, int * statusPtr)
-    {
-        stage = epiBase + sub * 2 * EPI_BOX_BYTES;
-        boxes = 0;
-        map = m;
-        bars = SmemAddr(barPair);
-        phase = 0;
-        abortFlag = abortPtr;
-        status = statusPtr;
-        fOn = false;
-        fTotal = 0;
-        oldCurOk = oldNxtOk = false;
-    }
-
-    /* Old C values of wide tiles (beta != 0, half output): every lane keeps the 64 columns
-       of its row that the next chunk needs in registers, requested one chunk ahead (the
-       first chunk of a tile before the accumulator is waited for), so the memory latency
-       of one chunk runs under the work on the chunk before it. */
-    static constexpr bool OLD_REGS = OLDC && sizeof(OutT) == 2;
-    uint4 oldCur[OLD_REGS ? 8 : 1], oldNxt[OLD_REGS ? 8 : 1];
-    bool oldCurOk, oldNxtOk;
-
-    __device__ __forceinline__ void OldRequest(const TcParams & p, const OutT * cRow, int c0, bool rowOk)
-    {
-        oldNxtOk = false;
-        if (!OLD_REGS)
-            return;
-        oldNxtOk = !fOn && p.beta != 0.f && p.cVec && rowOk && c0 + 64 <= p.N;
-        if (oldNxtOk) {
-#pragma unroll
-            for (int j = 0; j < (OLD_REGS ? 8 : 1); j++)
-                oldNxt[j] = *(const uint4 *)(cRow + c0 + j * 8);
-        }
-    }
-
-    __device__ __forceinline__ void OldAdvance()
-    {
-#pragma unroll
-        for (int j = 0; j < (OLD_REGS ? 8 : 1); j++)
-            oldCur[j] = oldNxt[j];
-        oldCurOk = oldNxtOk;
-        oldNxtOk = false;
-    }
-
-    /* v <- alpha * v + beta * old for the 32 columns whose old values sit in o[0..3] */
-    __device__ __forceinline__ void CombineOld32(const TcParams & p, const uint4 * o, float * v)
-    {
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            float2 f;
-            f = __half22float2(*(const __half2 *)&o[j].x);
-            v[j * 8 + 0] = fmaf(p.beta, f.x, p.alpha * v[j * 8 + 0]); v[j * 8 + 1] = fmaf(p.beta, f.y, p.alpha * v[j * 8 + 1]);
-            f = __half22float2(*(const __half2 *)&o[j].y);
-            v[j * 8 + 2] = fmaf(p.beta, f.x, p.alpha * v[j * 8 + 2]); v[j * 8 + 3] = fmaf(p.beta, f.y, p.alpha * v[j * 8 + 3]);
-            f = __half22float2(*(const __half2 *)&o[j].z);
-            v[j * 8 + 4] = fmaf(p.beta, f.x, p.alpha * v[j * 8 + 4]); v[j * 8 + 5] = fmaf(p.beta, f.y, p.alpha * v[j * 8 + 5]);
-            f = __half22float2(*(const __half2 *)&o[j].w);
-            v[j * 8 + 6] = fmaf(p.beta, f.x, p.alpha * v[j * 8 + 6]); v[j * 8 + 7] = fmaf(p.beta, f.y, p.alpha * v[j * 8 + 7]);
-        }
-    }
-
-    /* lane 0: request old C values of box k of the current tile into buffer bufIdx */
-    __device__ __forceinline__ void FetchBox(const TcParams & p, int k, uint32_t bufIdx)
-    {
-        const int sub = k >= fPerSub ? 1 : 0;
-        const int row0 = fRow0 + sub * fRowStep;
-        const int col = fCol0 + (k - sub * fPerSub) * BOX_COLS;
-        if (row0 < p.M) {
-            const uint32_t bar = bars + bufIdx * 8;
-            MbarExpectTx(bar, EPI_BOX_BYTES);
-            TmaLoad3D(stage + bufIdx * EPI_BOX_BYTES, map, bar, col, row0, fBatch);
-        }
-    }
-
-    /* Announces the next tile of this warp: nSub (1 or 2) sub-tiles of 32 rows starting at
-       row0 and row0 + rowStep, columns col0 .. col0 + cols - 1 (col0 on a box boundary),
-       visited sub-tile by sub-tile, left to right; cLane points at column col0 of row
-       row0 + lane. Call it before waiting for the accumulator. */
-    __device__ __forceinline__ void BeginTile(const TcParams & p, const OutT * cLane, int row0, int rowStep, int nSub,
-                                              int col0, int cols, int batch, int lane)
-    {
-        fOn = false;
-        if (!OLDC || !p.cTma || p.beta == 0.f)
-            return;
-        int live = p.N - col0 < cols ? p.N - col0 : cols;
-        fPerSub = live > 0 ? (live + BOX_COLS - 1) / BOX_COLS : 0;
-        fTotal = fPerSub * nSub;
-        fRow0 = row0; fRowStep = rowStep; fCol0 = col0; fBatch = batch;
-        if (fTotal > 2) {
-            /* more boxes than staging buffers: a later box could only be requested after the
-               store two boxes earlier has left its buffer, and that store queues in the TMA
-               unit behind the next tile's operand loads. Such tiles read old C directly;
-               here it is only pulled into L2. */
-            if (p.cPrefetch == 1 && lane == 0) {
-                for (int k = 0; k < fTotal; k++) {
-                    const int sub = k >= fPerSub ? 1 : 0;
-                    if (fRow0 + sub * fRowStep < p.M)
-                        TmaPrefetch3D(map, fCol0 + (k - sub * fPerSub) * BOX_COLS, fRow0 + sub * fRowStep, fBatch);
-                }
-            }
-            if (p.cPrefetch == 2) {
-                /* every lane asks for the lines of its own rows */
-                for (int sub = 0; sub < nSub; sub++) {
-                    if (row0 + sub * rowStep + lane < p.M) {
-                        const char * line = (const char *)(cLane + (long long)sub * rowStep * p.ldc);
-                        for (int b = 0; b < live * (int)sizeof(OutT); b += 128)
-                            asm volatile("prefetch.global.L2 [%0];" :: "l"(line + b));
-                    }
-                }
-            }
-            return;
-        }
-        fOn = true;
-        if (lane == 0 && fTotal > 0) {
-            /* every earlier store has read its buffer */
-            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-            for (int k = 0; k < fTotal; k++)
-                FetchBox(p, k, (boxes + (uint32_t)k) & 1u);
-        }
-    }
-
-    /* v: raw accumulators of columns c0 .. c0+31 of this lane's row (row = row0 + lane) */
-    __device__ __forceinline__ void Put32(const TcParams & p, OutT * cRow, bool rowOk, int row0, int c0,
-                                          int batch, float * v, int lane)
-    {
-        const bool fromRegs = OLD_REGS && oldCurOk;       /* old values of this chunk are in oldCur */
-        if (fromRegs) {
-            if (c0 & 32)
-                CombineOld32(p, oldCur + (OLD_REGS ? 4 : 0), v);
-            else
-                CombineOld32(p, oldCur, v);
-        }
-        if (!p.cTma) {
-            ScaleRow32(cRow, c0, rowOk, v, p, fromRegs);
-            if (rowOk)
-                StoreRow32Direct(cRow, c0, v, p);
-            return;
-        }
-        const int colInBox = c0 % BOX_COLS;
-        const uint32_t bufIdx = boxes & 1u;
-        const uint32_t box = stage + bufIdx * EPI_BOX_BYTES;
-        const bool live = row0 < p.M;             /* uniform across the warp */
-        if (colInBox == 0) {
-            if (fOn) {
-                /* the old values of this box were requested into this buffer */
-                if (live) {
-                    MbarWait(bars + bufIdx * 8, (phase >> bufIdx) & 1u, abortFlag, status, 20);
-                    phase ^= 1u << bufIdx;
-                }
-                else {
-                    __syncwarp();                 /* lane 0 has waited for the last reader of this buffer */
-                }
-            }
-            else {
-                /* the store that used this box two boxes ago must have read it */
-                if (lane == 0 && boxes >= 2)
-                    asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-                __syncwarp();
-            }
-        }
-        const uint32_t rowAddr = box + lane * ROW_BYTES;
-        const int firstChunk = colInBox * (int)sizeof(OutT) / 16;
-        if (fOn && live) {
-            /* alpha * v + beta * old, the old values read from where the result will go */
-#pragma unroll
-            for (int j = 0; j < CHUNKS; j++) {
-                const uint32_t src = rowAddr + (uint32_t)(((firstChunk + j) ^ (lane & 7)) << 4);
-                uint32_t w0, w1, w2, w3;
-                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3) : "r"(src) : "memory");
-                if (sizeof(OutT) == 2) {
-                    float2 f;
-                    f = __half22float2(*(__half2 *)&w0);
-                    v[j * 8 + 0] = fmaf(p.beta, f.x, p.alpha * v[j * 8 + 0]); v[j * 8 + 1] = fmaf(p.beta, f.y, p.alpha * v[j * 8 + 1]);
-                    f = __half22float2(*(__half2 *)&w1);
-                    v[j * 8 + 2] = fmaf(p.beta, f.x, p.alpha * v[j * 8 + 2]); v[j * 8 + 3] = fmaf(p.beta, f.y, p.alpha * v[j * 8 + 3]);
-                    f = __half22float2(*(__half2 *)&w2);
-                    v[j * 8 + 4] = fmaf(p.beta, f.x, p.alpha * v[j * 8 + 4]); v[j * 8 + 5] = fmaf(p.beta, f.y, p.alpha * v[j * 8 + 5]);
-                    f = __half22float2(*(__half2 *)&w3);
-                    v[j * 8 + 6] = fmaf(p.beta, f.x, p.alpha * v[j * 8 + 6]); v[j * 8 + 7] = fmaf(p.beta, f.y, p.alpha * v[j * 8 + 7]);
-                }
-                else {
-                    v[j * 4 + 0] = fmaf(p.beta, __uint_as_float(w0), p.alpha * v[j * 4 + 0]);
-                    v[j * 4 + 1] = fmaf(p.beta, __uint_as_float(w1), p.alpha * v[j * 4 + 1]);
-                    v[j * 4 + 2] = fmaf(p.beta, __uint_as_float(w2), p.alpha * v[j * 4 + 2]);
-                    v[j * 4 + 3] = fmaf(p.beta, __uint_as_float(w3), p.alpha * v[j * 4 + 3]);
-                }
-            }
-            ScaleRow32(cRow, c0, rowOk, v, p, true);
-        }
-        else {
-            ScaleRow32(cRow, c0, rowOk, v, p, fromRegs);
-        }
-#pragma unroll
-        for (int j = 0; j < CHUNKS; j++) {
-            const uint32_t dst = rowAddr + (uint32_t)(((firstChunk + j) ^ (lane & 7)) << 4);
-            uint32_t w0, w1, w2, w3;
-            if (sizeof(OutT) == 2) {
-                __half2 h0 = __floats2half2_rn(v[j * 8 + 0], v[j * 8 + 1]);
-                __half2 h1 = __floats2half2_rn(v[j * 8 + 2], v[j * 8 + 3]);
-                __half2 h2 = __floats2half2_rn(v[j * 8 + 4], v[j * 8 + 5]);
-                __half2 h3 = __floats2half2_rn(v[j * 8 + 6], v[j * 8 + 7]);
-                w0 = *(uint32_t *)&h0; w1 = *(uint32_t *)&h1; w2 = *(uint32_t *)&h2; w3 = *(uint32_t *)&h3;
-            }
-            else {
-                w0 = __float_as_uint(v[j * 4 + 0]); w1 = __float_as_uint(v[j * 4 + 1]);
-                w2 = __float_as_uint(v[j * 4 + 2]); w3 = __float_as_uint(v[j * 4 + 3]);
-            }
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" :: "r"(dst), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
-        }
-        if (colInBox + 32 == BOX_COLS || c0 + 32 >= p.N) {
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0 && row0 < p.M) {
-                asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
-                             :: "l"(map), "r"(c0 - colInBox), "r"(row0), "r"(batch), "r"(box) : "memory");
-                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-            }
-            if (OLDC && p.nPeers > 0 && live)
-                BoxToPeers(p, cRow - (long long)lane * p.ldc, box, row0, c0 - colInBox, lane);
-            boxes++;
-        }
-    }
-
-    /* The finished box (32 rows x 128 bytes, swizzled in shared memory) goes to the same
-       place of every peer buffer with plain 16-byte stores: eight lanes cover the 128 bytes
-       of one row, so a warp instruction writes four full lines. cBox0 points at row row0,
-       column 0 of this problem's C. */
-    __device__ __forceinline__ void BoxToPeers(const TcParams & p, const OutT * cBox0, uint32_t box, int row0, int col0,
-                                               int lane)
-    {
-        constexpr int VN = Vec16<OutT>::N;
-        const long long base = cBox0 - (const OutT *)p.c;          /* element offset of (row0, 0) in C */
-        const int chunk = lane & 7;
-        const int col = col0 + chunk * VN;
-#pragma unroll
-        for (int r = 0; r < 8; r++) {
-            const int rr = r * 4 + (lane >> 3);
-            uint32_t w0, w1, w2, w3;
-            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3)
-                         : "r"(box + (uint32_t)rr * ROW_BYTES + (uint32_t)((chunk ^ (rr & 7)) << 4)) : "memory");
-            if (row0 + rr < p.M && col + VN <= p.N) {
-                const long long off = base + (long long)rr * p.ldc + col;
-                for (int k = 0; k < p.nPeers; k++)
-                    *(uint4 *)((OutT *)p.peers[k] + off) = make_uint4(w0, w1, w2, w3);
-            }
-            else if (row0 + rr < p.M) {
-                const uint32_t w[4] = { w0, w1, w2, w3 };          /* ragged right edge: element by element */
-                const OutT * e = (const OutT *)w;
-                for (int j = 0; j < VN; j++)
-                    if (col + j < p.N) {
-                        const long long off = base + (long long)rr * p.ldc + col + j;
-                        for (int k = 0; k < p.nPeers; k++)
-                            ((OutT *)p.peers[k])[off] = e[j];
-                    }
-            }
-        }
-    }
-
-    /* all of this warp's stores have read their staging boxes, so shared memory may go
-       away; the writes themselves complete before the grid does */
-    __device__ __forceinline__ void Finish(int lane)
-    {
-        if (lane == 0)
-            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-        __syncwarp();
-    }
-};
-
-/* ---------------------------------------------------------------- tile walk */
-
-struct TileCoord {
-    int prob, mBlk, nBlk;
-};
-
-/* Tiles of one problem are visited in bands of `GROUP` m-blocks, n fastest inside a band's
-   column, so the CTAs running at the same time share A row panels and B column panels
-   in L2. */
-__device__ __forceinline__ TileCoord DecodeTile(int t, const TcParams & p)
-{
-    TileCoord tc;
-    uint32_t prob, r, band, inBand, q, rem;
-    p.fdPerProb.DivMod((uint32_t)t, prob, r);
-    p.fdBand.DivMod(r, band, inBand);
-    const int first = (int)band * p.group;
-    if (p.tilesM - first >= p.group)
-        p.fdGroup.DivMod(inBand, q, rem);
-    else
-        p.fdLast.DivMod(inBand, q, rem);
-    tc.prob = (int)prob;
-    tc.mBlk = first + (int)rem;
-    tc.nBlk = (int)q;
-    return tc;
-}
-
-/* (p, q) = (prob / Q, prob % Q) */
-__device__ __forceinline__ void SplitProb(const TcParams & p, int prob, int & pp, int & qq)
-{
-    uint32_t a, b;
-    p.fdQ.DivMod((uint32_t)prob, a, b);
-    pp = (int)a;
-    qq = (int)b;
-}
-
-__device__ __forceinline__ int BatchCoord(int sel, int prob, const TcParams & p)
-{
-    if (sel == 0)
-        return 0;
-    if (sel == 3)
-        return prob;
-    int pp, qq;
-    SplitProb(p, prob, pp, qq);
-    return sel == 1 ? pp : qq;
-}
 
 /* ---------------------------------------------------------------- the kernel */
 
@@ -1086,734 +528,6 @@ GemmTcKernel(const __grid_constant__ TcGroup grp)
 #endif
 }
 
-/* ---------------------------------------------------------------- the CTA-pair kernel */
-
-__device__ __forceinline__ uint32_t ClusterCtaRank()
-{
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-
-/* address of the same shared-memory object in the CTA of rank `rank` of this cluster */
-__device__ __forceinline__ uint32_t MapToCta(uint32_t addr, uint32_t rank)
-{
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-    return r;
-}
-
-__device__ __forceinline__ void MbarArriveCluster(uint32_t clusterAddr)
-{
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(clusterAddr) : "memory");
-}
-
-__device__ __forceinline__ void ClusterSync()
-{
-    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
-}
-
-/* L2 eviction policy for a stream of loads: 1 keep (evict last), 2 stream (evict first) */
-__device__ __forceinline__ uint64_t L2Policy(int kind)
-{
-    uint64_t pol = 0;
-    if (kind == 1)
-        asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
-    else if (kind == 2)
-        asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
-    return pol;
-}
-
-/* the pair load with an L2 eviction policy */
-__device__ __forceinline__ void TmaLoad3DPairHint(uint32_t dst, const CUtensorMap * map, uint32_t barCluster, int c0, int c1,
-                                                  int c2, uint64_t policy)
-{
-    asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
-                 " [%0], [%1, {%3, %4, %5}], [%2], %6;"
-                 :: "r"(dst), "l"(map), "r"(barCluster), "r"(c0), "r"(c1), "r"(c2), "l"(policy) : "memory");
-}
-
-/* TMA load whose completion bytes are counted on a barrier of the pair's leader CTA */
-__device__ __forceinline__ void TmaLoad3DPair(uint32_t dst, const CUtensorMap * map, uint32_t barCluster, int c0, int c1, int c2)
-{
-    asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
-                 " [%0], [%1, {%3, %4, %5}], [%2];"
-                 :: "r"(dst), "l"(map), "r"(barCluster), "r"(c0), "r"(c1), "r"(c2) : "memory");
-}
-
-__device__ __forceinline__ void TcMmaPairLH(uint32_t dTmem, uint32_t aLo, uint32_t aHi, uint32_t bLo, uint32_t bHi,
-                                            uint32_t iDesc, uint32_t accumulate)
-{
-    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"
-                 "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
-                 "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n\t}"
-                 :: "r"(dTmem), "r"(aLo), "r"(aHi), "r"(bLo), "r"(bHi), "r"(iDesc), "r"(accumulate) : "memory");
-}
-
-/* arrive, once the MMAs issued so far have finished, on the barrier at this offset in
-   both CTAs of the pair */
-__device__ __forceinline__ void TcCommitPair(uint32_t bar)
-{
-    const uint16_t mask = 3;
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-                 :: "r"(bar), "h"(mask) : "memory");
-}
-
-/*
- * fp16 GEMM on pairs of CTAs (a cluster of two SMs, tcgen05 cta_group::2). A pair owns a
- * (256 * MSUB) x BN output tile, BN = 256 or 128. CTA r of the pair loads, per k-block, MSUB
- * sub-tiles of 128 rows of A (rows j*256 + r*128.. of the tile) and columns r*BN/2.. of the
- * B tile into its own shared memory; the leader (rank 0) issues, per k-step, MSUB
- * 256 x BN x 16 MMAs that read both CTAs' shared memory, and each CTA's TMEM receives its
- * 128 rows of each accumulator. Every CTA fetches half as much of B per flop as a lone CTA
- * with the same accumulator, and with MSUB = 2 half as much again: the rate at which
- * operand tiles reach the SMs, not the tensor pipe, bounds the smaller tiles. The narrow
- * tile gives mid-size products (a few hundred 128 x 128 blocks of output) twice as many
- * CTAs at three quarters of the single-CTA kernel's traffic.
- *
- * MSUB = 1 keeps two accumulator sets, so the epilogue of a tile overlaps the main loop of
- * the next; MSUB = 2 with BN = 256 fills all 512 TMEM columns with one tile and the
- * epilogue runs between main loops while the producer already refills the pipeline.
- * G k-blocks share a barrier hand-shake as in the single-CTA kernel.
- *
- * Barriers: full[s] lives in the leader and counts the bytes of both CTAs' loads;
- * empty[s] and tfull[buf] exist in both CTAs and are signalled together by the leader's
- * tcgen05.commit; tempty[buf] lives in the leader and collects the eight epilogue warps
- * of the pair. All waits are local and bounded as in the single-CTA kernel.
- */
-template <int MSUB, int BN, int STAGES, int G, typename OutT, bool OLDC>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
-GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmC, TcParams p)
-{
-    constexpr int ES = 2;
-    constexpr int EPR = ROW_BYTES / ES;                 /* 64 halves of K per stage */
-    constexpr int NSTG = STAGES / G;                    /* barrier pairs: G k-blocks share a hand-shake */
-    static_assert(STAGES % G == 0 && (BN == 256 || BN == 128), "pair tile");
-    constexpr int BNH = BN / 2;                         /* columns of B this CTA loads */
-    constexpr int PM = 2 * BM * MSUB;                   /* rows of the pair's tile */
-    constexpr int NBUF = 2 / MSUB;                      /* accumulator sets that fit in TMEM */
-    constexpr int B_TILE_BYTES = BNH * ROW_BYTES;
-    constexpr int STAGE_BYTES = MSUB * A_TILE_BYTES + B_TILE_BYTES;
-    constexpr int TMEM_COLS = 512;
-    constexpr int KSTEPS = ROW_BYTES / UMMA_K_BYTES;
-    static_assert(MSUB == 1 || MSUB == 2, "one or two A sub-tiles per CTA");
-
-    extern __shared__ uint8_t smemRaw[];
-    __shared__ __align__(8) uint64_t barFull[STAGES];
-    __shared__ __align__(8) uint64_t barEmpty[STAGES];
-    __shared__ __align__(8) uint64_t barTFull[2];
-    __shared__ __align__(8) uint64_t barTEmpty[2];
-    __shared__ __align__(8) uint64_t barOldC[8];    /* per epilogue warp and staging box: old C values have landed */
-    __shared__ uint32_t tmemBaseSlot;
-    __shared__ int abortFlag;
-
-    const int warp = threadIdx.x >> 5;
-    const int lane = threadIdx.x & 31;
-    const uint32_t rank = ClusterCtaRank();
-    const uint32_t smemBase = (SmemAddr(smemRaw) + 1023u) & ~1023u;
-    volatile int * abortPtr = &abortFlag;
-    /* a kernel launched behind this one with programmatic serialisation may start setting up */
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-
-    if (threadIdx.x == 128 || threadIdx.x == 160) {
-        /* idle epilogue lanes in the scheduler partitions of the producer warp and of the
-           MMA warp pull the kernel parameters (one of them also the tensor maps) towards
-           their constant caches while the other warps set up */
-        if (threadIdx.x == 128) {
-            PrefetchTensorMap(&tmA);
-            PrefetchTensorMap(&tmB);
-            if (p.cTma)
-                PrefetchTensorMap(&tmC);
-        }
-        int touch = 0;
-        const int * words = (const int *)&p;
-        for (int w = 0; w < (int)(sizeof(TcParams) / sizeof(int)); w += 8)
-            touch += words[w];
-        asm volatile("" :: "r"(touch));
-    }
-    if (warp == 0) {
-        if (lane < STAGES) {
-            MbarInit(SmemAddr(&barFull[lane]), 1);
-            MbarInit(SmemAddr(&barEmpty[lane]), 1);
-        }
-        else if (lane >= 8 && lane < 10) {
-            MbarInit(SmemAddr(&barTFull[lane - 8]), 1);
-            MbarInit(SmemAddr(&barTEmpty[lane - 8]), 8);
-        }
-        else if (OLDC && lane >= 16 && lane < 24) {
-            MbarInit(SmemAddr(&barOldC[lane - 16]), 1);
-        }
-        if (lane == 0)
-            abortFlag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
-                     :: "r"(SmemAddr(&tmemBaseSlot)), "r"((uint32_t)TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-    }
-    TcFenceBefore();
-    ClusterSync();              /* barriers of both CTAs are initialised before any remote signal */
-    TcFenceAfter();
-    const uint32_t tmemBase = *(volatile uint32_t *)&tmemBaseSlot;
-
-#ifdef NTB_WAIT_STATS
-    long long wstat[4] = {0, 0, 0, 0};
-    const long long kernelT0 = clock64();
-#endif
-    const int kBlocks = (p.K + EPR - 1) / EPR;
-    /* set-up is done; nothing before this point touched global memory. A kernel launched
-       with programmatic serialisation waits here for the kernels before it in the stream. */
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int firstTile = blockIdx.x >> 1;
-    const int tileStep = gridDim.x >> 1;
-
-    if (warp == 0) {
-        if (lane == 0) {
-            int s = 0;
-            uint32_t ph = 0;
-            bool ok = true;
-            for (int t = firstTile; ok && t < p.totalTiles; t += tileStep) {
-                TileCoord tc = DecodeTile(t, p);
-                const int m0 = tc.mBlk * PM + (int)rank * BM;
-                const int n0 = tc.nBlk * BN + (int)rank * BNH;
-                const int ba = BatchCoord(p.aSel, tc.prob, p);
-                const int bb = BatchCoord(p.bSel, tc.prob, p);
-                const bool aMN = p.aMN != 0, bMN = p.bMN != 0;
-                int * const status = p.status;
-                const int hint = p.l2Hint;
-                const uint64_t polA = L2Policy(hint & 3), polB = L2Policy((hint >> 2) & 3);
-                for (int kb = 0; kb < kBlocks; kb += G) {
-                    NTB_TIMED(0, ok = MbarWait(SmemAddr(&barEmpty[s]), ph ^ 1u, abortPtr, status));
-                    if (!ok)
-                        break;
-                    const uint32_t fullLeader = MapToCta(SmemAddr(&barFull[s]), 0);
-                    const int nb = G == 1 ? 1 : (kBlocks - kb < G ? kBlocks - kb : G);
-                    if (rank == 0)
-                        MbarExpectTx(SmemAddr(&barFull[s]), (uint32_t)nb * 2u * STAGE_BYTES);
-#pragma unroll
-                    for (int j = 0; j < G; j++) {
-                        if (j < nb) {
-                            const uint32_t aDst = smemBase + (uint32_t)(s * G + j) * STAGE_BYTES;
-                            const uint32_t bDst = aDst + MSUB * A_TILE_BYTES;
-                            const int k0 = (kb + j) * EPR;
-#pragma unroll
-                            for (int sub = 0; sub < MSUB; sub++) {
-                                const int ms = m0 + sub * 2 * BM;
-                                const uint32_t dst = aDst + sub * A_TILE_BYTES;
-                                if (!aMN) {
-                                    if (hint & 3)
-                                        TmaLoad3DPairHint(dst, &tmA, fullLeader, k0, ms, ba, polA);
-                                    else
-                                        TmaLoad3DPair(dst, &tmA, fullLeader, k0, ms, ba);
-                                }
-                                else {
-#pragma unroll
-                                    for (int i = 0; i < BM / EPR; i++)
-                                        TmaLoad3DPair(dst + i * EPR * ROW_BYTES, &tmA, fullLeader, ms + i * EPR, k0, ba);
-                                }
-                            }
-                            if (!bMN) {
-                                if (hint >> 2)
-                                    TmaLoad3DPairHint(bDst, &tmB, fullLeader, k0, n0, bb, polB);
-                                else
-                                    TmaLoad3DPair(bDst, &tmB, fullLeader, k0, n0, bb);
-                            }
-                            else {
-#pragma unroll
-                                for (int i = 0; i < BNH / EPR; i++) {
-                                    if (hint >> 2)
-                                        TmaLoad3DPairHint(bDst + i * EPR * ROW_BYTES, &tmB, fullLeader, n0 + i * EPR, k0, bb, polB);
-                                    else
-                                        TmaLoad3DPair(bDst + i * EPR * ROW_BYTES, &tmB, fullLeader, n0 + i * EPR, k0, bb);
-                                }
-                            }
-                        }
-                    }
-                    if (++s == NSTG) { s = 0; ph ^= 1u; }
-                }
-            }
-        }
-    }
-    else if (warp == 1) {
-        if (lane == 0 && rank == 0) {
-            const uint32_t iDesc = (1u << 4) | ((uint32_t)(p.aMN ? 1 : 0) << 15) | ((uint32_t)(p.bMN ? 1 : 0) << 16)
-                                 | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
-            const uint32_t aLbo = p.aMN ? EPR * ROW_BYTES : 16, bLbo = p.bMN ? EPR * ROW_BYTES : 16;
-            const uint32_t mnStep = (UMMA_K_BYTES / ES) * ROW_BYTES;
-            const uint32_t aStep = p.aMN ? mnStep : UMMA_K_BYTES;
-            const uint32_t bStep = p.bMN ? mnStep : UMMA_K_BYTES;
-            int s = 0;
-            uint32_t ph = 0;
-            uint32_t it = 0;
-            bool ok = true;
-            int * const status = p.status;
-            /* descriptors of slot 0, k-step 0; in the loop only the start-address field moves */
-            const uint64_t aD0 = SmemDesc(smemBase, aLbo, 1024, 2);
-            const uint64_t bD0 = SmemDesc(smemBase + MSUB * A_TILE_BYTES, bLbo, 1024, 2);
-            const uint32_t aLo0 = (uint32_t)aD0, aHiW = (uint32_t)(aD0 >> 32);
-            const uint32_t bLo0 = (uint32_t)bD0, bHiW = (uint32_t)(bD0 >> 32);
-            const uint32_t aStep4 = aStep >> 4, bStep4 = bStep >> 4;
-            const uint32_t barFull0 = SmemAddr(&barFull[0]), barEmpty0 = SmemAddr(&barEmpty[0]);
-            uint32_t stageOff = 0;                /* s * G * STAGE_BYTES in 16-byte units */
-            for (int t = firstTile; ok && t < p.totalTiles; t += tileStep, ++it) {
-                const uint32_t buf = it % NBUF;
-                NTB_TIMED(2, ok = MbarWait(SmemAddr(&barTEmpty[buf]), ((it / NBUF) & 1u) ^ 1u, abortPtr, status));
-                if (!ok)
-                    break;
-                TcFenceAfter();
-                const uint32_t dTmem = tmemBase + buf * (MSUB * BN);
-                uint32_t acc = 0u;
-                for (int kb = 0; kb < kBlocks; kb += G) {
-                    NTB_TIMED(1, ok = MbarWait(barFull0 + (uint32_t)s * 8u, ph, abortPtr, status));
-                    if (!ok)
-                        break;
-                    TcFenceAfter();
-                    const int nb = G == 1 ? 1 : (kBlocks - kb < G ? kBlocks - kb : G);
-#pragma unroll
-                    for (int j = 0; j < G; j++) {
-                        if (j < nb) {
-                            uint32_t aLo = aLo0 + stageOff + (uint32_t)j * (STAGE_BYTES >> 4);
-                            uint32_t bLo = bLo0 + stageOff + (uint32_t)j * (STAGE_BYTES >> 4);
-#pragma unroll
-                            for (int k = 0; k < KSTEPS; k++) {
-#pragma unroll
-                                for (int sub = 0; sub < MSUB; sub++)
-                                    TcMmaPairLH(dTmem + sub * BN, aLo + (uint32_t)sub * (A_TILE_BYTES >> 4), aHiW, bLo, bHiW, iDesc, acc);
-                                acc = 1u;
-                                aLo += aStep4;
-                                bLo += bStep4;
-                            }
-                        }
-                    }
-                    TcCommitPair(barEmpty0 + (uint32_t)s * 8u);
-                    stageOff += (uint32_t)G * (STAGE_BYTES >> 4);
-                    if (++s == NSTG) { s = 0; ph ^= 1u; stageOff = 0; }
-                }
-                if (ok)
-                    TcCommitPair(SmemAddr(&barTFull[buf]));
-            }
-        }
-    }
-    else {
-        const int sub32 = warp & 3;
-        uint32_t it = 0;
-        bool ok = true;
-        TileWriter<OutT, OLDC> writer;
-        writer.Init(smemBase + STAGES * STAGE_BYTES, sub32, &tmC, &barOldC[sub32 * 2], abortPtr, p.status);
-        for (int t = firstTile; ok && t < p.totalTiles; t += tileStep, ++it) {
-            TileCoord tc = DecodeTile(t, p);
-            const int n0 = tc.nBlk * BN;
-            int pp, qq;
-            SplitProb(p, tc.prob, pp, qq);
-            const int bc = BatchCoord(p.cSel, tc.prob, p);
-            OutT * cBase = (OutT *)p.c + pp * p.sCp + qq * p.sCq;
-            const uint32_t buf = it % NBUF;
-            writer.BeginTile(p, cBase + (long long)(tc.mBlk * PM + (int)rank * BM + sub32 * 32 + lane) * p.ldc + n0,
-                             tc.mBlk * PM + (int)rank * BM + sub32 * 32, 2 * BM, MSUB, n0, BN, bc, lane);
-            {
-                const int r0 = tc.mBlk * PM + (int)rank * BM + sub32 * 32 + lane;
-                writer.OldRequest(p, cBase + (long long)r0 * p.ldc, n0, r0 < p.M);
-            }
-            NTB_TIMED(3, ok = MbarWaitWarp(SmemAddr(&barTFull[buf]), (it / NBUF) & 1u, abortPtr, p.status, (uint32_t)p.epiHint));
-            if (!ok)
-                break;
-            TcFenceAfter();
-#pragma unroll 1
-            for (int sub = 0; sub < MSUB; sub++) {
-                const int row0 = tc.mBlk * PM + sub * 2 * BM + (int)rank * BM + sub32 * 32;
-                const int row = row0 + lane;
-                OutT * cRow = cBase + (long long)row * p.ldc;
-                const bool rowOk = row < p.M;
-                const uint32_t tRow = tmemBase + ((uint32_t)(sub32 * 32) << 16) + buf * (MSUB * BN) + sub * BN;
-#pragma unroll 1
-                for (int ch = 0; ch < BN / 64; ch++) {
-                    const int c0 = n0 + ch * 64;
-                    if (c0 >= p.N)
-                        break;
-                    writer.OldAdvance();
-                    if (ch + 1 < BN / 64 && c0 + 64 < p.N)
-                        writer.OldRequest(p, cRow, c0 + 64, rowOk);
-                    else if (sub + 1 < MSUB)
-                        writer.OldRequest(p, cRow + (long long)(2 * BM) * p.ldc, n0, row + 2 * BM < p.M);
-                    float v[64];
-                    TmemLoad64(tRow + ch * 64, v);
-                    writer.Put32(p, cRow, rowOk, row0, c0, bc, v, lane);
-                    if (c0 + 32 < p.N)
-                        writer.Put32(p, cRow, rowOk, row0, c0 + 32, bc, v + 32, lane);
-                }
-            }
-            TcFenceBefore();
-            __syncwarp();
-            if (lane == 0)
-                MbarArriveCluster(MapToCta(SmemAddr(&barTEmpty[buf]), 0));
-        }
-        writer.Finish(lane);
-    }
-
-#ifdef NTB_WAIT_STATS
-    if (lane == 0 && (warp <= 2)) {
-        if (warp == 0) { atomicAdd(&gWaitStats[0], (unsigned long long)wstat[0]); atomicAdd(&gWaitStats[5], 1ULL);
-                         if (blockIdx.x == 0) atomicAdd(&gWaitStats[4], (unsigned long long)(clock64() - kernelT0)); }
-        if (warp == 1) { atomicAdd(&gWaitStats[1], (unsigned long long)wstat[1]); atomicAdd(&gWaitStats[2], (unsigned long long)wstat[2]); }
-        if (warp == 2) atomicAdd(&gWaitStats[3], (unsigned long long)wstat[3]);
-    }
-#endif
-    __syncwarp();
-    if (*abortPtr) {
-        const long long t0 = clock64();
-        while (clock64() - t0 < 2000000LL) { }
-    }
-    TcFenceBefore();
-    ClusterSync();              /* neither CTA's shared memory or TMEM goes away while the other may still use it */
-    TcFenceAfter();
-    if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;"
-                     :: "r"(tmemBase), "r"((uint32_t)TMEM_COLS) : "memory");
-    }
-}
-
-/* ---------------------------------------------------------------- the split-K kernel */
-
-/* barrier probe that also acquires what other CTAs of the cluster wrote before arriving */
-__device__ __forceinline__ uint32_t MbarTryWaitCluster(uint32_t bar, uint32_t parity, uint32_t hintNs)
-{
-    uint32_t done;
-    asm volatile("{\n\t.reg .pred p;\n\t"
-                 "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
-                 "selp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(done) : "r"(bar), "r"(parity), "r"(hintNs) : "memory");
-    return done;
-}
-
-__device__ __forceinline__ bool MbarWaitClusterWarp(uint32_t bar, uint32_t parity, volatile int * abortFlag, int * status)
-{
-    uint32_t ok = 1;
-    if ((threadIdx.x & 31) == 0) {
-        const long long t0 = clock64();
-        for (uint32_t it = 0; ; ++it) {
-            if (MbarTryWaitCluster(bar, parity, 200))
-                break;
-            if ((it & 63u) == 63u) {
-                if (*abortFlag) { ok = 0; break; }
-                if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-                    *abortFlag = 1;
-                    atomicExch(status, NTB_ERR_DEVICE_WAIT);
-                    ok = 0;
-                    break;
-                }
-            }
-        }
-    }
-    ok = __shfl_sync(0xffffffffu, ok, 0);
-    /* every lane acquires at cluster scope before it reads what the peers wrote */
-    asm volatile("fence.acq_rel.cluster;" ::: "memory");
-    return ok != 0;
-}
-
-/*
- * fp16 GEMM for products with few output tiles and a long K (weight gradients: K is the
- * number of tokens): a cluster of S CTAs shares one 128 x 128 output tile, CTA r running the
- * main loop over the r-th part of the k-blocks with its own TMA pipeline and TMEM
- * accumulators. The partial sums are combined through distributed shared memory as a
- * reduce-scatter: CTA d owns columns [d*W, (d+1)*W) of the tile (W = 128 / S); every other
- * CTA writes its fp32 partial of that slice into CTA d's receive area (st.shared::cluster,
- * swizzled so that one-row-per-lane writes do not collide) and arrives on CTA d's barrier;
- * CTA d adds the S - 1 partials to its own in rank order -- a fixed order, so results do not
- * depend on timing -- and runs the usual epilogue on its slice. No global workspace, no
- * atomics. The receive area is double-buffered; a sender cannot be two tiles ahead of a
- * receiver, because its own wait for tile i+1 needs the receiver's partials of tile i+1,
- * which the receiver's warp sends only after it has consumed tile i.
- */
-template <int S, int STAGES, int G, typename OutT, bool OLDC>
-__global__ void __cluster_dims__(S, 1, 1) __launch_bounds__(192, 1)
-GemmTcSplitKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                  const __grid_constant__ CUtensorMap tmC, TcParams p)
-{
-    constexpr int ES = 2;
-    constexpr int EPR = ROW_BYTES / ES;
-    constexpr int BN = 128;
-    constexpr int W = BN / S;                           /* columns of the tile this CTA finishes */
-    constexpr int B_TILE_BYTES = BN * ROW_BYTES;
-    constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
-    constexpr int TMEM_COLS = 256;
-    constexpr int KSTEPS = ROW_BYTES / UMMA_K_BYTES;
-    constexpr int SLOT_BYTES = BM * W * 4;              /* one sender's slice: 128 rows x W floats */
-    constexpr int RECV_BYTES = 2 * (S - 1) * SLOT_BYTES;
-    constexpr int NSTG = STAGES / G;                    /* barrier pairs: G k-blocks share a hand-shake */
-    static_assert((S == 2 || S == 4) && STAGES % G == 0, "cluster size, k-blocks per hand-shake");
-
-    extern __shared__ uint8_t smemRaw[];
-    __shared__ __align__(8) uint64_t barFull[STAGES];
-    __shared__ __align__(8) uint64_t barEmpty[STAGES];
-    __shared__ __align__(8) uint64_t barTFull[2];
-    __shared__ __align__(8) uint64_t barTEmpty[2];
-    __shared__ __align__(8) uint64_t barOldC[8];    /* per epilogue warp and staging box: old C values have landed */
-    __shared__ __align__(8) uint64_t barRecv[2];
-    __shared__ uint32_t tmemBaseSlot;
-    __shared__ int abortFlag;
-
-    const int warp = threadIdx.x >> 5;
-    const int lane = threadIdx.x & 31;
-    const uint32_t rank = ClusterCtaRank();
-    const uint32_t smemBase = (SmemAddr(smemRaw) + 1023u) & ~1023u;
-    const uint32_t recvBase = smemBase + STAGES * STAGE_BYTES;
-    volatile int * abortPtr = &abortFlag;
-    /* a kernel launched behind this one with programmatic serialisation may start setting up */
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-
-    if (threadIdx.x == 128 || threadIdx.x == 160) {
-        /* idle epilogue lanes in the scheduler partitions of the producer warp and of the
-           MMA warp pull the kernel parameters (one of them also the tensor maps) towards
-           their constant caches while the other warps set up */
-        if (threadIdx.x == 128) {
-            PrefetchTensorMap(&tmA);
-            PrefetchTensorMap(&tmB);
-            if (p.cTma)
-                PrefetchTensorMap(&tmC);
-        }
-        int touch = 0;
-        const int * words = (const int *)&p;
-        for (int w = 0; w < (int)(sizeof(TcParams) / sizeof(int)); w += 8)
-            touch += words[w];
-        asm volatile("" :: "r"(touch));
-    }
-    if (warp == 0) {
-        if (lane < STAGES) {
-            MbarInit(SmemAddr(&barFull[lane]), 1);
-            MbarInit(SmemAddr(&barEmpty[lane]), 1);
-        }
-        else if (lane >= 8 && lane < 10) {
-            MbarInit(SmemAddr(&barTFull[lane - 8]), 1);
-            MbarInit(SmemAddr(&barTEmpty[lane - 8]), 4);
-            MbarInit(SmemAddr(&barRecv[lane - 8]), (S - 1) * 4);
-        }
-        else if (OLDC && lane >= 16 && lane < 24) {
-            MbarInit(SmemAddr(&barOldC[lane - 16]), 1);
-        }
-        if (lane == 0)
-            abortFlag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     :: "r"(SmemAddr(&tmemBaseSlot)), "r"((uint32_t)TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    TcFenceBefore();
-    ClusterSync();              /* every CTA's barriers exist before a peer signals them */
-    TcFenceAfter();
-    const uint32_t tmemBase = *(volatile uint32_t *)&tmemBaseSlot;
-
-    const int kBlocks = (p.K + EPR - 1) / EPR;
-    const int kbLo = (int)((long long)kBlocks * rank / S), kbHi = (int)((long long)kBlocks * (rank + 1) / S);
-    /* set-up is done; nothing before this point touched global memory. A kernel launched
-       with programmatic serialisation waits here for the kernels before it in the stream. */
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int firstTile = blockIdx.x / S;
-    const int tileStep = gridDim.x / S;
-
-    if (warp == 0) {
-        if (lane == 0) {
-            int s = 0;
-            uint32_t ph = 0;
-            bool ok = true;
-            for (int t = firstTile; ok && t < p.totalTiles; t += tileStep) {
-                TileCoord tc = DecodeTile(t, p);
-                const int m0 = tc.mBlk * BM, n0 = tc.nBlk * BN;
-                const int ba = BatchCoord(p.aSel, tc.prob, p);
-                const int bb = BatchCoord(p.bSel, tc.prob, p);
-                const bool aMN = p.aMN != 0, bMN = p.bMN != 0;
-                int * const status = p.status;
-                for (int kb = kbLo; kb < kbHi; kb += G) {
-                    ok = MbarWait(SmemAddr(&barEmpty[s]), ph ^ 1u, abortPtr, status);
-                    if (!ok)
-                        break;
-                    const uint32_t full = SmemAddr(&barFull[s]);
-                    const int nb = G == 1 ? 1 : (kbHi - kb < G ? kbHi - kb : G);
-                    MbarExpectTx(full, (uint32_t)nb * STAGE_BYTES);
-#pragma unroll
-                    for (int j = 0; j < G; j++) {
-                        if (j < nb) {
-                            const uint32_t aDst = smemBase + (uint32_t)(s * G + j) * STAGE_BYTES;
-                            const uint32_t bDst = aDst + A_TILE_BYTES;
-                            const int k0 = (kb + j) * EPR;
-                            if (!aMN) {
-                                TmaLoad3D(aDst, &tmA, full, k0, m0, ba);
-                            }
-                            else {
-#pragma unroll
-                                for (int i = 0; i < BM / EPR; i++)
-                                    TmaLoad3D(aDst + i * EPR * ROW_BYTES, &tmA, full, m0 + i * EPR, k0, ba);
-                            }
-                            if (!bMN) {
-                                TmaLoad3D(bDst, &tmB, full, k0, n0, bb);
-                            }
-                            else {
-#pragma unroll
-                                for (int i = 0; i < BN / EPR; i++)
-                                    TmaLoad3D(bDst + i * EPR * ROW_BYTES, &tmB, full, n0 + i * EPR, k0, bb);
-                            }
-                        }
-                    }
-                    if (++s == NSTG) { s = 0; ph ^= 1u; }
-                }
-            }
-        }
-    }
-    else if (warp == 1) {
-        if (lane == 0) {
-            const uint32_t iDesc = InstrDesc(0, p.aMN, p.bMN, BN);
-            const uint32_t aLbo = p.aMN ? EPR * ROW_BYTES : 16, bLbo = p.bMN ? EPR * ROW_BYTES : 16;
-            const uint32_t mnStep = (UMMA_K_BYTES / ES) * ROW_BYTES;
-            const uint32_t aStep = p.aMN ? mnStep : UMMA_K_BYTES;
-            const uint32_t bStep = p.bMN ? mnStep : UMMA_K_BYTES;
-            int s = 0;
-            uint32_t ph = 0, it = 0;
-            bool ok = true;
-            int * const status = p.status;
-            const uint64_t aD0 = SmemDesc(smemBase, aLbo, 1024, 2);
-            const uint64_t bD0 = SmemDesc(smemBase + A_TILE_BYTES, bLbo, 1024, 2);
-            const uint32_t aLo0 = (uint32_t)aD0, aHiW = (uint32_t)(aD0 >> 32);
-            const uint32_t bLo0 = (uint32_t)bD0, bHiW = (uint32_t)(bD0 >> 32);
-            const uint32_t aStep4 = aStep >> 4, bStep4 = bStep >> 4;
-            const uint32_t barFull0 = SmemAddr(&barFull[0]), barEmpty0 = SmemAddr(&barEmpty[0]);
-            uint32_t stageOff = 0;
-            for (int t = firstTile; ok && t < p.totalTiles; t += tileStep, ++it) {
-                const uint32_t buf = it & 1u;
-                ok = MbarWait(SmemAddr(&barTEmpty[buf]), ((it >> 1) & 1u) ^ 1u, abortPtr, status);
-                if (!ok)
-                    break;
-                TcFenceAfter();
-                const uint32_t dTmem = tmemBase + buf * BN;
-                uint32_t acc = 0u;
-                for (int kb = kbLo; kb < kbHi; kb += G) {
-                    ok = MbarWait(barFull0 + (uint32_t)s * 8u, ph, abortPtr, status);
-                    if (!ok)
-                        break;
-                    TcFenceAfter();
-                    const int nb = G == 1 ? 1 : (kbHi - kb < G ? kbHi - kb : G);
-#pragma unroll
-                    for (int j = 0; j < G; j++) {
-                        if (j < nb) {
-                            uint32_t aLo = aLo0 + stageOff + (uint32_t)j * (STAGE_BYTES >> 4);
-                            uint32_t bLo = bLo0 + stageOff + (uint32_t)j * (STAGE_BYTES >> 4);
-#pragma unroll
-                            for (int k = 0; k < KSTEPS; k++) {
-                                TcMmaLH<0>(dTmem, aLo, aHiW, bLo, bHiW, iDesc, acc);
-                                acc = 1u;
-                                aLo += aStep4;
-                                bLo += bStep4;
-                            }
-                        }
-                    }
-                    TcCommit(barEmpty0 + (uint32_t)s * 8u);
-                    stageOff += (uint32_t)G * (STAGE_BYTES >> 4);
-                    if (++s == NSTG) { s = 0; ph ^= 1u; stageOff = 0; }
-                }
-                if (ok)
-                    TcCommit(SmemAddr(&barTFull[buf]));
-            }
-        }
-    }
-    else {
-        const int sub = warp & 3;
-        const int rowInTile = sub * 32 + lane;
-        uint32_t it = 0;
-        bool ok = true;
-        TileWriter<OutT, OLDC> writer;
-        writer.Init(recvBase + RECV_BYTES, sub, &tmC, &barOldC[sub * 2], abortPtr, p.status);
-        for (int t = firstTile; ok && t < p.totalTiles; t += tileStep, ++it) {
-            TileCoord tc = DecodeTile(t, p);
-            const uint32_t buf = it & 1u;
-            const int row0 = tc.mBlk * BM + sub * 32, row = row0 + lane;
-            const int n0 = tc.nBlk * BN;
-            int pp, qq;
-            SplitProb(p, tc.prob, pp, qq);
-            const int bc = BatchCoord(p.cSel, tc.prob, p);
-            OutT * cRow = (OutT *)p.c + pp * p.sCp + qq * p.sCq + (long long)row * p.ldc;
-            const bool rowOk = row < p.M;
-            writer.BeginTile(p, cRow + n0 + (int)rank * W, row0, 0, 1, n0 + (int)rank * W, W, bc, lane);
-            ok = MbarWaitWarp(SmemAddr(&barTFull[buf]), (it >> 1) & 1u, abortPtr, p.status, (uint32_t)p.epiHint);
-            if (!ok)
-                break;
-            TcFenceAfter();
-            const uint32_t tRow = tmemBase + ((uint32_t)(sub * 32) << 16) + buf * BN;
-            /* this CTA's partial sums of the other CTAs' column slices go to their receive areas */
-#pragma unroll
-            for (int dd = 1; dd < S; dd++) {
-                const uint32_t d = (rank + dd) % S;
-                const uint32_t slot = rank < d ? rank : rank - 1;          /* position among d's senders */
-                const uint32_t dstRow = MapToCta(recvBase + (buf * (S - 1) + slot) * SLOT_BYTES
-                                                 + rowInTile * (W * 4), d);
-#pragma unroll
-                for (int cc = 0; cc < W / 32; cc++) {
-                    float v[32];
-                    TmemLoad32(tRow + d * W + cc * 32, v);
-#pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        const uint32_t chunk = (uint32_t)((cc * 8 + j) ^ (lane & 7));
-                        asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};"
-                                     :: "r"(dstRow + (chunk << 4)), "f"(v[j * 4]), "f"(v[j * 4 + 1]), "f"(v[j * 4 + 2]),
-                                        "f"(v[j * 4 + 3]) : "memory");
-                    }
-                }
-            }
-            asm volatile("fence.acq_rel.cluster;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) {
-#pragma unroll
-                for (int dd = 1; dd < S; dd++)
-                    MbarArriveCluster(MapToCta(SmemAddr(&barRecv[buf]), (rank + dd) % S));
-            }
-            /* this CTA's slice: own partial plus the others', in rank order */
-            ok = MbarWaitClusterWarp(SmemAddr(&barRecv[buf]), (it >> 1) & 1u, abortPtr, p.status);
-            if (!ok)
-                break;
-#pragma unroll
-            for (int cc = 0; cc < W / 32; cc++) {
-                float v[32];
-                TmemLoad32(tRow + rank * W + cc * 32, v);
-#pragma unroll
-                for (int sl = 0; sl < S - 1; sl++) {
-                    const uint32_t srcRow = recvBase + (buf * (S - 1) + sl) * SLOT_BYTES + rowInTile * (W * 4);
-#pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        const uint32_t chunk = (uint32_t)((cc * 8 + j) ^ (lane & 7));
-                        float4 r;
-                        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                                     : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "r"(srcRow + (chunk << 4)) : "memory");
-                        v[j * 4] += r.x; v[j * 4 + 1] += r.y; v[j * 4 + 2] += r.z; v[j * 4 + 3] += r.w;
-                    }
-                }
-                const int c0 = n0 + (int)rank * W + cc * 32;
-                if (c0 < p.N)
-                    writer.Put32(p, cRow, rowOk, row0, c0, bc, v, lane);
-            }
-            TcFenceBefore();
-            __syncwarp();
-            if (lane == 0)
-                MbarArrive(SmemAddr(&barTEmpty[buf]));
-        }
-        writer.Finish(lane);
-    }
-
-    __syncwarp();
-    if (*abortPtr) {
-        const long long t0 = clock64();
-        while (clock64() - t0 < 2000000LL) { }
-    }
-    TcFenceBefore();
-    ClusterSync();              /* no CTA's shared memory goes away while a peer may still write to it */
-    TcFenceAfter();
-    if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
-                     :: "r"(tmemBase), "r"((uint32_t)TMEM_COLS) : "memory");
-    }
-}
-
 /* ---------------------------------------------------------------- host side */
 
 /* offset of operand x for problem i is idx * stride with idx in {p, q, i}; find which */
@@ -1826,11 +540,24 @@ bool BatchSelector(long long sp, long long sq, int P, int Q, int * sel, long lon
     return false;
 }
 
-/* integer tuning knob from the environment, read at every launch */
+/* integer knob from the environment, read at every launch: the knobs that pick a kernel
+   (tests and tuning runs change these between calls of one process) */
 int Knob(const char * name, int dflt)
 {
     const char * v = getenv(name);
     return v && *v ? atoi(v) : dflt;
+}
+
+/* knobs that only tune a kernel already chosen are read once per process */
+struct TuneKnobs {
+    int pfDist, group, epiHint, cPrefetch, l2Hint, l2Promotion, tmaStore, debugChoice;
+};
+const TuneKnobs & Tune()
+{
+    static const TuneKnobs k = { Knob("NTB_PREFETCH_DIST", 0), Knob("NTB_TILE_GROUP", 8), Knob("NTB_EPI_HINT_NS", 2000),
+                                 Knob("NTB_C_PREFETCH", 0), Knob("NTB_L2_HINT", 0), Knob("NTB_L2_PROMOTION", 3),
+                                 Knob("NTB_TMA_STORE", 1), Knob("NTB_DEBUG_CHOICE", 0) };
+    return k;
 }
 
 template <int MODE, int BN, int STAGES, int G, typename OutT, bool OLDC>
@@ -1839,38 +566,15 @@ int LaunchOne(const TcGroup & grp, int smCount, cudaStream_t stream)
     constexpr int stage = (A_TILE_BYTES + BN * ROW_BYTES) * (MODE == 0 ? 1 : 2);
     constexpr int smem = stage * STAGES + EPI_BYTES + 1024;
     auto kern = GemmTcKernel<MODE, BN, STAGES, G, OutT, OLDC>;
-    static bool configured[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-            return NTB_ERR_CUDA;
-        configured[dev] = true;
-    }
+    static SmemOptIn optIn;
+    if (!optIn.Ensure((const void *)kern, smem))
+        return NTB_ERR_CUDA;
     const int grid = grp.total < smCount ? grp.total : smCount;
     const cudaError_t err = LaunchPdl(kern, grid, MODE == 0 ? 192 : 192 + CONV_THREADS, smem, stream, grp);
     CountLaunch();
     return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? NTB_OK : NTB_ERR_CUDA;
 }
 
-template <int S, int STAGES, int G, typename OutT, bool OLDC>
-int LaunchSplit(const CUtensorMap & tmA, const CUtensorMap & tmB, const CUtensorMap & tmC, const TcParams & tp, int clusters,
-                cudaStream_t stream)
-{
-    constexpr int smem = (A_TILE_BYTES + 128 * ROW_BYTES) * STAGES + 2 * (S - 1) * (BM * (128 / S) * 4) + EPI_BYTES + 1024;
-    auto kern = GemmTcSplitKernel<S, STAGES, G, OutT, OLDC>;
-    static bool configured[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-            return NTB_ERR_CUDA;
-        configured[dev] = true;
-    }
-    const cudaError_t err = LaunchPdl(kern, S * clusters, 192, smem, stream, tmA, tmB, tmC, tp);
-    CountLaunch();
-    return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? NTB_OK : NTB_ERR_CUDA;
-}
 
 
 /* single-CTA kernel for a group, chosen by operand mode, tile width and output type */
@@ -1902,24 +606,6 @@ int LaunchGroup(const TcGroup & grp, int mode, int bn, int dtC, int smCount, cud
 #undef NTB_ONE
 }
 
-template <int MSUB, int BN, int STAGES, int G, typename OutT, bool OLDC>
-int LaunchPair(const CUtensorMap & tmA, const CUtensorMap & tmB, const CUtensorMap & tmC, const TcParams & tp, int pairs,
-               cudaStream_t stream)
-{
-    constexpr int smem = (MSUB * A_TILE_BYTES + (BN / 2) * ROW_BYTES) * STAGES + EPI_BYTES + 1024;
-    auto kern = GemmTcPairKernel<MSUB, BN, STAGES, G, OutT, OLDC>;
-    static bool configured[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-            return NTB_ERR_CUDA;
-        configured[dev] = true;
-    }
-    const cudaError_t err = LaunchPdl(kern, 2 * pairs, 192, smem, stream, tmA, tmB, tmC, tp);
-    CountLaunch();
-    return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? NTB_OK : NTB_ERR_CUDA;
-}
 
 int EncodeOperand(CUtensorMap * map, int mode, const void * base, int mnMajor, int rows, int cols,
                   long long ld, long long batchStride, int batchExtent, int tileRows)
@@ -1936,7 +622,7 @@ int EncodeOperand(CUtensorMap * map, int mode, const void * base, int mnMajor, i
        MN-major: the stored row is M (or N) -> box = 128 bytes of MN x one stage of K rows. */
     cuuint32_t box[3] = { (cuuint32_t)epr, (cuuint32_t)(mnMajor ? epr : tileRows), 1 };
     cuuint32_t estr[3] = { 1, 1, 1 };
-    const int promo = Knob("NTB_L2_PROMOTION", 3);   /* tuning: L2 fetch granularity of operand loads */
+    const int promo = Tune().l2Promotion;   /* tuning: L2 fetch granularity of operand loads */
     CUresult r = enc(map, mode == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
                      3, (void *)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      (mode != 0 && mnMajor) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
@@ -2121,13 +807,13 @@ int Prepare(const DeviceCtx & ctx, const Problem & p, int mode, int bn, bool pai
     for (int i = 0; i < NTB_MAX_PEERS; i++)
         tp.peers[i] = i < p.nPeers ? p.peers[i] : nullptr;
     tp.status = ctx.status;
-    tp.pfDist = Knob("NTB_PREFETCH_DIST", 0);
-    tp.group = Knob("NTB_TILE_GROUP", 8);
+    tp.pfDist = Tune().pfDist;
+    tp.group = Tune().group;
     if (tp.group < 1)
         tp.group = 1;
-    tp.epiHint = Knob("NTB_EPI_HINT_NS", 2000);
-    tp.cPrefetch = Knob("NTB_C_PREFETCH", 0);
-    tp.l2Hint = Knob("NTB_L2_HINT", 0);
+    tp.epiHint = Tune().epiHint;
+    tp.cPrefetch = Tune().cPrefetch;
+    tp.l2Hint = Tune().l2Hint;
     tp.fdPerProb.Set((uint32_t)(tp.tilesM * tp.tilesN));
     tp.fdBand.Set((uint32_t)(tp.group * tp.tilesN));
     tp.fdGroup.Set((uint32_t)tp.group);
@@ -2155,7 +841,7 @@ int Prepare(const DeviceCtx & ctx, const Problem & p, int mode, int bn, bool pai
     long long stC = 0;
     int extC = 1;
     tp.cSel = 0;
-    tp.cTma = tp.cVec && Knob("NTB_TMA_STORE", 1) != 0 && p.ldc >= p.N &&
+    tp.cTma = tp.cVec && Tune().tmaStore != 0 && p.ldc >= p.N &&
               BatchSelector(p.sCp, p.sCq, P, p.Q, &tp.cSel, &stC, &extC) && stC >= 0;
     if (tp.cTma) {
         rc = EncodeOutput(&maps[2], p.dtC, p.c, p.M, p.N, p.ldc, stC, extC);
@@ -2204,7 +890,7 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
     if (pair)
         bn = bn <= -8 ? 128 : 256;
     *route = mode != 0 ? NTB_ROUTE_TC_3XTF32 : pair ? NTB_ROUTE_TC_F16_PAIR : NTB_ROUTE_TC_F16;
-    if (Knob("NTB_DEBUG_CHOICE", 0))
+    if (Tune().debugChoice)
         fprintf(stderr, "ntb: M %d N %d K %d count %d -> %s width %d msub %d split %d\n", p.M, p.N, p.K, p.count,
                 pair ? "pair" : split ? "split-K" : "single", bn, msub, split);
 
@@ -2228,16 +914,7 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
         const int clusters = (int)(tp.totalTiles < ctx.smCount / split ? tp.totalTiles : ctx.smCount / split);
         const bool half = p.dtC == NTB_X_FLOAT16;
         const bool oldc = tp.beta != 0.f || tp.nPeers > 0;
-#define NTB_SPLIT(SS, ST, GG, T) (oldc ? LaunchSplit<SS, ST, GG, T, true>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, clusters, stream) \
-                                       : LaunchSplit<SS, ST, GG, T, false>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, clusters, stream))
-        const int sg = Knob("NTB_SPLIT_G", 2);
-        if (split == 2) {
-            if (sg == 1)
-                return half ? NTB_SPLIT(2, 4, 1, __half) : NTB_SPLIT(2, 4, 1, float);
-            return half ? NTB_SPLIT(2, 4, 2, __half) : NTB_SPLIT(2, 4, 2, float);
-        }
-        return half ? NTB_SPLIT(4, 3, 1, __half) : NTB_SPLIT(4, 3, 1, float);
-#undef NTB_SPLIT
+        return LaunchSplitKernel(split, Knob("NTB_SPLIT_G", 2), half, oldc, grp.tm[0], tp, clusters, stream);
     }
     if (pair) {
         const TcParams & tp = grp.p[0];
@@ -2248,16 +925,7 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
            four (NTB_PAIR_G = 4) gain a few per cent on short K and lose more on long K */
         const int g = Knob("NTB_PAIR_G", 2);
         const bool oldc = tp.beta != 0.f || tp.nPeers > 0;
-#define NTB_PAIR2(MS, W, ST, GG, T) (oldc ? LaunchPair<MS, W, ST, GG, T, true>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, pairs, stream) \
-                                          : LaunchPair<MS, W, ST, GG, T, false>(grp.tm[0][0], grp.tm[0][1], grp.tm[0][2], tp, pairs, stream))
-#define NTB_PAIR(MS, W, ST, GG) (half ? NTB_PAIR2(MS, W, ST, GG, __half) : NTB_PAIR2(MS, W, ST, GG, float))
-        if (bn == 256)
-            return msub == 2 ? NTB_PAIR(2, 256, 4, 1) : NTB_PAIR(1, 256, 6, 1);
-        if (msub == 2)
-            return NTB_PAIR(2, 128, 4, 2);
-        return g == 4 ? NTB_PAIR(1, 128, 8, 4) : NTB_PAIR(1, 128, 8, 2);
-#undef NTB_PAIR2
-#undef NTB_PAIR
+        return LaunchPairKernel(msub, bn, g, half, oldc, grp.tm[0], tp, pairs, stream);
     }
     return LaunchGroup(grp, mode, bn, p.dtC, ctx.smCount, stream);
 }
@@ -2309,14 +977,6 @@ int LaunchTcTwo(const DeviceCtx & ctx, const Problem & p0, const Problem & p1, c
 
 
 #ifdef NTB_WAIT_STATS
-extern "C" void ntb_debug_wait_stats(unsigned long long * out)
-{
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out, gWaitStats, sizeof(unsigned long long) * 8);
-    unsigned long long zero[8] = {0};
-    cudaMemcpyToSymbol(gWaitStats, zero, sizeof(zero));
-}
-
 extern "C" void ntb_debug_timeline(unsigned long long * out)
 {
     cudaDeviceSynchronize();
