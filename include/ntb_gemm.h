@@ -234,6 +234,61 @@ int ntb_gemm_peers(int devID, void * stream,
                    float alpha, float beta);
 
 /*
+ * One product sharded over nDev GPUs driven by ONE process -- NiuTensor's own process model
+ * (one process, a worker thread per device: source/train/XWorkerJob.cpp, XLeader.cpp). The
+ * reference never shards an operator; the only cross-device movement it has is a
+ * whole-tensor device-to-device cudaMemcpy after the operator (source/tensor/XUtility.cpp:
+ * 196-201, source/train/XWorkerCollect.cpp:59-78), which is what `gather` replaces.
+ *
+ * devIDs[d] runs shard d on streams[d] (streams == NULL: each device's default stream).
+ * All per-device arrays have nDev entries of device pointers on that device.
+ *
+ * NTB_SHARD_COLUMNS (2-D form, count == 1): a[d] is the whole stored a (replicated); device
+ * d owns columns [lo_d, hi_d) = ntb_shard_range(mc, nDev, d, 8) of c; b[d] is the PACKED
+ * part of the stored b that produces them -- rows lo_d..hi_d-1 of b when transB ==
+ * NTB_X_TRANS (rows of a vocabulary matrix), columns otherwise -- and nb, mb, nc, mc are the
+ * extents of the WHOLE b and c. gather == 0: c[d] is the packed nc x (hi_d - lo_d) block.
+ * gather != 0: every c[d] is a whole nc x mc matrix; device d's epilogue writes its block
+ * into its own c[d] and, over NVLink, into every other c[e] (peer access is enabled here;
+ * old values for beta != 0 are read from c[d] only), and each stream is then made to wait for
+ * all shards, so work queued afterwards on any of the streams sees the whole c.
+ *
+ * NTB_SHARD_BATCH: `count` products of one shape (MatrixMulBatched); device d owns problems
+ * ntb_shard_range(count, nDev, d, 1); a[d], b[d] hold that device's problems, packed.
+ * gather == 0: so does c[d]. gather != 0: every c[d] has room for all `count` results; each
+ * device computes its own in place and copies them to the other devices.
+ *
+ * The call only queues work; it returns without waiting for the GPUs. More than
+ * NTB_MAX_PEERS + 1 devices: NTB_ERR_LIMIT.
+ */
+#define NTB_SHARD_COLUMNS 0
+#define NTB_SHARD_BATCH   1
+int ntb_gemm_sharded(const int * devIDs, int nDev, void * const * streams,
+                     const void * const * a, int transA, const void * const * b, int transB, void * const * c,
+                     int dtypeAB, int dtypeC,
+                     int na, int ma, int nb, int mb, int nc, int mc,
+                     int count, int shardAxis, int gather, float alpha, float beta);
+
+/*
+ * [lo, hi) of `total` units owned by shard `shard` of `shards`: contiguous, balanced in
+ * units of `multiple` (the last shard takes a ragged remainder). The split used by
+ * ntb_gemm_sharded: multiple = 8 for columns, so that fp16 row segments stay 16-byte
+ * aligned, 1 for the batch. No counterpart in the reference, which never shards an operator.
+ */
+void ntb_shard_range(int total, int shards, int shard, int multiple, int * lo, int * hi);
+
+/*
+ * Column shards that a collective left one after the other -- src holds `shards` packed
+ * matrices of rows x colsPerShard, as an all-gather of packed shards writes them -- become
+ * the row-major matrix dst (rows x shards * colsPerShard, row pitch ldDst elements) in one
+ * pass. Used when the whole c is gathered with NCCL instead of by the products' own
+ * epilogues. Addresses and row segments must be 16-byte aligned, else NTB_ERR_ARG. No
+ * counterpart in the reference (it has no collectives).
+ */
+int ntb_unshard_columns(int devID, void * stream, const void * src, void * dst, int dtype,
+                        long long rows, int shards, int colsPerShard, long long ldDst);
+
+/*
  * Host-buffer form: a, b and c are HOST memory (pinned or pageable). Copies the
  * operands (and c when beta != 0) to staging buffers owned by the device context, runs
  * the strided-batched GEMM, copies c back and synchronises the stream. This is what a
@@ -293,6 +348,19 @@ int ntb_set_route(int route);
  * kernel abandoned a bounded wait since the last call (the word is cleared on read).
  */
 int ntb_device_status(int devID);
+
+/*
+ * Test hook for the give-up path of the kernels' bounded waits; it has no counterpart in the
+ * reference, which has no device-side waits. skipKBlock >= 0: from now on the copy engine
+ * producers of the tensor-core kernels (single-CTA and CTA-pair) announce that k-block of
+ * their first tile but never load it, so the consumer's wait on it cannot complete;
+ * waitLimitKiloCycles > 0: waits on `devID` give up after that many thousand SM clocks
+ * instead of about two seconds. The kernel then records NTB_ERR_DEVICE_WAIT, lets copies in
+ * flight land, frees its tensor memory and returns; nothing traps or faults. (-1, 0) restores
+ * normal operation. Process-wide for the producers, per device for the limit; meant for
+ * tests only. Synchronises the device.
+ */
+int ntb_debug_inject(int devID, int skipKBlock, int waitLimitKiloCycles);
 
 /*
  * The kernel the tile cost model picks for `count` fp16 (NTB_X_FLOAT16) or fp32 products

@@ -222,6 +222,90 @@ def run_output_layer(iters, use_graph, with_cublas, dev):
     return line
 
 
+def _compact(line):
+    """The fields of a run_config line that the benchmark's one-line summary carries."""
+    bound = line.get("bound", "tensor")
+    frac = line.get("frac_of_hbm_peak") if bound == "hbm" else line.get("frac_of_tensor_peak")
+    out = {"what": line["what"], "us": round(line["us_per_call"], 2), "tflops": round(line["tflops"], 1),
+           "algorithmic_gb_per_s": round(line["algorithmic_gb_per_s"], 1) if "algorithmic_gb_per_s" in line else None,
+           "bound": bound, "frac": round(frac, 4) if frac is not None else None,
+           "frac_of": "measured HBM copy GB/s" if bound == "hbm" else "measured bf16 cuBLAS burst TFLOP/s",
+           "route": line.get("route")}
+    for k in ("cublas_us_per_call", "unfused_chain_us", "torch_sdpa_us", "torch_matmul_log_softmax_us"):
+        if k in line:
+            out[k.replace("_per_call", "")] = round(line[k], 2)
+    return out
+
+
+def driver_table(dev, iters=60):
+    """Every benchmark configuration except the headline one, timed in this process on one
+    GPU (CUDA-graph replay over an operand ring larger than twice the L2), each beside
+    cuBLAS / torch on the same operands."""
+    table = {}
+    for name in ("1", "2a", "2b", "3a", "3b", "3fused", "4", "4lsm", "5f32"):
+        try:
+            if name == "3fused":
+                line = run_attention(iters, True, True, dev)
+            elif name == "4lsm":
+                line = run_output_layer(iters, True, True, dev)
+            else:
+                line = run_config(name, iters if name != "5f32" else 8, True, True, dev)
+            table[name] = _compact(line)
+        except Exception as exc:
+            table[name] = {"failed": repr(exc)}
+    return table
+
+
+def sharded_table(dev, world, rank, timed):
+    """N > 1: the output layer with the vocabulary sharded over the ranks, logits left
+    sharded (config 4), and the fp32 form of the large square product, column-sharded with C
+    left distributed. `timed(fn, steps)` is the caller's barrier-bracketed timer (max over
+    ranks)."""
+    from . import shard
+    table = {}
+    g = torch.Generator(device=dev)
+    g.manual_seed(1004)
+    rows, hidden, vocab = 256, 512, 65536
+    lo, hi = shard.split_range(vocab, world, rank, 8)
+    nbytes = 2.0 * (rows * hidden + (hi - lo) * hidden + rows * (hi - lo))
+    ring = max(1, min(64, int(math.ceil(2.0 * L2_BYTES / nbytes))))
+    sets = [(torch.randn(rows, hidden, device=dev, generator=g).half(),
+             (torch.randn(hi - lo, hidden, device=dev, generator=g) * 0.02).half(),
+             torch.empty(rows, hi - lo, device=dev, dtype=torch.float16)) for _ in range(ring)]
+    state = {"i": 0}
+
+    def out_layer():
+        h, w_local, c = sets[state["i"] % ring]
+        state["i"] += 1
+        ops._MatrixMul2D(h, X_NOTRANS, w_local, X_TRANS, c, 1.0, 0.0)
+
+    for _ in range(ring):
+        out_layer()
+    ms, _, _ = timed(out_layer, 4 * ring)
+    flops = 2.0 * rows * hidden * vocab
+    table["4"] = {"what": "output layer H*W^T, vocabulary rows sharded over %d ranks, logits left sharded" % world,
+                  "us": round(ms * 1e3, 2), "tflops": round(flops / ms / 1e9, 1),
+                  "algorithmic_gb_per_s_per_gpu": round(nbytes / ms / 1e6, 1), "bound": "hbm",
+                  "timing": "back-to-back calls from Python, max over ranks (host launch gaps included)"}
+    del sets
+    torch.cuda.empty_cache()
+    n = 8192
+    clo, chi = shard.column_shard(n, world, rank)
+    a = (torch.rand(n, n, device=dev, generator=g) * 2 - 1)
+    b = (torch.rand(n, chi - clo, device=dev, generator=g) * 2 - 1)
+    c = torch.randn(n, chi - clo, device=dev, generator=g)
+
+    def big_f32():
+        ops._MatrixMul2D(a, X_NOTRANS, b, X_NOTRANS, c, 1.0, 0.5)
+
+    for _ in range(2):
+        big_f32()
+    ms, _, _ = timed(big_f32, 5)
+    table["5f32"] = {"what": "fp32 8192^3, beta 0.5, column-sharded over %d ranks, C left distributed" % world,
+                     "us": round(ms * 1e3, 1), "tflops": round(2.0 * n * n * n / ms / 1e9, 1), "bound": "tensor"}
+    return table
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--configs", default="1,2a,2b,3a,3b,3fused,4,4lsm,5,5f32")

@@ -17,6 +17,7 @@ MAX_PEERS = 8
 PLAN_PAIR_256X256, PLAN_PAIR_512X256, PLAN_SPLIT_K2, PLAN_SPLIT_K4, PLAN_PAIR_256X128, PLAN_PAIR_512X128 = 0, -1, -2, -4, -8, -9
 NOALLOC_MAX_BYTES = 16 << 20
 ACT_NONE, ACT_RECTIFY = 0, 1
+SHARD_COLUMNS, SHARD_BATCH = 0, 1
 
 _vp = ctypes.c_void_p
 _i = ctypes.c_int
@@ -36,12 +37,17 @@ PROTOTYPES = {
     "ntb_gemm_peers": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, ctypes.POINTER(_vp), _i, _i, _i] + [_i] * 6 + [_ll] * 3 + [_f, _f]),
     "ntb_gemm_list": (_i, [_i, _vp, ctypes.POINTER(_vp), _i, ctypes.POINTER(_vp), _i, ctypes.POINTER(_vp),
                            _i, _i, _i] + [_i] * 6 + [_f, _f]),
+    "ntb_gemm_sharded": (_i, [ctypes.POINTER(_i), _i, ctypes.POINTER(_vp), ctypes.POINTER(_vp), _i, ctypes.POINTER(_vp), _i,
+                              ctypes.POINTER(_vp), _i, _i] + [_i] * 6 + [_i, _i, _i, _f, _f]),
+    "ntb_shard_range": (None, [_i, _i, _i, _i, ctypes.POINTER(_i), ctypes.POINTER(_i)]),
+    "ntb_unshard_columns": (_i, [_i, _vp, _vp, _vp, _i, _ll, _i, _i, _ll]),
     "ntb_gemm_host": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _i, _i] + [_i] * 6 + [_ll] * 3 + [_i, _f, _f]),
     "ntb_gemm_host_noalloc": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _i, _i] + [_i] * 6 + [_f, _f]),
     "ntb_last_route": (_i, []),
     "ntb_set_route": (_i, [_i]),
     "ntb_device_status": (_i, [_i]),
     "ntb_plan": (_i, [_i] * 6),
+    "ntb_debug_inject": (_i, [_i, _i, _i]),
     "ntb_launch_count": (_ll, []),
     "ntb_release": (None, []),
     "ntb_strerror": (ctypes.c_char_p, [_i]),

@@ -19,6 +19,7 @@ std::mutex gLock;
 DeviceCtx * gCtx[MAX_DEV] = { nullptr };
 std::atomic<long long> gLaunches(0);
 std::atomic<int> gForcedRoute(0);
+std::atomic<int> gSkipKBlock(-1);
 thread_local int tLastRoute = NTB_ROUTE_NONE;
 
 /* save / restore the calling thread's current device around a call */
@@ -55,8 +56,8 @@ DeviceCtx * GetCtx(int dev)
     memset(c, 0, sizeof(*c));
     c->devID = dev;
     if (cudaDeviceGetAttribute(&c->smCount, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
-        cudaMalloc((void **)&c->status, sizeof(int)) != cudaSuccess ||
-        cudaMemset(c->status, 0, sizeof(int)) != cudaSuccess) {
+        cudaMalloc((void **)&c->status, 2 * sizeof(int)) != cudaSuccess ||
+        cudaMemset(c->status, 0, 2 * sizeof(int)) != cudaSuccess) {
         cudaGetLastError();
         delete c;
         return nullptr;
@@ -179,6 +180,11 @@ void CountLaunch()
 void SetLastRoute(int route)
 {
     tLastRoute = route;
+}
+
+int InjectedSkipKBlock()
+{
+    return gSkipKBlock.load();
 }
 
 int ForcedRoute()
@@ -615,6 +621,27 @@ int ntb_gemm_host(int devID, void * stream,
         cudaGetLastError();
         return NTB_ERR_CUDA;
     }
+    return NTB_OK;
+}
+
+int ntb_debug_inject(int devID, int skipKBlock, int waitLimitKiloCycles)
+{
+    if (waitLimitKiloCycles < 0)
+        return NTB_ERR_ARG;
+    DeviceGuard guard(devID);
+    if (!guard.ok) {
+        cudaGetLastError();
+        return NTB_ERR_CUDA;
+    }
+    DeviceCtx * ctx = GetCtx(devID);
+    if (!ctx)
+        return NTB_ERR_CUDA;
+    if (cudaDeviceSynchronize() != cudaSuccess ||
+        cudaMemcpy(ctx->status + 1, &waitLimitKiloCycles, sizeof(int), cudaMemcpyHostToDevice) != cudaSuccess) {
+        cudaGetLastError();
+        return NTB_ERR_CUDA;
+    }
+    gSkipKBlock.store(skipKBlock < 0 ? -1 : skipKBlock);
     return NTB_OK;
 }
 

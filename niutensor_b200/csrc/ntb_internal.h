@@ -41,7 +41,7 @@ struct Problem {
 struct DeviceCtx {
     int devID;
     int smCount;
-    int * status;           /* device word written by a kernel that gave up a wait */
+    int * status;           /* two device words: [0] written by a kernel that gave up a wait, [1] test-only wait limit */
     void * stage[3];        /* host-buffer entry point: device staging for a, b, c */
     size_t stageBytes[3];
     /* host-buffer entry point, pipelined form: copy-in and copy-out streams, one event pair per chunk */
@@ -99,6 +99,7 @@ DeviceCtx * CtxFor(int dev);
 
 void CountLaunch();
 int ForcedRoute();           /* value of the last ntb_set_route() */
+int InjectedSkipKBlock();    /* test hook (ntb_debug_inject): k-block whose loads the producers leave out, or -1 */
 void SetLastRoute(int route); /* what ntb_last_route() reports for the calling thread */
 
 /* The opt-in to more than 48 KB of dynamic shared memory is per kernel and per device. One

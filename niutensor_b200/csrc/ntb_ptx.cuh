@@ -21,6 +21,15 @@ constexpr int A_TILE_BYTES = BM * ROW_BYTES;
 constexpr int UMMA_K_BYTES = 32;    /* K extent of one tcgen05.mma: 16 halves / 8 tf32 */
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;   /* about two seconds */
 
+/* The status area of a device is two words: [0] the error code a kernel leaves, [1] a wait
+   limit in units of 1024 clocks set by the host for tests of the give-up path (0, the
+   normal state: WAIT_LIMIT_CYCLES). Only a wait that is already long reads it. */
+__device__ __forceinline__ long long WaitLimit(const int * status)
+{
+    const int k = ((const volatile int *)status)[1];
+    return k > 0 ? ((long long)k << 10) : WAIT_LIMIT_CYCLES;
+}
+
 /* ---------------------------------------------------------------- PTX wrappers */
 
 #ifndef NTB_WAIT_HINT_NS
@@ -81,7 +90,7 @@ __device__ __forceinline__ bool MbarWait(uint32_t bar, uint32_t parity, volatile
         if ((it & 63u) == 0) {
             if (*abortFlag)
                 return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            if (clock64() - t0 > WaitLimit(status)) {
                 *abortFlag = 1;
                 atomicExch(status, NTB_ERR_DEVICE_WAIT);
                 return false;

@@ -209,6 +209,7 @@ GemmTcKernel(const __grid_constant__ TcGroup grp)
                    kernel parameter */
                 const bool aMN = p.aMN != 0, bMN = p.bMN != 0;
                 const int pfDist = p.pfDist, nkb = kBlocks;
+                const int skipKb = t == firstTile ? p.skipKBlock : -1;    /* test hook, -1 in normal use */
                 int * const status = p.status;
                 const CUtensorMap * const mapA = &tmA;
                 const CUtensorMap * const mapB = &tmB;
@@ -226,7 +227,7 @@ GemmTcKernel(const __grid_constant__ TcGroup grp)
                     NTB_MARK(14);
 #pragma unroll
                     for (int j = 0; j < G; j++) {
-                        if (j < nb) {
+                        if (j < nb && kb + j != skipKb) {
                             const uint32_t aDst = smemBase + (uint32_t)(s * G + j) * STAGE_BYTES;
                             const uint32_t bDst = aDst + A_TILE_BYTES;
                             const int k0 = (kb + j) * EPR;
@@ -807,6 +808,7 @@ int Prepare(const DeviceCtx & ctx, const Problem & p, int mode, int bn, bool pai
     for (int i = 0; i < NTB_MAX_PEERS; i++)
         tp.peers[i] = i < p.nPeers ? p.peers[i] : nullptr;
     tp.status = ctx.status;
+    tp.skipKBlock = InjectedSkipKBlock();
     tp.pfDist = Tune().pfDist;
     tp.group = Tune().group;
     if (tp.group < 1)

@@ -52,6 +52,7 @@ struct TcParams {
     const void * bias;      /* N values of C's type added to every output row, or NULL */
     int act;                /* 1: max(x, 0) applied last */
     int * status;
+    int skipKBlock;         /* test hook: the producer arms this k-block of its first tile but never loads it; -1 off */
 };
 
 

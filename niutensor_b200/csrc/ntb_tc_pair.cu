@@ -131,6 +131,7 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 const bool aMN = p.aMN != 0, bMN = p.bMN != 0;
                 int * const status = p.status;
                 const int hint = p.l2Hint;
+                const int skipKb = t == firstTile ? p.skipKBlock : -1;    /* test hook, -1 in normal use */
                 const uint64_t polA = L2Policy(hint & 3), polB = L2Policy((hint >> 2) & 3);
                 for (int kb = 0; kb < kBlocks; kb += G) {
                     NTB_TIMED(0, ok = MbarWait(SmemAddr(&barEmpty[s]), ph ^ 1u, abortPtr, status));
@@ -142,7 +143,7 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         MbarExpectTx(SmemAddr(&barFull[s]), (uint32_t)nb * 2u * STAGE_BYTES);
 #pragma unroll
                     for (int j = 0; j < G; j++) {
-                        if (j < nb) {
+                        if (j < nb && kb + j != skipKb) {
                             const uint32_t aDst = smemBase + (uint32_t)(s * G + j) * STAGE_BYTES;
                             const uint32_t bDst = aDst + MSUB * A_TILE_BYTES;
                             const int k0 = (kb + j) * EPR;

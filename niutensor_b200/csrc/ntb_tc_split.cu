@@ -29,7 +29,7 @@ __device__ __forceinline__ bool MbarWaitClusterWarp(uint32_t bar, uint32_t parit
                 break;
             if ((it & 63u) == 63u) {
                 if (*abortFlag) { ok = 0; break; }
-                if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                if (clock64() - t0 > WaitLimit(status)) {
                     *abortFlag = 1;
                     atomicExch(status, NTB_ERR_DEVICE_WAIT);
                     ok = 0;

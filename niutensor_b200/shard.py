@@ -88,11 +88,31 @@ def matmul_column_shard_to_all(a, transposedA, b_local, transposedB, c_sym, peer
 
 
 def gather_columns(c_local, n_cols, group=None):
-    """All ranks receive the full [..., M, n_cols] matrix from the per-rank column shards."""
+    """All ranks receive the full [..., M, n_cols] matrix from the per-rank column shards.
+
+    Equal shards on CUDA devices take one collective and one pass: all_gather_into_tensor
+    leaves the packed shards one after the other ([world][rows][w]) and one kernel
+    (ntb_unshard_columns) writes them to their columns of the row-major result. Ragged
+    shards, and CPU tensors in the gloo tests, are padded to a common width, gathered as a
+    list and copied into place."""
     world = dist.get_world_size(group)
     widths = [column_shard(n_cols, world, r) for r in range(world)]
     wmax = max(hi - lo for lo, hi in widths)
     lead = tuple(c_local.shape[:-1])
+    es = c_local.element_size()
+    uniform = all(hi - lo == wmax for lo, hi in widths) and wmax * world == n_cols
+    if uniform and c_local.is_cuda and c_local.dtype in (torch.float16, torch.float32) and (wmax * es) % 16 == 0:
+        from . import capi
+        piece = c_local if c_local.is_contiguous() else c_local.contiguous()
+        rows = piece.numel() // wmax
+        packed = torch.empty((world,) + lead + (wmax,), dtype=piece.dtype, device=piece.device)
+        dist.all_gather_into_tensor(packed, piece, group=group)
+        full = torch.empty(lead + (n_cols,), dtype=piece.dtype, device=piece.device)
+        code = capi.X_FLOAT16 if piece.dtype == torch.float16 else capi.X_FLOAT
+        rc = capi.lib().ntb_unshard_columns(piece.device.index, torch.cuda.current_stream(piece.device).cuda_stream,
+                                            packed.data_ptr(), full.data_ptr(), code, rows, world, wmax, n_cols)
+        capi.check(rc, "ntb_unshard_columns")
+        return full
     # equal-sized pieces for all_gather: pad the narrower shards
     piece = torch.zeros(lead + (wmax,), dtype=c_local.dtype, device=c_local.device)
     piece[..., :c_local.shape[-1]] = c_local

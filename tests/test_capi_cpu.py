@@ -54,6 +54,46 @@ def test_argument_checks_run_before_cuda():
     assert capi.strerror(capi.ERR_SHAPE) == "unmatched tensors in multiplication"
 
 
+def test_shard_range_matches_the_python_split():
+    from niutensor_b200 import shard
+    L = capi.lib()
+    lo, hi = ctypes.c_int(), ctypes.c_int()
+    for total in (0, 1, 7, 8, 1000, 8192, 65536):
+        for shards in (1, 2, 3, 4, 8):
+            for mult in (1, 8):
+                for r in range(shards):
+                    L.ntb_shard_range(total, shards, r, mult, ctypes.byref(lo), ctypes.byref(hi))
+                    assert (lo.value, hi.value) == shard.split_range(total, shards, r, mult)
+
+
+def test_sharded_entry_checks_arguments_before_cuda():
+    L = capi.lib()
+    f16 = capi.X_FLOAT16
+    vp = ctypes.c_void_p
+
+    def arr(n, v=4096):
+        return (vp * n)(*([v] * n))
+
+    def call(n_dev=2, devs=None, a=None, ta=1, tb=1, dims=(8, 8, 8, 8, 8, 8), dt=(f16, f16), count=1, axis=0, gather=0):
+        devs = (ctypes.c_int * max(1, n_dev))(*(devs or [0] * max(1, n_dev)))
+        return L.ntb_gemm_sharded(devs, n_dev, None, a if a is not None else arr(max(1, n_dev)), ta, arr(max(1, n_dev)), tb,
+                                  arr(max(1, n_dev)), dt[0], dt[1], *dims, count, axis, gather, 1.0, 0.0)
+
+    assert call(n_dev=0) == capi.ERR_ARG
+    assert call(n_dev=capi.MAX_PEERS + 2) == capi.ERR_LIMIT
+    assert call(axis=5) == capi.ERR_ARG
+    assert call(ta=3) == capi.ERR_ARG
+    assert call(dims=(8, 8, 9, 8, 8, 8)) == capi.ERR_SHAPE
+    assert call(dt=(capi.X_DOUBLE, capi.X_DOUBLE)) == capi.ERR_DTYPE
+    assert call(devs=[0, -1]) == capi.ERR_ARG
+    assert call(count=2, axis=capi.SHARD_COLUMNS) == capi.ERR_ARG       # column shards are for the 2-D form
+    assert call(count=0, axis=capi.SHARD_BATCH) == capi.OK               # nothing to do
+    # un-interleave helper: misaligned shard width (3 halves = 6 bytes)
+    assert L.ntb_unshard_columns(0, None, 4096, 8192, f16, 4, 2, 3, 6) == capi.ERR_ARG
+    assert L.ntb_unshard_columns(0, None, 4096, 8192, f16, 4, 2, 8, 15) == capi.ERR_ARG   # pitch below the row
+    assert L.ntb_unshard_columns(0, None, 4096, 8192, f16, 0, 2, 8, 16) == capi.OK
+
+
 def test_no_cpu_fallback_without_a_device():
     import torch
     if torch.cuda.is_available():
