@@ -67,6 +67,8 @@ extern "C" {
 #define NTB_ROUTE_TC_3XTF32 2   /* tcgen05 kind::tf32, three passes on hi/lo split fp32 */
 #define NTB_ROUTE_SIMT      3   /* FFMA kernel for operands TMA cannot address */
 #define NTB_ROUTE_TC_F16_PAIR 4 /* kind::f16 on CTA pairs (cta_group::2), 256 x 256 tiles */
+#define NTB_ROUTE_TC_F16X2  5   /* large fp32 products: every value as two scaled half pieces, three
+                                   kind::f16 products on CTA pairs (needs scratch for the pieces) */
 
 /*
  * Single GEMM. Replaces _CudaBLASMatrixMUL

@@ -55,6 +55,7 @@ DeviceCtx * GetCtx(int dev)
     DeviceCtx * c = new DeviceCtx();
     memset(c, 0, sizeof(*c));
     c->devID = dev;
+    c->mayAllocate = true;
     if (cudaDeviceGetAttribute(&c->smCount, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
         cudaMalloc((void **)&c->status, 2 * sizeof(int)) != cudaSuccess ||
         cudaMemset(c->status, 0, 2 * sizeof(int)) != cudaSuccess) {
@@ -170,6 +171,67 @@ int GrowStage(DeviceCtx * ctx, int slot, size_t bytes)
 DeviceCtx * CtxFor(int dev)
 {
     return GetCtx(dev);
+}
+
+int EnsureScratch(const DeviceCtx & ctx, int slot, size_t bytes, void ** out)
+{
+    DeviceCtx * c = ctx.mayAllocate ? GetCtx(ctx.devID) : nullptr;
+    if (!c || slot < 0 || slot >= 3)
+        return NTB_ERR_CUDA;
+    std::lock_guard<std::mutex> g(gLock);
+    if (c->scratchBytes[slot] < bytes) {
+        if (c->scratch[slot]) {
+            /* queued work may still use the old buffer */
+            if (cudaDeviceSynchronize() != cudaSuccess) {
+                cudaGetLastError();
+                return NTB_ERR_CUDA;
+            }
+            cudaFree(c->scratch[slot]);
+        }
+        c->scratch[slot] = nullptr;
+        c->scratchBytes[slot] = 0;
+        const size_t want = bytes + bytes / 8;              /* some room, so that slowly growing shapes do not reallocate each time */
+        if (cudaMalloc(&c->scratch[slot], want) != cudaSuccess) {
+            cudaGetLastError();
+            return NTB_ERR_CUDA;
+        }
+        c->scratchBytes[slot] = want;
+    }
+    *out = c->scratch[slot];
+    return NTB_OK;
+}
+
+int ScratchAcquire(const DeviceCtx & ctx, cudaStream_t stream)
+{
+    DeviceCtx * c = ctx.mayAllocate ? GetCtx(ctx.devID) : nullptr;
+    if (!c)
+        return NTB_ERR_CUDA;
+    std::lock_guard<std::mutex> g(gLock);
+    if (c->haveScratchEvent && cudaStreamWaitEvent(stream, c->scratchEvent, 0) != cudaSuccess) {
+        cudaGetLastError();
+        return NTB_ERR_CUDA;
+    }
+    return NTB_OK;
+}
+
+int ScratchRelease(const DeviceCtx & ctx, cudaStream_t stream)
+{
+    DeviceCtx * c = ctx.mayAllocate ? GetCtx(ctx.devID) : nullptr;
+    if (!c)
+        return NTB_ERR_CUDA;
+    std::lock_guard<std::mutex> g(gLock);
+    if (!c->haveScratchEvent) {
+        if (cudaEventCreateWithFlags(&c->scratchEvent, cudaEventDisableTiming) != cudaSuccess) {
+            cudaGetLastError();
+            return NTB_ERR_CUDA;
+        }
+        c->haveScratchEvent = true;
+    }
+    if (cudaEventRecord(c->scratchEvent, stream) != cudaSuccess) {
+        cudaGetLastError();
+        return NTB_ERR_CUDA;
+    }
+    return NTB_OK;
 }
 
 void CountLaunch()
@@ -723,6 +785,11 @@ void ntb_release(void)
                     cudaEventDestroy(c->evOut[i]);
                 }
             }
+            for (int s = 0; s < 3; s++)
+                if (c->scratch[s])
+                    cudaFree(c->scratch[s]);
+            if (c->haveScratchEvent)
+                cudaEventDestroy(c->scratchEvent);
             cudaFree(c->status);
         }
         if (prev >= 0)

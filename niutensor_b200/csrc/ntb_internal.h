@@ -48,6 +48,13 @@ struct DeviceCtx {
     cudaStream_t copyIn, copyOut;
     cudaEvent_t evIn[16], evOut[16], evStart;
     bool pipeReady;
+    /* fp32-as-two-halves route: planes of a and b, scale vectors; shared by the calls on this
+       device, which are ordered on the device through scratchEvent */
+    bool mayAllocate;       /* false for the context of the entry point that must not allocate */
+    void * scratch[3];
+    size_t scratchBytes[3];
+    cudaEvent_t scratchEvent;
+    bool haveScratchEvent;
 };
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
@@ -96,6 +103,20 @@ int LaunchTcTwo(const DeviceCtx & ctx, const Problem & p0, const Problem & p1, c
 
 /* the device's context (created on first use); the caller has made `dev` current */
 DeviceCtx * CtxFor(int dev);
+/* scratch buffer `slot` of the device's context, at least `bytes` long (grown with cudaMalloc when
+   needed, after the device has finished with the old one); the device is current */
+int EnsureScratch(const DeviceCtx & ctx, int slot, size_t bytes, void ** out);
+/* orders this stream behind the last use of the device's scratch / marks a new last use */
+int ScratchAcquire(const DeviceCtx & ctx, cudaStream_t stream);
+int ScratchRelease(const DeviceCtx & ctx, cudaStream_t stream);
+/* tensor maps of an operand and of the output (ntb_tc.cu) */
+int EncodeOperandMap(CUtensorMap * map, int mode, const void * base, int mnMajor, int rows, int cols,
+                     long long ld, long long batchStride, int batchExtent, int tileRows);
+int EncodeOutputMap(CUtensorMap * map, int dtC, void * base, int rows, int cols, long long ld,
+                    long long batchStride, int batchExtent);
+/* large 2-D fp32 products as three half-precision products of split operands (ntb_tc_f32pair.cu) */
+bool F32SplitEligible(const DeviceCtx & ctx, const Problem & p);
+int LaunchF32Split(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream);
 
 void CountLaunch();
 int ForcedRoute();           /* value of the last ntb_set_route() */

@@ -758,6 +758,18 @@ int PickBN(const Problem & p, int smCount, int mode)
 
 }
 
+int EncodeOperandMap(CUtensorMap * map, int mode, const void * base, int mnMajor, int rows, int cols,
+                     long long ld, long long batchStride, int batchExtent, int tileRows)
+{
+    return EncodeOperand(map, mode, base, mnMajor, rows, cols, ld, batchStride, batchExtent, tileRows);
+}
+
+int EncodeOutputMap(CUtensorMap * map, int dtC, void * base, int rows, int cols, long long ld,
+                    long long batchStride, int batchExtent)
+{
+    return EncodeOutput(map, dtC, base, rows, cols, ld, batchStride, batchExtent);
+}
+
 bool TcEligible(const Problem & p)
 {
     if (p.M <= 0 || p.N <= 0 || p.K <= 0 || p.count <= 0)
@@ -858,8 +870,16 @@ int Prepare(const DeviceCtx & ctx, const Problem & p, int mode, int bn, bool pai
 int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int * route)
 {
     const int mode = p.dtAB == NTB_X_FLOAT16 ? 0 : 1;
-    int bn = PickBN(p, ctx.smCount, mode);
     const int forced = ForcedRoute();
+    /* large 2-D fp32 products: two half-precision pieces per value on the fp16 pipe of CTA
+       pairs (NTB_F32_SPLIT=0, or a forced kind::tf32 route, keeps them on the tf32 kernel) */
+    if (mode == 1 && forced != NTB_ROUTE_TC_3XTF32 && Knob("NTB_F32_SPLIT", 1) != 0 && F32SplitEligible(ctx, p)) {
+        const int rc = LaunchF32Split(ctx, p, stream);
+        if (rc == NTB_OK)
+            *route = NTB_ROUTE_TC_F16X2;
+        return rc;
+    }
+    int bn = PickBN(p, ctx.smCount, mode);
     const int knobBN = Knob("NTB_BN", 0);           /* tuning: force the single-CTA tile width */
     if (knobBN == 64 || knobBN == 128 || (knobBN == 256 && mode == 0))
         bn = knobBN;
@@ -888,7 +908,11 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
     if (split)
         bn = 128;
     const bool pair = bn <= 0;
-    const int msub = (bn == -1 || bn == -9) ? 2 : 1;
+    int msub = (bn == -1 || bn == -9) ? 2 : 1;
+    /* tuning: height of the pair tile in 256-row units (the model's choice otherwise) */
+    const int knobMsub = Knob("NTB_PAIR_MSUB", 0);
+    if (pair && (knobMsub == 1 || knobMsub == 2))
+        msub = knobMsub;
     if (pair)
         bn = bn <= -8 ? 128 : 256;
     *route = mode != 0 ? NTB_ROUTE_TC_3XTF32 : pair ? NTB_ROUTE_TC_F16_PAIR : NTB_ROUTE_TC_F16;
@@ -927,7 +951,9 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
            four (NTB_PAIR_G = 4) gain a few per cent on short K and lose more on long K */
         const int g = Knob("NTB_PAIR_G", 2);
         const bool oldc = tp.beta != 0.f || tp.nPeers > 0;
-        return LaunchPairKernel(msub, bn, g, half, oldc, grp.tm[0], tp, pairs, stream);
+        /* tuning: epilogue warps of the 512 x 256 tile (8: two per tensor-memory sub-partition) */
+        const int epiWarps = Knob("NTB_PAIR_EPIW", 8) == 4 ? 4 : 8;
+        return LaunchPairKernel(msub, bn, g, epiWarps, half, oldc, grp.tm[0], tp, pairs, stream);
     }
     return LaunchGroup(grp, mode, bn, p.dtC, ctx.smCount, stream);
 }

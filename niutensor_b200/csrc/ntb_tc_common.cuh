@@ -57,7 +57,7 @@ struct TcParams {
 
 
 /* launchers of the cluster kernels (ntb_tc_pair.cu, ntb_tc_split.cu); maps: A, B, C */
-int LaunchPairKernel(int msub, int bn, int g, bool half, bool oldc, const CUtensorMap * maps, const TcParams & tp,
+int LaunchPairKernel(int msub, int bn, int g, int epiWarps, bool half, bool oldc, const CUtensorMap * maps, const TcParams & tp,
                      int pairs, cudaStream_t stream);
 int LaunchSplitKernel(int split, int g, bool half, bool oldc, const CUtensorMap * maps, const TcParams & tp,
                       int clusters, cudaStream_t stream);
@@ -250,7 +250,9 @@ constexpr int EPI_BYTES = 4 * 2 * EPI_BOX_BYTES;            /* four epilogue war
 /* OLDC: the kernel was built for products that read the old C (beta != 0) or that also
    store their result to peer buffers; without it all of that support compiles away, which
    keeps the epilogue of the plain beta == 0 product short */
-template <typename OutT, bool OLDC>
+/* NBOX: staging boxes this warp alternates between (2, or 1 where eight epilogue warps
+   share the staging space of four) */
+template <typename OutT, bool OLDC, int NBOX = 2>
 struct TileWriter {
     static constexpr int BOX_COLS = ROW_BYTES / (int)sizeof(OutT);   /* 64 halves / 32 floats */
     static constexpr int CHUNKS = 32 * (int)sizeof(OutT) / 16;      /* 16-byte chunks per 32 columns */
@@ -269,7 +271,7 @@ struct TileWriter {
     __device__ __forceinline__ void Init(uint32_t epiBase, int sub, const CUtensorMap * m, uint64_t * barPair,
                                          volatile int * abortPtr, int * statusPtr)
     {
-        stage = epiBase + sub * 2 * EPI_BOX_BYTES;
+        stage = epiBase + sub * NBOX * EPI_BOX_BYTES;
         boxes = 0;
         map = m;
         bars = SmemAddr(barPair);
@@ -355,7 +357,7 @@ struct TileWriter {
         fPerSub = live > 0 ? (live + BOX_COLS - 1) / BOX_COLS : 0;
         fTotal = fPerSub * nSub;
         fRow0 = row0; fRowStep = rowStep; fCol0 = col0; fBatch = batch;
-        if (fTotal > 2) {
+        if (fTotal > NBOX) {
             /* more boxes than staging buffers: a later box could only be requested after the
                store two boxes earlier has left its buffer, and that store queues in the TMA
                unit behind the next tile's operand loads. Such tiles read old C directly;
@@ -384,7 +386,7 @@ struct TileWriter {
             /* every earlier store has read its buffer */
             asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
             for (int k = 0; k < fTotal; k++)
-                FetchBox(p, k, (boxes + (uint32_t)k) & 1u);
+                FetchBox(p, k, (boxes + (uint32_t)k) & (uint32_t)(NBOX - 1));
         }
     }
 
@@ -406,7 +408,7 @@ struct TileWriter {
             return;
         }
         const int colInBox = c0 % BOX_COLS;
-        const uint32_t bufIdx = boxes & 1u;
+        const uint32_t bufIdx = boxes & (uint32_t)(NBOX - 1);
         const uint32_t box = stage + bufIdx * EPI_BOX_BYTES;
         const bool live = row0 < p.M;             /* uniform across the warp */
         if (colInBox == 0) {
@@ -421,9 +423,13 @@ struct TileWriter {
                 }
             }
             else {
-                /* the store that used this box two boxes ago must have read it */
-                if (lane == 0 && boxes >= 2)
-                    asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                /* the store that last used this box (NBOX boxes ago) must have read it */
+                if (lane == 0 && boxes >= (uint32_t)NBOX) {
+                    if (NBOX == 2)
+                        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                    else
+                        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                }
                 __syncwarp();
             }
         }

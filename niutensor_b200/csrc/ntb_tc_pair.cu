@@ -29,8 +29,8 @@ namespace {
  * tcgen05.commit; tempty[buf] lives in the leader and collects the eight epilogue warps
  * of the pair. All waits are local and bounded as in the single-CTA kernel.
  */
-template <int MSUB, int BN, int STAGES, int G, typename OutT, bool OLDC>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+template <int MSUB, int BN, int STAGES, int G, int EPIW, typename OutT, bool OLDC>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + 32 * EPIW, 1)
 GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, TcParams p)
 {
@@ -46,13 +46,22 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     constexpr int TMEM_COLS = 512;
     constexpr int KSTEPS = ROW_BYTES / UMMA_K_BYTES;
     static_assert(MSUB == 1 || MSUB == 2, "one or two A sub-tiles per CTA");
+    /* EPIW epilogue warps: 4, or 8 -- two per TMEM sub-partition, each taking half of the
+       tile's 64-column chunks, which halves the time the accumulators of a tile that fills
+       tensor memory (no second set to overlap with) stay occupied after its last MMA. Eight
+       warps share the staging space of four: one box each instead of two. */
+    static_assert(EPIW == 4 || EPIW == 8, "epilogue warps");
+    constexpr int NBOX = EPIW == 4 ? 2 : 1;
+    constexpr int CH_PER_SUB = BN / 64;
+    constexpr int CH_PER_WARP = MSUB * CH_PER_SUB / (EPIW / 4);
+    static_assert(CH_PER_WARP >= 1, "chunks per epilogue warp");
 
     extern __shared__ uint8_t smemRaw[];
     __shared__ __align__(8) uint64_t barFull[STAGES];
     __shared__ __align__(8) uint64_t barEmpty[STAGES];
     __shared__ __align__(8) uint64_t barTFull[2];
     __shared__ __align__(8) uint64_t barTEmpty[2];
-    __shared__ __align__(8) uint64_t barOldC[8];    /* per epilogue warp and staging box: old C values have landed */
+    __shared__ __align__(8) uint64_t barOldC[2 * EPIW];    /* per epilogue warp and staging box: old C values have landed */
     __shared__ uint32_t tmemBaseSlot;
     __shared__ int abortFlag;
 
@@ -87,9 +96,9 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         else if (lane >= 8 && lane < 10) {
             MbarInit(SmemAddr(&barTFull[lane - 8]), 1);
-            MbarInit(SmemAddr(&barTEmpty[lane - 8]), 8);
+            MbarInit(SmemAddr(&barTEmpty[lane - 8]), 2 * EPIW);
         }
-        else if (OLDC && lane >= 16 && lane < 24) {
+        else if (OLDC && lane >= 16 && lane < 16 + 2 * EPIW) {
             MbarInit(SmemAddr(&barOldC[lane - 16]), 1);
         }
         if (lane == 0)
@@ -246,11 +255,13 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
     }
     else {
-        const int sub32 = warp & 3;
+        const int sub32 = warp & 3;               /* TMEM sub-partition (lanes 32 * sub32 ..) this warp may read */
+        const int ew = warp - 2;                  /* 0 .. EPIW-1 */
+        const int chBeg = (ew >> 2) * CH_PER_WARP;    /* first of this warp's chunks, counted sub-tile by sub-tile */
         uint32_t it = 0;
         bool ok = true;
-        TileWriter<OutT, OLDC> writer;
-        writer.Init(smemBase + STAGES * STAGE_BYTES, sub32, &tmC, &barOldC[sub32 * 2], abortPtr, p.status);
+        TileWriter<OutT, OLDC, NBOX> writer;
+        writer.Init(smemBase + STAGES * STAGE_BYTES, ew, &tmC, &barOldC[ew * 2], abortPtr, p.status);
         for (int t = firstTile; ok && t < p.totalTiles; t += tileStep, ++it) {
             TileCoord tc = DecodeTile(t, p);
             const int n0 = tc.nBlk * BN;
@@ -259,39 +270,49 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const int bc = BatchCoord(p.cSel, tc.prob, p);
             OutT * cBase = (OutT *)p.c + pp * p.sCp + qq * p.sCq;
             const uint32_t buf = it % NBUF;
-            writer.BeginTile(p, cBase + (long long)(tc.mBlk * PM + (int)rank * BM + sub32 * 32 + lane) * p.ldc + n0,
-                             tc.mBlk * PM + (int)rank * BM + sub32 * 32, 2 * BM, MSUB, n0, BN, bc, lane);
+            const int tileRow0 = tc.mBlk * PM + (int)rank * BM + sub32 * 32;   /* this warp's rows of sub-tile 0 */
             {
-                const int r0 = tc.mBlk * PM + (int)rank * BM + sub32 * 32 + lane;
-                writer.OldRequest(p, cBase + (long long)r0 * p.ldc, n0, r0 < p.M);
+                /* this warp's part of the tile: sub-tiles firstSub .. lastSub, columns from colBeg */
+                const int firstSub = chBeg / CH_PER_SUB, lastSub = (chBeg + CH_PER_WARP - 1) / CH_PER_SUB;
+                const int colBeg = n0 + (chBeg % CH_PER_SUB) * 64;
+                const int cols = CH_PER_WARP >= CH_PER_SUB ? BN : CH_PER_WARP * 64;
+                const int r0 = tileRow0 + firstSub * 2 * BM;
+                writer.BeginTile(p, cBase + (long long)(r0 + lane) * p.ldc + colBeg, r0, 2 * BM, lastSub - firstSub + 1,
+                                 colBeg, cols, bc, lane);
+                writer.OldRequest(p, cBase + (long long)(r0 + lane) * p.ldc, colBeg, r0 + lane < p.M);
             }
             NTB_TIMED(3, ok = MbarWaitWarp(SmemAddr(&barTFull[buf]), (it / NBUF) & 1u, abortPtr, p.status, (uint32_t)p.epiHint));
             if (!ok)
                 break;
             TcFenceAfter();
 #pragma unroll 1
-            for (int sub = 0; sub < MSUB; sub++) {
-                const int row0 = tc.mBlk * PM + sub * 2 * BM + (int)rank * BM + sub32 * 32;
+            for (int i = 0; i < CH_PER_WARP; i++) {
+                const int idx = chBeg + i;
+                const int sub = idx / CH_PER_SUB, ch = idx % CH_PER_SUB;
+                const int row0 = tileRow0 + sub * 2 * BM;
                 const int row = row0 + lane;
                 OutT * cRow = cBase + (long long)row * p.ldc;
                 const bool rowOk = row < p.M;
-                const uint32_t tRow = tmemBase + ((uint32_t)(sub32 * 32) << 16) + buf * (MSUB * BN) + sub * BN;
-#pragma unroll 1
-                for (int ch = 0; ch < BN / 64; ch++) {
-                    const int c0 = n0 + ch * 64;
-                    if (c0 >= p.N)
-                        break;
-                    writer.OldAdvance();
-                    if (ch + 1 < BN / 64 && c0 + 64 < p.N)
-                        writer.OldRequest(p, cRow, c0 + 64, rowOk);
-                    else if (sub + 1 < MSUB)
+                const int c0 = n0 + ch * 64;
+                if (c0 >= p.N)
+                    continue;                      /* uniform across the warp */
+                writer.OldAdvance();
+                if (i + 1 < CH_PER_WARP) {
+                    /* old values of the chunk after this one: further right, or the next sub-tile's first */
+                    if (ch + 1 < CH_PER_SUB) {
+                        if (c0 + 64 < p.N)
+                            writer.OldRequest(p, cRow, c0 + 64, rowOk);
+                    }
+                    else {
                         writer.OldRequest(p, cRow + (long long)(2 * BM) * p.ldc, n0, row + 2 * BM < p.M);
-                    float v[64];
-                    TmemLoad64(tRow + ch * 64, v);
-                    writer.Put32(p, cRow, rowOk, row0, c0, bc, v, lane);
-                    if (c0 + 32 < p.N)
-                        writer.Put32(p, cRow, rowOk, row0, c0 + 32, bc, v + 32, lane);
+                    }
                 }
+                const uint32_t tRow = tmemBase + ((uint32_t)(sub32 * 32) << 16) + buf * (MSUB * BN) + sub * BN;
+                float v[64];
+                TmemLoad64(tRow + ch * 64, v);
+                writer.Put32(p, cRow, rowOk, row0, c0, bc, v, lane);
+                if (c0 + 32 < p.N)
+                    writer.Put32(p, cRow, rowOk, row0, c0 + 32, bc, v + 32, lane);
             }
             TcFenceBefore();
             __syncwarp();
@@ -323,33 +344,36 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
 }
 
-template <int MSUB, int BN, int STAGES, int G, typename OutT, bool OLDC>
+template <int MSUB, int BN, int STAGES, int G, int EPIW, typename OutT, bool OLDC>
 int LaunchPair(const CUtensorMap & tmA, const CUtensorMap & tmB, const CUtensorMap & tmC, const TcParams & tp, int pairs,
                cudaStream_t stream)
 {
     constexpr int smem = (MSUB * A_TILE_BYTES + (BN / 2) * ROW_BYTES) * STAGES + EPI_BYTES + 1024;
-    auto kern = GemmTcPairKernel<MSUB, BN, STAGES, G, OutT, OLDC>;
+    auto kern = GemmTcPairKernel<MSUB, BN, STAGES, G, EPIW, OutT, OLDC>;
     static SmemOptIn optIn;
     if (!optIn.Ensure((const void *)kern, smem))
         return NTB_ERR_CUDA;
-    const cudaError_t err = LaunchPdl(kern, 2 * pairs, 192, smem, stream, tmA, tmB, tmC, tp);
+    const cudaError_t err = LaunchPdl(kern, 2 * pairs, 64 + 32 * EPIW, smem, stream, tmA, tmB, tmC, tp);
     CountLaunch();
     return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? NTB_OK : NTB_ERR_CUDA;
 }
 
 }
 
-int LaunchPairKernel(int msub, int bn, int g, bool half, bool oldc, const CUtensorMap * maps, const TcParams & tp,
+int LaunchPairKernel(int msub, int bn, int g, int epiWarps, bool half, bool oldc, const CUtensorMap * maps, const TcParams & tp,
                      int pairs, cudaStream_t stream)
 {
-#define NTB_PAIR2(MS, W, ST, GG, T) (oldc ? LaunchPair<MS, W, ST, GG, T, true>(maps[0], maps[1], maps[2], tp, pairs, stream) \
-                                          : LaunchPair<MS, W, ST, GG, T, false>(maps[0], maps[1], maps[2], tp, pairs, stream))
-#define NTB_PAIR(MS, W, ST, GG) (half ? NTB_PAIR2(MS, W, ST, GG, __half) : NTB_PAIR2(MS, W, ST, GG, float))
-    if (bn == 256)
-        return msub == 2 ? NTB_PAIR(2, 256, 4, 1) : NTB_PAIR(1, 256, 6, 1);
+#define NTB_PAIR2(MS, W, ST, GG, EW, T) (oldc ? LaunchPair<MS, W, ST, GG, EW, T, true>(maps[0], maps[1], maps[2], tp, pairs, stream) \
+                                              : LaunchPair<MS, W, ST, GG, EW, T, false>(maps[0], maps[1], maps[2], tp, pairs, stream))
+#define NTB_PAIR(MS, W, ST, GG, EW) (half ? NTB_PAIR2(MS, W, ST, GG, EW, __half) : NTB_PAIR2(MS, W, ST, GG, EW, float))
+    if (bn == 256) {
+        if (msub == 2)
+            return epiWarps == 4 ? NTB_PAIR(2, 256, 4, 1, 4) : NTB_PAIR(2, 256, 4, 1, 8);
+        return NTB_PAIR(1, 256, 6, 1, 4);
+    }
     if (msub == 2)
-        return NTB_PAIR(2, 128, 4, 2);
-    return g == 4 ? NTB_PAIR(1, 128, 8, 4) : NTB_PAIR(1, 128, 8, 2);
+        return NTB_PAIR(2, 128, 4, 2, 4);
+    return g == 4 ? NTB_PAIR(1, 128, 8, 4, 4) : NTB_PAIR(1, 128, 8, 2, 4);
 #undef NTB_PAIR2
 #undef NTB_PAIR
 }
