@@ -380,6 +380,10 @@ int ntb_debug_inject(int devID, int skipKBlock, int waitLimitKiloCycles);
 #define NTB_PLAN_PAIR_512X128  (-9)
 int ntb_plan(int dtypeAB, int M, int N, int K, int count, int smCount);
 
+/* Products issued so far in this process through the kernel family `route` (NTB_ROUTE_*): shows,
+   for a whole program, how many products alignment pushed off the tensor cores. */
+long long ntb_route_count(int route);
+
 /* Number of kernels this library has launched in the process so far. */
 long long ntb_launch_count(void);
 

@@ -48,6 +48,7 @@ PROTOTYPES = {
     "ntb_device_status": (_i, [_i]),
     "ntb_plan": (_i, [_i] * 6),
     "ntb_debug_inject": (_i, [_i, _i, _i]),
+    "ntb_route_count": (_ll, [_i]),
     "ntb_launch_count": (_ll, []),
     "ntb_release": (None, []),
     "ntb_strerror": (ctypes.c_char_p, [_i]),

@@ -20,6 +20,7 @@ DeviceCtx * gCtx[MAX_DEV] = { nullptr };
 std::atomic<long long> gLaunches(0);
 std::atomic<int> gForcedRoute(0);
 std::atomic<int> gSkipKBlock(-1);
+std::atomic<long long> gRouteCount[8];
 thread_local int tLastRoute = NTB_ROUTE_NONE;
 
 /* save / restore the calling thread's current device around a call */
@@ -120,14 +121,14 @@ int Dispatch(int devID, cudaStream_t stream, Problem & p)
         int route = NTB_ROUTE_NONE;
         rc = LaunchTc(*ctx, p, stream, &route);
         if (rc == NTB_OK)
-            tLastRoute = route;
+            SetLastRoute(route);
     }
     else {
         if (forced == NTB_ROUTE_TC_F16 || forced == NTB_ROUTE_TC_3XTF32 || forced == NTB_ROUTE_TC_F16_PAIR)
             return NTB_ERR_ARG;
         rc = LaunchSimt(*ctx, p, stream);
         if (rc == NTB_OK)
-            tLastRoute = NTB_ROUTE_SIMT;
+            SetLastRoute(NTB_ROUTE_SIMT);
     }
     return rc;
 }
@@ -242,6 +243,8 @@ void CountLaunch()
 void SetLastRoute(int route)
 {
     tLastRoute = route;
+    if (route >= 0 && route < 8)
+        gRouteCount[route].fetch_add(1);
 }
 
 int InjectedSkipKBlock()
@@ -422,7 +425,7 @@ int ntb_gemm_grad(int devID, void * stream,
         if (TcTileChoice(*ctx, pa) > 0 && TcTileChoice(*ctx, pb) > 0) {
             rc = LaunchTcTwo(*ctx, pa, pb, st);
             if (rc == NTB_OK)
-                tLastRoute = dtype == NTB_X_FLOAT16 ? NTB_ROUTE_TC_F16 : NTB_ROUTE_TC_3XTF32;
+                SetLastRoute(dtype == NTB_X_FLOAT16 ? NTB_ROUTE_TC_F16 : NTB_ROUTE_TC_3XTF32);
             return rc;
         }
     }
@@ -756,6 +759,11 @@ int ntb_plan(int dtypeAB, int M, int N, int K, int count, int smCount)
     memset(&ctx, 0, sizeof(ctx));
     ctx.smCount = smCount;
     return TcTileChoice(ctx, p);
+}
+
+long long ntb_route_count(int route)
+{
+    return route >= 0 && route < 8 ? gRouteCount[route].load() : 0;
 }
 
 long long ntb_launch_count(void)
