@@ -20,7 +20,7 @@ LIB = os.path.join(HERE, "libntb_gemm.so")
 SOURCES = ["ntb_api.cu", "ntb_tc.cu", "ntb_tc_pair.cu", "ntb_tc_split.cu", "ntb_tc_f32pair.cu", "ntb_tc_ldg.cu",
            "ntb_simt.cu", "ntb_noalloc.cu", "ntb_attn.cu", "ntb_logsoftmax.cu", "ntb_sharded.cu", "ntb_grouped.cu"]
 HEADERS = [os.path.join(CSRC, "ntb_internal.h"), os.path.join(CSRC, "ntb_ptx.cuh"),
-           os.path.join(CSRC, "ntb_tc_common.cuh"),
+           os.path.join(CSRC, "ntb_tc_common.cuh"), os.path.join(CSRC, "ntb_tc_single.cuh"),
            os.path.join(os.path.dirname(HERE), "include", "ntb_gemm.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall", "-cudart", "static"]

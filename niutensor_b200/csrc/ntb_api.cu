@@ -114,12 +114,15 @@ int Dispatch(int devID, cudaStream_t stream, Problem & p)
         return NTB_ERR_CUDA;
     const int forced = ForcedRoute();
     const bool tc = forced != NTB_ROUTE_SIMT && TcEligible(p);
-    if (p.nPeers > 0 && !tc)
+    /* operands TMA cannot address still go to the tensor cores, through loader warps; the FFMA
+       kernel remains for K == 0 and for a forced NTB_ROUTE_SIMT */
+    const bool ldg = !tc && forced != NTB_ROUTE_SIMT && forced != NTB_ROUTE_TC_F16_PAIR && LdgEligible(p);
+    if (p.nPeers > 0 && !tc && !ldg)
         return NTB_ERR_ARG;                         /* only the tensor-core kernels store to peers */
     int rc;
-    if (tc) {
+    if (tc || ldg) {
         int route = NTB_ROUTE_NONE;
-        rc = LaunchTc(*ctx, p, stream, &route);
+        rc = tc ? LaunchTc(*ctx, p, stream, &route) : LaunchLdg(*ctx, p, stream, &route);
         if (rc == NTB_OK)
             SetLastRoute(route);
     }
@@ -207,6 +210,11 @@ int ScratchAcquire(const DeviceCtx & ctx, cudaStream_t stream)
     DeviceCtx * c = ctx.mayAllocate ? GetCtx(ctx.devID) : nullptr;
     if (!c)
         return NTB_ERR_CUDA;
+    /* inside a stream capture the graph orders its own nodes; work outside it is the caller's to order */
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone)
+        return NTB_OK;
+    cudaGetLastError();
     std::lock_guard<std::mutex> g(gLock);
     if (c->haveScratchEvent && cudaStreamWaitEvent(stream, c->scratchEvent, 0) != cudaSuccess) {
         cudaGetLastError();
@@ -220,6 +228,10 @@ int ScratchRelease(const DeviceCtx & ctx, cudaStream_t stream)
     DeviceCtx * c = ctx.mayAllocate ? GetCtx(ctx.devID) : nullptr;
     if (!c)
         return NTB_ERR_CUDA;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone)
+        return NTB_OK;
+    cudaGetLastError();
     std::lock_guard<std::mutex> g(gLock);
     if (!c->haveScratchEvent) {
         if (cudaEventCreateWithFlags(&c->scratchEvent, cudaEventDisableTiming) != cudaSuccess) {

@@ -68,6 +68,10 @@ bool TcEligible(const Problem & p);
 /* *route receives the NTB_ROUTE_* code of the kernel launched */
 int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int * route);
 int LaunchSimt(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream);
+/* tensor-core route for operands TMA cannot address (base or pitch not a multiple of 16 bytes):
+   loader warps fetch them with ordinary loads */
+bool LdgEligible(const Problem & p);
+int LaunchLdg(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int * route);
 /* NTB_PDL=0 in the environment turns programmatic stream serialisation off */
 inline bool PdlEnabled()
 {

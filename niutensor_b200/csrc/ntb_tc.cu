@@ -37,9 +37,10 @@
  * CTA's abort flag, records NTB_ERR_DEVICE_WAIT in the device status word, and every role
  * leaves its loop; the CTA then lets copies in flight land, frees its TMEM and returns.
  */
-#include "ntb_tc_common.cuh"
+#include "ntb_tc_single.cuh"
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <cmath>
 #include <atomic>
 #include <mutex>
@@ -47,487 +48,6 @@
 namespace ntb {
 
 namespace {
-
-/* ---------------------------------------------------------------- the kernel */
-
-/* Up to two problems of different shapes in one launch (the two gradient products of a
-   matrix multiplication): tiles [0, split) belong to problem 0, the rest to problem 1. */
-struct TcGroup {
-    CUtensorMap tm[2][3];      /* A, B, C maps of each problem */
-    TcParams p[2];
-    int n, split, total;
-};
-
-/* per-tile view of the problem a tile belongs to; names match the single-problem code */
-#define NTB_SELECT_PROBLEM() \
-    const int gi = t >= grp.split ? 1 : 0; \
-    const TcParams & p = grp.p[gi]; \
-    const CUtensorMap & tmA = grp.tm[gi][0]; \
-    const CUtensorMap & tmB = grp.tm[gi][1]; \
-    const CUtensorMap & tmC = grp.tm[gi][2]; \
-    (void)tmA; (void)tmB; (void)tmC; \
-    const int tl = t - gi * grp.split; \
-    const int kBlocks = (p.K + EPR - 1) / EPR; \
-    /* k-blocks accumulated in TMEM before the partial sum is handed to the epilogue */ \
-    const int chunkBlocks = MODE == 0 ? kBlocks : FP32_CHUNK_BLOCKS; \
-    (void)chunkBlocks
-
-template <int MODE, int BN, int STAGES, int G, typename OutT, bool OLDC>
-__global__ void __launch_bounds__(MODE == 0 ? 192 : 192 + CONV_THREADS, 1)
-GemmTcKernel(const __grid_constant__ TcGroup grp)
-{
-    /* G k-blocks share one full / empty barrier pair: the producer and the MMA thread each
-       pay for a barrier hand-shake (a few hundred clocks of their own time, most of it the
-       MMA thread's shared-memory probe waiting behind the tensor-core instructions it has
-       just issued) once per G k-blocks instead of once per k-block */
-    static_assert(STAGES % G == 0 && (MODE == 0 || G == 1), "k-blocks per hand-shake");
-    constexpr int NSTG = STAGES / G;                    /* barrier pairs in the ring */
-    constexpr int ES = MODE == 0 ? 2 : 4;               /* operand element size */
-    constexpr int EPR = ROW_BYTES / ES;                 /* elements per 128-byte row = K per stage */
-    constexpr int B_TILE_BYTES = BN * ROW_BYTES;
-    constexpr int PLANE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
-    constexpr int STAGE_BYTES = PLANE_BYTES * (MODE == 0 ? 1 : 2);   /* fp32: hi plane + lo plane */
-    /* two accumulators, plus (fp32 route) one running sum; a power of two */
-    constexpr int TMEM_NEED = (MODE == 0 ? 2 : 3) * BN;
-    constexpr int TMEM_COLS = TMEM_NEED <= 128 ? 128 : TMEM_NEED <= 256 ? 256 : 512;
-    constexpr int KSTEPS = ROW_BYTES / UMMA_K_BYTES;                 /* 4 */
-    static_assert(BN == 64 || BN == 128 || BN == 256, "tile width");
-    static_assert(STAGES <= 8, "barrier initialisation assigns lanes 0-7 to the stages");
-
-#ifdef NTB_WAIT_STATS
-    const long long kernelT0 = clock64();
-    __shared__ unsigned long long tlShared[64];
-    if (threadIdx.x < 64) tlShared[threadIdx.x] = 0;
-    __syncthreads();
-#endif
-    extern __shared__ uint8_t smemRaw[];
-    __shared__ __align__(8) uint64_t barFull[STAGES];
-    __shared__ __align__(8) uint64_t barEmpty[STAGES];
-    __shared__ __align__(8) uint64_t barConv[STAGES];
-    __shared__ __align__(8) uint64_t barTFull[2];
-    __shared__ __align__(8) uint64_t barTEmpty[2];
-    __shared__ __align__(8) uint64_t barOldC[8];    /* per epilogue warp and staging box: old C values have landed */
-    __shared__ uint32_t tmemBaseSlot;
-    __shared__ int abortFlag;
-
-    const int warp = threadIdx.x >> 5;
-    const int lane = threadIdx.x & 31;
-    const uint32_t smemBase = (SmemAddr(smemRaw) + 1023u) & ~1023u;
-    volatile int * abortPtr = &abortFlag;
-    /* a kernel launched behind this one with programmatic serialisation may start setting up */
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-
-    if (threadIdx.x == 128 || threadIdx.x == 160) {
-        /* Idle epilogue lanes pull the kernel parameters (and one of them the tensor maps)
-           towards the SM while the other warps set up. Warps 4 and 5 share their scheduler
-           partition, and with it the first-level constant cache, with the producer warp and
-           the MMA warp: a constant load that misses stalls its warp for the whole miss,
-           one line after the other, and the producer reads half a dozen lines before its
-           first copy. */
-        int touch = grp.total + grp.split;
-        for (int gi = 0; gi < grp.n; gi++) {
-            const TcParams & p = grp.p[gi];
-            if (threadIdx.x == 128) {
-                PrefetchTensorMap(&grp.tm[gi][0]);
-                PrefetchTensorMap(&grp.tm[gi][1]);
-                if (p.cTma)
-                    PrefetchTensorMap(&grp.tm[gi][2]);
-            }
-            const int * words = (const int *)&p;
-            for (int w = 0; w < (int)(sizeof(TcParams) / sizeof(int)); w += 8)
-                touch += words[w];
-        }
-        asm volatile("" :: "r"(touch));
-    }
-    if (warp == 0) {
-        /* one barrier per lane: thirty-odd initialisations one after the other cost the
-           producer, which goes first, several hundred clocks */
-        if (lane == 0) NTB_MARK(8);
-        if (lane < STAGES) {
-            MbarInit(SmemAddr(&barFull[lane]), 1);
-            MbarInit(SmemAddr(&barEmpty[lane]), 1);
-            MbarInit(SmemAddr(&barConv[lane]), CONV_THREADS);
-        }
-        else if (lane >= 8 && lane < 10) {
-            MbarInit(SmemAddr(&barTFull[lane - 8]), 1);
-            MbarInit(SmemAddr(&barTEmpty[lane - 8]), 4);
-        }
-        else if (OLDC && lane >= 16 && lane < 24) {
-            MbarInit(SmemAddr(&barOldC[lane - 16]), 1);
-        }
-        if (lane == 0)
-            abortFlag = 0;
-        if (lane == 0) NTB_MARK(9);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        if (lane == 0) NTB_MARK(10);
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     :: "r"(SmemAddr(&tmemBaseSlot)), "r"((uint32_t)TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-        if (lane == 0) NTB_MARK(11);
-    }
-    /* The producer warp initialised the barriers itself and needs no TMEM: it signals the
-       CTA-wide barrier without waiting and starts loading, so the TMEM allocation and the
-       hand-shake overlap the first copies. Everybody else waits for both. */
-    uint32_t tmemBase = 0;
-    if (warp == 0) {
-        __syncwarp();
-        asm volatile("bar.arrive 1, %0;" :: "r"((uint32_t)blockDim.x) : "memory");
-    }
-    else {
-        TcFenceBefore();
-        asm volatile("bar.sync 1, %0;" :: "r"((uint32_t)blockDim.x) : "memory");
-        TcFenceAfter();
-        tmemBase = *(volatile uint32_t *)&tmemBaseSlot;
-    }
-
-#ifdef NTB_WAIT_STATS
-    long long wstat[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#endif
-    if (threadIdx.x == 0) NTB_MARK(0);
-    /* set-up is done; nothing before this point touched global memory. A kernel launched
-       with programmatic serialisation waits here for the kernels before it in the stream. */
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int firstTile = blockIdx.x;
-    const int tileStep = gridDim.x;
-
-    if (warp == 0) {
-        /* ------------------------------------------------------------ TMA producer */
-        if (lane == 0) {
-            int s = 0;
-            uint32_t ph = 0;
-            bool ok = true;
-            for (int t = firstTile; ok && t < grp.total; t += tileStep) {
-                NTB_SELECT_PROBLEM();
-                TileCoord tc = DecodeTile(tl, p);
-                const int m0 = tc.mBlk * BM, n0 = tc.nBlk * BN;
-                const int ba = BatchCoord(p.aSel, tc.prob, p);
-                const int bb = BatchCoord(p.bSel, tc.prob, p);
-                NTB_MARK(12);
-                /* everything the k-loop needs, in registers: the loop itself touches no
-                   kernel parameter */
-                const bool aMN = p.aMN != 0, bMN = p.bMN != 0;
-                const int pfDist = p.pfDist, nkb = kBlocks;
-                const int skipKb = t == firstTile ? p.skipKBlock : -1;    /* test hook, -1 in normal use */
-                int * const status = p.status;
-                const CUtensorMap * const mapA = &tmA;
-                const CUtensorMap * const mapB = &tmB;
-#ifdef NTB_WAIT_STATS
-                const long long loopT0 = clock64();
-#endif
-                for (int kb = 0; kb < nkb; kb += G) {
-                    NTB_TIMED(0, ok = MbarWait(SmemAddr(&barEmpty[s]), ph ^ 1u, abortPtr, status));
-                    NTB_MARK(13);
-                    if (!ok)
-                        break;
-                    const uint32_t full = SmemAddr(&barFull[s]);
-                    const int nb = G == 1 ? 1 : (nkb - kb < G ? nkb - kb : G);
-                    NTB_TIMED(6, MbarExpectTx(full, (uint32_t)nb * PLANE_BYTES));
-                    NTB_MARK(14);
-#pragma unroll
-                    for (int j = 0; j < G; j++) {
-                        if (j < nb && kb + j != skipKb) {
-                            const uint32_t aDst = smemBase + (uint32_t)(s * G + j) * STAGE_BYTES;
-                            const uint32_t bDst = aDst + A_TILE_BYTES;
-                            const int k0 = (kb + j) * EPR;
-                            if (!aMN) {
-                                NTB_TIMED(7, TmaLoad3D(aDst, mapA, full, k0, m0, ba));
-                            }
-                            else {
-#pragma unroll
-                                for (int i = 0; i < BM / EPR; i++)
-                                    TmaLoad3D(aDst + i * EPR * ROW_BYTES, mapA, full, m0 + i * EPR, k0, ba);
-                            }
-                            if (!bMN) {
-                                NTB_TIMED(5, TmaLoad3D(bDst, mapB, full, k0, n0, bb));
-                            }
-                            else {
-#pragma unroll
-                                for (int i = 0; i < BN / EPR; i++)
-                                    TmaLoad3D(bDst + i * EPR * ROW_BYTES, mapB, full, n0 + i * EPR, k0, bb);
-                            }
-                            if (pfDist > 0 && kb + j + pfDist < nkb) {
-                                const int kp = k0 + pfDist * EPR;
-                                if (!aMN) {
-                                    TmaPrefetch3D(mapA, kp, m0, ba);
-                                }
-                                else {
-#pragma unroll
-                                    for (int i = 0; i < BM / EPR; i++)
-                                        TmaPrefetch3D(mapA, m0 + i * EPR, kp, ba);
-                                }
-                                if (!bMN) {
-                                    TmaPrefetch3D(mapB, kp, n0, bb);
-                                }
-                                else {
-#pragma unroll
-                                    for (int i = 0; i < BN / EPR; i++)
-                                        TmaPrefetch3D(mapB, n0 + i * EPR, kp, bb);
-                                }
-                            }
-                        }
-                    }
-                    NTB_MARK(1);
-                    NTB_MARKK(0, kb);
-                    if (++s == NSTG) { s = 0; ph ^= 1u; }
-                }
-#ifdef NTB_WAIT_STATS
-                wstat[3] += clock64() - loopT0;
-#endif
-            }
-        }
-    }
-    else if (warp == 1) {
-        /* ------------------------------------------------------------ MMA issuer */
-        if (lane == 0) {
-            int s = 0;
-            uint32_t ph = 0;
-            uint32_t stageOff = 0;                /* s * STAGE_BYTES in 16-byte units */
-            uint32_t it = 0;                      /* accumulator hand-overs so far */
-            bool ok = true;
-            const uint32_t barFull0 = SmemAddr(MODE == 0 ? &barFull[0] : &barConv[0]);
-            const uint32_t barEmpty0 = SmemAddr(&barEmpty[0]);
-            for (int t = firstTile; ok && t < grp.total; t += tileStep) {
-                NTB_SELECT_PROBLEM();
-                (void)tl;
-                const uint32_t iDesc = InstrDesc(MODE, p.aMN, p.bMN, BN);
-                /* K-major: rows of 128 B, 8-row groups 1024 B apart, k-step = 32 B along the row.
-                   MN-major: boxes of EPR k-rows x 128 B; 64- (or 32-) element MN chunks are
-                   EPR*128 B apart (leading offset), 8-k-row groups 1024 B apart (stride offset),
-                   k-step = UMMA_K k-rows. */
-                const uint32_t aLbo = p.aMN ? EPR * ROW_BYTES : 16, bLbo = p.bMN ? EPR * ROW_BYTES : 16;
-                const uint32_t mnStep = (UMMA_K_BYTES / ES) * ROW_BYTES;
-                const uint32_t aStep = p.aMN ? mnStep : UMMA_K_BYTES;
-                const uint32_t bStep = p.bMN ? mnStep : UMMA_K_BYTES;
-                /* MN-major fp32 tiles are loaded with the 32-byte-chunk swizzle, whose pattern
-                   repeats every 4 k-rows (512 B) instead of every 8 */
-                const uint32_t aLay = (MODE != 0 && p.aMN) ? 1u : 2u, bLay = (MODE != 0 && p.bMN) ? 1u : 2u;
-                const uint32_t aSbo = (MODE != 0 && p.aMN) ? 512u : 1024u, bSbo = (MODE != 0 && p.bMN) ? 512u : 1024u;
-                int * const status = p.status;
-                const int nkb = kBlocks, chunk = chunkBlocks;
-                /* descriptors of stage 0, k-step 0; inside the loop only their start-address
-                   field (bits 0-13 of the low word, in 16-byte units) moves */
-                const uint64_t aD0 = SmemDesc(smemBase, aLbo, aSbo, aLay);
-                const uint64_t bD0 = SmemDesc(smemBase + A_TILE_BYTES, bLbo, bSbo, bLay);
-                const uint32_t aLo0 = (uint32_t)aD0, aHiW = (uint32_t)(aD0 >> 32);
-                const uint32_t bLo0 = (uint32_t)bD0, bHiW = (uint32_t)(bD0 >> 32);
-                const uint32_t aStep4 = aStep >> 4, bStep4 = bStep >> 4;
-                for (int kb0 = 0; ok && kb0 < nkb; kb0 += chunk, ++it) {
-                    const uint32_t buf = it & 1u;
-                    NTB_TIMED(2, ok = MbarWait(SmemAddr(&barTEmpty[buf]), ((it >> 1) & 1u) ^ 1u, abortPtr, status));
-                    if (!ok)
-                        break;
-                    TcFenceAfter();
-                    const uint32_t dTmem = tmemBase + buf * BN;
-                    const int kbEnd = min(nkb, kb0 + chunk);
-                    uint32_t acc = 0u;                /* the first instruction of a chain overwrites */
-                    for (int kb = kb0; kb < kbEnd; kb += G) {
-                        NTB_TIMED(1, ok = MbarWait(barFull0 + (uint32_t)s * 8u, ph, abortPtr, status));
-                        if (!ok)
-                            break;
-                        NTB_MARK(2);
-                        NTB_MARKK(1, kb);
-                        TcFenceAfter();
-                        const int nb = G == 1 ? 1 : (kbEnd - kb < G ? kbEnd - kb : G);
-#pragma unroll
-                        for (int j = 0; j < G; j++) {
-                            if (j < nb) {
-                                uint32_t aLo = aLo0 + stageOff + (uint32_t)j * (STAGE_BYTES >> 4);
-                                uint32_t bLo = bLo0 + stageOff + (uint32_t)j * (STAGE_BYTES >> 4);
-#pragma unroll
-                                for (int k = 0; k < KSTEPS; k++) {
-                                    if (MODE == 0) {
-                                        TcMmaLH<MODE>(dTmem, aLo, aHiW, bLo, bHiW, iDesc, acc);
-                                    }
-                                    else {
-                                        constexpr uint32_t PLANE4 = PLANE_BYTES >> 4;
-                                        TcMmaLH<MODE>(dTmem, aLo + PLANE4, aHiW, bLo, bHiW, iDesc, acc);
-                                        TcMmaLH<MODE>(dTmem, aLo, aHiW, bLo + PLANE4, bHiW, iDesc, 1u);
-                                        TcMmaLH<MODE>(dTmem, aLo, aHiW, bLo, bHiW, iDesc, 1u);
-                                    }
-                                    acc = 1u;
-                                    aLo += aStep4;
-                                    bLo += bStep4;
-                                }
-                            }
-                        }
-                        TcCommit(barEmpty0 + (uint32_t)s * 8u);
-                        NTB_MARKK(2, kb);
-                        stageOff += (uint32_t)G * (STAGE_BYTES >> 4);
-                        if (++s == NSTG) { s = 0; ph ^= 1u; stageOff = 0; }
-                    }
-                    if (ok)
-                        TcCommit(SmemAddr(&barTFull[buf]));
-                    NTB_MARK(3);
-                }
-            }
-        }
-    }
-    else if (warp < 6) {
-        /* ------------------------------------------------------------ epilogue */
-        const int sub = warp & 3;                 /* TMEM sub-partition this warp may read */
-        uint32_t it = 0;
-        bool ok = true;
-        TileWriter<OutT, OLDC> writer;
-        writer.Init(smemBase + STAGES * STAGE_BYTES, sub, nullptr, &barOldC[sub * 2], abortPtr, nullptr);
-        for (int t = firstTile; ok && t < grp.total; t += tileStep) {
-            NTB_SELECT_PROBLEM();
-            writer.map = &tmC;
-            writer.status = p.status;
-            TileCoord tc = DecodeTile(tl, p);
-            const int row0 = tc.mBlk * BM + sub * 32;
-            const int row = row0 + lane;
-            const int n0 = tc.nBlk * BN;
-            int pp, qq;
-            SplitProb(p, tc.prob, pp, qq);
-            const int bc = BatchCoord(p.cSel, tc.prob, p);
-            OutT * cRow = (OutT *)p.c + pp * p.sCp + qq * p.sCq + (long long)row * p.ldc;
-            const bool rowOk = row < p.M;
-            writer.BeginTile(p, cRow + n0, row0, 0, 1, n0, BN, bc, lane);
-            if (MODE == 0) {
-                writer.OldRequest(p, cRow, n0, rowOk);
-                /* one accumulator hand-over per tile: load 32 columns, scale, store */
-                const uint32_t buf = it & 1u;
-                ok = MbarWaitWarp(SmemAddr(&barTFull[buf]), (it >> 1) & 1u, abortPtr, p.status, (uint32_t)p.epiHint);
-                if (!ok)
-                    break;
-                if (warp == 2 && lane == 0) NTB_MARK(4);
-                TcFenceAfter();
-                const uint32_t tRow = tmemBase + ((uint32_t)(sub * 32) << 16) + buf * BN;
-#pragma unroll 1
-                for (int ch = 0; ch < BN / 64; ch++) {
-                    const int c0 = n0 + ch * 64;
-                    if (c0 >= p.N)
-                        break;                     /* uniform across the warp */
-                    writer.OldAdvance();
-                    if (ch + 1 < BN / 64 && c0 + 64 < p.N)
-                        writer.OldRequest(p, cRow, c0 + 64, rowOk);
-                    float v[64];
-                    TmemLoad64(tRow + ch * 64, v);
-                    writer.Put32(p, cRow, rowOk, row0, c0, bc, v, lane);
-                    if (c0 + 32 < p.N)
-                        writer.Put32(p, cRow, rowOk, row0, c0 + 32, bc, v + 32, lane);
-                }
-                TcFenceBefore();
-                __syncwarp();
-                if (lane == 0)
-                    MbarArrive(SmemAddr(&barTEmpty[buf]));
-                ++it;
-            }
-            else {
-                /* fp32 inputs: the tensor core truncates its fp32 accumulator after every
-                   instruction, an error that grows with the length of the accumulation
-                   chain. K is therefore cut into chunks of chunkBlocks k-blocks; each
-                   chunk's partial sum is handed over here and added, with round-to-nearest
-                   FADDs, to a running sum kept in a third TMEM region (the sum of a
-                   128-column row does not fit the registers a ten-warp CTA leaves a thread). */
-                const uint32_t tRun = tmemBase + ((uint32_t)(sub * 32) << 16) + 2 * BN;   /* running sum */
-                for (int kb0 = 0; ok && kb0 < kBlocks; kb0 += chunkBlocks, ++it) {
-                    const uint32_t buf = it & 1u;
-                    ok = MbarWaitWarp(SmemAddr(&barTFull[buf]), (it >> 1) & 1u, abortPtr, p.status, (uint32_t)p.epiHint);
-                    if (!ok)
-                        break;
-                    TcFenceAfter();
-                    const uint32_t tRow = tmemBase + ((uint32_t)(sub * 32) << 16) + buf * BN;
-                    const bool first = kb0 == 0, last = kb0 + chunkBlocks >= kBlocks;
-#pragma unroll 1
-                    for (int ch = 0; ch < BN / 32; ch++) {
-                        float v[32];
-                        TmemLoad32(tRow + ch * 32, v);
-                        if (!first) {
-                            float r[32];
-                            TmemLoad32(tRun + ch * 32, r);
-#pragma unroll
-                            for (int e = 0; e < 32; e++)
-                                v[e] += r[e];
-                        }
-                        if (!last) {
-                            TmemStore32(tRun + ch * 32, v);
-                        }
-                        else {
-                            const int c0 = n0 + ch * 32;
-                            if (c0 < p.N)
-                                writer.Put32(p, cRow, rowOk, row0, c0, bc, v, lane);
-                        }
-                    }
-                    TcFenceBefore();
-                    __syncwarp();
-                    if (lane == 0)
-                        MbarArrive(SmemAddr(&barTEmpty[buf]));
-                }
-            }
-        }
-        if (warp == 2 && lane == 0) NTB_MARK(5);
-        writer.Finish(lane);
-        if (warp == 2 && lane == 0) NTB_MARK(6);
-    }
-    else if (MODE != 0) {
-        /* ------------------------------------------------------------ fp32 hi/lo split */
-        const int ct = threadIdx.x - 192;         /* 0 .. CONV_THREADS-1 */
-        int s = 0;
-        uint32_t ph = 0;
-        bool ok = true;
-        for (int t = firstTile; ok && t < grp.total; t += tileStep) {
-            NTB_SELECT_PROBLEM();
-            (void)tl;
-            for (int kb = 0; kb < kBlocks; kb++) {
-                ok = MbarWait(SmemAddr(&barFull[s]), ph, abortPtr, p.status);
-                if (!ok)
-                    break;
-                uint8_t * hi = smemRaw + (smemBase - SmemAddr(smemRaw)) + s * STAGE_BYTES;
-                uint8_t * lo = hi + PLANE_BYTES;
-#pragma unroll 4
-                for (int i = ct; i < PLANE_BYTES / 16; i += CONV_THREADS) {
-                    /* The tensor core reads an fp32 word as tf32 by ignoring its 13 low mantissa
-                       bits, so the loaded plane already is the hi operand (hi = x truncated);
-                       only lo = x - hi, exact in fp32, has to be written. Rounding hi to
-                       nearest instead halves |lo| but costs a second 32 KB store per stage on
-                       a path bound by shared-memory traffic: 168 -> 188 TFLOP/s at 8192^3 for
-                       a relative error of 2.2e-6 instead of 1.8e-6 (budget 1e-5). */
-                    const float4 x = *(const float4 *)(hi + i * 16);
-                    float4 l;
-                    l.x = x.x - __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u);
-                    l.y = x.y - __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u);
-                    l.z = x.z - __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u);
-                    l.w = x.w - __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u);
-                    *(float4 *)(lo + i * 16) = l;
-                }
-                /* make the generic-proxy stores visible to the tensor core's async-proxy reads */
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                MbarArrive(SmemAddr(&barConv[s]));
-                if (++s == STAGES) { s = 0; ph ^= 1u; }
-            }
-        }
-    }
-
-    /* ---------------------------------------------------------------- teardown */
-#ifdef NTB_WAIT_STATS
-    if (lane == 0 && warp <= 1) {
-        if (warp == 0) { atomicAdd(&gWaitStats[0], (unsigned long long)wstat[0]); atomicAdd(&gWaitStats[5], 1ULL); atomicAdd(&gWaitStats[6], (unsigned long long)wstat[6]); atomicAdd(&gWaitStats[7], (unsigned long long)wstat[7]); atomicAdd(&gWaitStats[3], (unsigned long long)wstat[3]); atomicAdd(&gWaitStats[2], (unsigned long long)wstat[5]);
-                         if (blockIdx.x == 0) atomicAdd(&gWaitStats[4], (unsigned long long)(clock64() - kernelT0)); }
-        if (warp == 1) { atomicAdd(&gWaitStats[1], (unsigned long long)wstat[1]); }
-    }
-#endif
-    __syncwarp();
-    if (*abortPtr) {
-        /* give copies and MMAs in flight time to land before shared memory and TMEM go away */
-        const long long t0 = clock64();
-        while (clock64() - t0 < 2000000LL) { }
-    }
-    TcFenceBefore();
-    __syncthreads();
-    TcFenceAfter();
-    if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
-                     :: "r"(tmemBase), "r"((uint32_t)TMEM_COLS) : "memory");
-    }
-#ifdef NTB_WAIT_STATS
-    if (threadIdx.x == 32) NTB_MARK(7);
-    __syncthreads();
-    if (blockIdx.x == 0 && threadIdx.x < 64) gTimeline[threadIdx.x] = tlShared[threadIdx.x];
-#endif
-}
 
 /* ---------------------------------------------------------------- host side */
 
@@ -560,23 +80,6 @@ const TuneKnobs & Tune()
                                  Knob("NTB_TMA_STORE", 1), Knob("NTB_DEBUG_CHOICE", 0) };
     return k;
 }
-
-template <int MODE, int BN, int STAGES, int G, typename OutT, bool OLDC>
-int LaunchOne(const TcGroup & grp, int smCount, cudaStream_t stream)
-{
-    constexpr int stage = (A_TILE_BYTES + BN * ROW_BYTES) * (MODE == 0 ? 1 : 2);
-    constexpr int smem = stage * STAGES + EPI_BYTES + 1024;
-    auto kern = GemmTcKernel<MODE, BN, STAGES, G, OutT, OLDC>;
-    static SmemOptIn optIn;
-    if (!optIn.Ensure((const void *)kern, smem))
-        return NTB_ERR_CUDA;
-    const int grid = grp.total < smCount ? grp.total : smCount;
-    const cudaError_t err = LaunchPdl(kern, grid, MODE == 0 ? 192 : 192 + CONV_THREADS, smem, stream, grp);
-    CountLaunch();
-    return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? NTB_OK : NTB_ERR_CUDA;
-}
-
-
 
 /* single-CTA kernel for a group, chosen by operand mode, tile width and output type */
 int LaunchGroup(const TcGroup & grp, int mode, int bn, int dtC, int smCount, cudaStream_t stream)
@@ -802,7 +305,7 @@ namespace {
 /* kernel parameters and tensor maps of one problem for tile width bn (pair: CTA-pair
    kernel with msub 128-row sub-tiles per CTA) */
 int Prepare(const DeviceCtx & ctx, const Problem & p, int mode, int bn, bool pair, int msub,
-            TcParams & tp, CUtensorMap * maps)
+            TcParams & tp, CUtensorMap * maps, bool ldg = false)
 {
     const int P = p.count / p.Q;
     tp.c = p.c; tp.ldc = p.ldc; tp.sCp = p.sCp; tp.sCq = p.sCq;
@@ -842,12 +345,23 @@ int Prepare(const DeviceCtx & ctx, const Problem & p, int mode, int bn, bool pai
     BatchSelector(p.sAp, p.sAq, P, p.Q, &tp.aSel, &stA, &extA);
     BatchSelector(p.sBp, p.sBq, P, p.Q, &tp.bSel, &stB, &extB);
 
-    int rc = EncodeOperand(&maps[0], mode, p.a, p.aMN, p.aRows, p.aCols, p.lda, stA, extA, BM);
-    if (rc != NTB_OK)
-        return rc;
-    rc = EncodeOperand(&maps[1], mode, p.b, p.bMN, p.bRows, p.bCols, p.ldb, stB, extB, pair ? bn / 2 : bn);
-    if (rc != NTB_OK)
-        return rc;
+    tp.a = p.a; tp.b = p.b;
+    tp.lda = p.lda; tp.ldb = p.ldb;
+    tp.sAp = p.sAp; tp.sAq = p.sAq; tp.sBp = p.sBp; tp.sBq = p.sBq;
+    int rc = NTB_OK;
+    if (ldg) {
+        /* loader warps address the operands themselves; no tensor maps */
+        memset(&maps[0], 0, sizeof(CUtensorMap));
+        memset(&maps[1], 0, sizeof(CUtensorMap));
+    }
+    else {
+        rc = EncodeOperand(&maps[0], mode, p.a, p.aMN, p.aRows, p.aCols, p.lda, stA, extA, BM);
+        if (rc != NTB_OK)
+            return rc;
+        rc = EncodeOperand(&maps[1], mode, p.b, p.bMN, p.bRows, p.bCols, p.ldb, stB, extB, pair ? bn / 2 : bn);
+        if (rc != NTB_OK)
+            return rc;
+    }
 
     /* C through TMA stores when its base, pitch and batch strides are 16-byte aligned and
        its batch offset is one index times one stride; otherwise direct stores */
@@ -865,6 +379,50 @@ int Prepare(const DeviceCtx & ctx, const Problem & p, int mode, int bn, bool pai
     return NTB_OK;
 }
 
+}
+
+bool LdgEligible(const Problem & p)
+{
+    if (p.M <= 0 || p.N <= 0 || p.K <= 0 || p.count <= 0)
+        return false;
+    const bool f16 = p.dtAB == NTB_X_FLOAT16 && (p.dtC == NTB_X_FLOAT16 || p.dtC == NTB_X_FLOAT);
+    const bool f32 = p.dtAB == NTB_X_FLOAT && p.dtC == NTB_X_FLOAT;
+    if (!f16 && !f32)
+        return false;
+    const long long es = ElemSize(p.dtAB);
+    if (((uintptr_t)p.a % es) || ((uintptr_t)p.b % es) || p.lda < p.aCols || p.ldb < p.bCols)
+        return false;
+    return p.sAp >= 0 && p.sAq >= 0 && p.sBp >= 0 && p.sBq >= 0;
+}
+
+int LaunchLdg(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int * route)
+{
+    const int mode = p.dtAB == NTB_X_FLOAT16 ? 0 : 1;
+    /* a large fp32 product is split into half pieces by a pre-pass that reads the operands with
+       ordinary loads anyway: alignment does not matter to it */
+    if (mode == 1 && ForcedRoute() != NTB_ROUTE_TC_3XTF32 && Knob("NTB_F32_SPLIT", 1) != 0 && F32SplitEligible(ctx, p)) {
+        const int rc = LaunchF32Split(ctx, p, stream);
+        if (rc == NTB_OK)
+            *route = NTB_ROUTE_TC_F16X2;
+        return rc;
+    }
+    TcGroup grp;
+    grp.n = 1;
+    int rc = Prepare(ctx, p, mode, 128, false, 1, grp.p[0], grp.tm[0], true);
+    if (rc != NTB_OK)
+        return rc;
+    grp.p[1] = grp.p[0];
+    for (int i = 0; i < 3; i++)
+        grp.tm[1][i] = grp.tm[0][i];
+    grp.split = grp.total = grp.p[0].totalTiles;
+    if (p.nPeers > 0 && !grp.p[0].cTma)
+        return NTB_ERR_ARG;
+    *route = mode == 0 ? NTB_ROUTE_TC_F16 : NTB_ROUTE_TC_3XTF32;
+    if (Tune().debugChoice)
+        fprintf(stderr, "ntb: M %d N %d K %d count %d -> single 128 wide, loader warps (operands not addressable by TMA)\n",
+                p.M, p.N, p.K, p.count);
+    const bool oldc = p.beta != 0.f || p.nPeers > 0;
+    return LaunchLdgKernel(grp, mode, p.dtC, oldc, ctx.smCount, stream);
 }
 
 int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int * route)

@@ -52,6 +52,10 @@ struct TcParams {
     const void * bias;      /* N values of C's type added to every output row, or NULL */
     int act;                /* 1: max(x, 0) applied last */
     int * status;
+    /* operands as plain addresses, for the kernels whose loader warps fetch them with ordinary loads */
+    const void * a;
+    const void * b;
+    long long lda, ldb, sAp, sAq, sBp, sBq;   /* elements */
     int skipKBlock;         /* test hook: the producer arms this k-block of its first tile but never loads it; -1 off */
 };
 

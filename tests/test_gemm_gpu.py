@@ -116,11 +116,9 @@ def test_2d_all_transpositions(dtype, tA, tB, oracle):
         route = L.ntb_last_route()
         es = 2 if dtype == torch.float16 else 4
         aligned = (a.shape[1] * es) % 16 == 0 and (b.shape[1] * es) % 16 == 0
-        if aligned:
-            assert route in ((capi.ROUTE_TC_F16, capi.ROUTE_TC_F16_PAIR) if dtype == torch.float16
-                             else (capi.ROUTE_TC_3XTF32,)), (M, N, K)
-        else:
-            assert route == capi.ROUTE_SIMT, (M, N, K)
+        # pitches that TMA cannot address go to the tensor cores too, through loader warps
+        assert route in ((capi.ROUTE_TC_F16, capi.ROUTE_TC_F16_PAIR) if dtype == torch.float16
+                         else (capi.ROUTE_TC_3XTF32,)), (M, N, K, aligned)
         err = rel_fro(c.float().cpu().numpy(), want)
         assert err <= TOL[dtype], (M, N, K, alpha, beta, err, route)
     status_ok()
@@ -166,8 +164,9 @@ def test_half_inputs_float_output(oracle):
     status_ok()
 
 
-def test_misaligned_base_pointers_take_the_ffma_route(oracle):
-    """XMem pools hand out pieces back to back, so a tensor may start at any element."""
+def test_misaligned_base_pointers_stay_on_the_tensor_cores(oracle):
+    """XMem pools hand out pieces back to back, so a tensor may start at any element: such
+    operands cannot be described to TMA and are fetched by loader warps instead."""
     rng = np.random.default_rng(8)
     L = capi.lib()
     for dtype in (torch.float16, torch.float32):
@@ -182,7 +181,7 @@ def test_misaligned_base_pointers_take_the_ffma_route(oracle):
         assert av.data_ptr() % 16 != 0
         c = torch.zeros(M, N, device=DEV, dtype=dtype)
         ops._MatrixMul2D(av, X_NOTRANS, to_dev(b, dtype), X_NOTRANS, c)
-        assert L.ntb_last_route() == capi.ROUTE_SIMT
+        assert L.ntb_last_route() == (capi.ROUTE_TC_F16 if dtype == torch.float16 else capi.ROUTE_TC_3XTF32)
         assert rel_fro(c.float().cpu().numpy(), oracle.matmul2d(a, X_NOTRANS, b, X_NOTRANS)) <= TOL[dtype]
         # misaligned C only: tensor cores with scalar stores
         cbuf = torch.zeros(M * N + 1, device=DEV, dtype=dtype)
@@ -397,7 +396,7 @@ def test_peer_stores_are_refused_where_no_kernel_makes_them():
 
 def test_seeded_random_shapes_against_the_oracle(oracle):
     """120 seeded random products: extents 1..700 (multiples of 8 or not, so both the
-    tensor-core kernels and the FFMA kernel are reached), every transposition, batch counts
+    TMA-fed kernels and the ones with loader warps are reached), every transposition, batch counts
     1..5 in the strided and the general (p, q) form, alpha/beta drawn from a small set, half
     and float tensors, whatever kernel the cost model picks."""
     rng = np.random.default_rng(20240)
@@ -424,7 +423,7 @@ def test_seeded_random_shapes_against_the_oracle(oracle):
         routes.add(capi.lib().ntb_last_route())
         err = rel_fro(c.float().cpu().numpy(), oracle.matmul_batched(a, tA, b, tB, alpha, beta, c0))
         assert err <= TOL[dtype], (case, M, N, K, tA, tB, cnt, alpha, beta, dtype, err)
-    assert capi.ROUTE_SIMT in routes and capi.ROUTE_TC_F16 in routes and capi.ROUTE_TC_3XTF32 in routes
+    assert capi.ROUTE_SIMT not in routes and capi.ROUTE_TC_F16 in routes and capi.ROUTE_TC_3XTF32 in routes
     status_ok()
 
 
@@ -738,4 +737,87 @@ def test_host_buffer_entry(oracle):
         want = oracle.matmul_batched(a.astype(np.float32), X_NOTRANS, b.astype(np.float32), X_TRANS, 1.0, 0.5,
                                      c0.astype(np.float32))
         assert rel_fro(c.astype(np.float32), want) <= TOL[dtype]
+    status_ok()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("tA", [X_TRANS, X_NOTRANS])
+@pytest.mark.parametrize("tB", [X_TRANS, X_NOTRANS])
+def test_loader_warp_route_every_offset_and_pitch(dtype, tA, tB, oracle):
+    """Operands at every element offset inside a 16-byte unit, odd pitches, ragged extents,
+    batches: the loader warps realign each 128-byte row segment with funnel shifts and zero
+    what lies outside the matrix. Guard elements around every operand must not leak in."""
+    rng = np.random.default_rng(900 + 2 * tA + tB)
+    per16 = 8 if dtype == torch.float16 else 4
+    for case, (M, N, K, cnt) in enumerate([(128, 128, 64, 1), (200, 136, 75, 1), (37, 29, 53, 3), (130, 67, 129, 2),
+                                            (64, 72, 321, 1), (1, 5, 7, 1)]):
+        offA, offB = (case * 3 + 1) % per16, (case * 5 + 2) % per16
+        a = stored(rng, (cnt,), M, K, tA)
+        b = stored(rng, (cnt,), K, N, tB)
+        c0 = rng.normal(size=(cnt, M, N)).astype(np.float32)
+        if dtype == torch.float16:
+            a, b, c0 = round_to_half(a), round_to_half(b), round_to_half(c0)
+
+        def place(x, off):
+            # the matrix sits at an element offset in a buffer filled with a large guard value
+            buf = torch.full((x.size + off + 16,), 3.0e4, device=DEV, dtype=dtype)
+            buf[off:off + x.size] = to_dev(x, dtype).reshape(-1)
+            return buf, buf[off:off + x.size].view(x.shape)
+
+        abuf, av = place(a, offA)
+        bbuf, bv = place(b, offB)
+        c = to_dev(c0, dtype)
+        ops._MatrixMulBatched(av, tA, bv, tB, c, 0.5, 0.25)
+        assert capi.lib().ntb_last_route() in (capi.ROUTE_TC_F16, capi.ROUTE_TC_3XTF32)
+        want = oracle.matmul_batched(a, tA, b, tB, 0.5, 0.25, c0)
+        err = rel_fro(c.float().cpu().numpy(), want)
+        assert err <= TOL[dtype], (case, M, N, K, cnt, offA, offB, err)
+    status_ok()
+
+
+def test_two_byte_offset_operands_run_close_to_aligned_ones():
+    """4096 x 512 x 2048 in half precision from bases two bytes off a 16-byte boundary,
+    against the same product from aligned bases and on the FFMA kernel (CUDA events, best of
+    five rounds of ten). The loader warps keep the product on the tensor cores; they are
+    still several times slower than TMA."""
+    M, N, K = 4096, 512, 2048
+    g = torch.Generator(device=DEV)
+    g.manual_seed(5)
+    abuf = torch.randn(M * K + 8, device=DEV, generator=g).half()
+    bbuf = (torch.randn(K * N + 8, device=DEV, generator=g) / 45).half()
+    c = torch.zeros(M, N, device=DEV, dtype=torch.float16)
+    c2 = torch.zeros(M, N, device=DEV, dtype=torch.float16)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def best(av, bv, out):
+        times = []
+        for _ in range(5):
+            ops._MatrixMul2D(av, X_NOTRANS, bv, X_NOTRANS, out)
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(10):
+                ops._MatrixMul2D(av, X_NOTRANS, bv, X_NOTRANS, out)
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1) / 10)
+        return min(times)
+
+    t_off = best(abuf[1:1 + M * K].view(M, K), bbuf[1:1 + K * N].view(K, N), c)
+    assert capi.lib().ntb_last_route() == capi.ROUTE_TC_F16
+    # the same values from aligned storage
+    a_al = abuf[1:1 + M * K].clone().view(M, K)
+    b_al = bbuf[1:1 + K * N].clone().view(K, N)
+    t_al = best(a_al, b_al, c2)
+    assert torch.equal(c, c2)               # same products, same accumulation order
+    # what such operands cost before: the FFMA kernel
+    c3 = torch.zeros(M, N, device=DEV, dtype=torch.float16)
+    capi.lib().ntb_set_route(capi.ROUTE_SIMT)
+    try:
+        t_ffma = best(abuf[1:1 + M * K].view(M, K), bbuf[1:1 + K * N].view(K, N), c3)
+    finally:
+        capi.lib().ntb_set_route(0)
+    print("two-byte offset %.1f us, aligned %.1f us (ratio %.2f), FFMA kernel %.1f us" %
+          (t_off * 1e3, t_al * 1e3, t_off / t_al, t_ffma * 1e3))
+    assert t_off <= 0.5 * t_ffma
+    assert t_off <= 6.0 * t_al
     status_ok()
