@@ -118,13 +118,25 @@ int ntb_gemm_bias_act(int devID, void * stream,
  * transformer sample -- BMMul(q, k^T), ConvertDataType, Sum(mask), Softmax, ConvertDataType,
  * BMMul(att, v) (source/sample/transformer/submodel/Attention.cpp:206-238) -- whose score
  * tensor never reaches HBM here. Softmax as source/tensor/function/Softmax.cpp:60-115
- * (maximum subtracted, fp32, a row whose sum is 0 gives zeros). Limits of this version:
- * dim == 64 and lenK <= 256, else NTB_ERR_LIMIT; no dropout.
+ * (maximum subtracted, fp32, a row whose sum is 0 gives zeros). dim is 64 or 128 (the
+ * sample's default head size, Config.cpp:126,137), else NTB_ERR_LIMIT; lenK is unlimited (keys
+ * are taken 256 at a time; beyond 256 the scores are computed twice, once for the row maxima
+ * and once for the sums and the second product).
+ *
+ * ntb_attention_dropout is the training form (Attention.cpp:229-230: Dropout on the
+ * probabilities): keep holds one byte per probability, [blocks, lenQ, lenK], 1 = keep, 0 =
+ * drop (NULL: no dropout), and kept probabilities are multiplied by keepScale = 1 / (1 - p).
+ * The mask is the caller's, so that the same one can be given to any other implementation.
  */
 int ntb_attention(int devID, void * stream,
                   const void * q, const void * k, const void * v, const float * mask, void * out,
                   int dtype, int blocks, int lenQ, int lenK, int dim,
                   long long maskBlockStride, float scale);
+int ntb_attention_dropout(int devID, void * stream,
+                          const void * q, const void * k, const void * v, const float * mask,
+                          const unsigned char * keep, void * out,
+                          int dtype, int blocks, int lenQ, int lenK, int dim,
+                          long long maskBlockStride, float scale, float keepScale);
 
 /*
  * Row-wise log-softmax over the last dimension in two halves, for logits whose rows are

@@ -29,6 +29,7 @@ PROTOTYPES = {
     "ntb_gemm": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _i, _i] + [_i] * 6 + [_ll] * 3 + [_f, _f]),
     "ntb_gemm_bias_act": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i] + [_i] * 6 + [_ll] * 3 + [_f, _f, _i]),
     "ntb_attention": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _ll, _f]),
+    "ntb_attention_dropout": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _ll, _f, _f]),
     "ntb_row_stats": (_i, [_i, _vp, _vp, _i, _i, _i, _ll, _vp, _vp]),
     "ntb_logsoftmax_apply": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _vp, _vp]),
     "ntb_gemm_grad": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f]),

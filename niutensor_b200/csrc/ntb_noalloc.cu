@@ -159,6 +159,9 @@ extern "C" int ntb_gemm_host_noalloc(int devID, void * stream,
         if (forced != NTB_ROUTE_SIMT && TcEligible(p)) {
             rc = LaunchTc(ctx, p, st, &route);
         }
+        else if (forced != NTB_ROUTE_SIMT && forced != NTB_ROUTE_TC_F16_PAIR && LdgEligible(p)) {
+            rc = LaunchLdg(ctx, p, st, &route);         /* pitches TMA cannot address: loader warps, as everywhere else */
+        }
         else if (forced == NTB_ROUTE_TC_F16 || forced == NTB_ROUTE_TC_3XTF32 || forced == NTB_ROUTE_TC_F16_PAIR) {
             rc = NTB_ERR_ARG;                       /* a tensor-core route was demanded and cannot address this */
         }

@@ -320,6 +320,7 @@ int Prepare(const DeviceCtx & ctx, const Problem & p, int mode, int bn, bool pai
     tp.alpha = p.alpha; tp.beta = p.beta;
     tp.bias = p.bias; tp.act = p.act;
     tp.nPeers = p.nPeers;
+    tp.peerTma = 0;
     for (int i = 0; i < NTB_MAX_PEERS; i++)
         tp.peers[i] = i < p.nPeers ? p.peers[i] : nullptr;
     tp.status = ctx.status;
@@ -511,7 +512,21 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
         const bool oldc = tp.beta != 0.f || tp.nPeers > 0;
         /* tuning: epilogue warps of the 512 x 256 tile (8: two per tensor-memory sub-partition) */
         const int epiWarps = Knob("NTB_PAIR_EPIW", 8) == 4 ? 4 : 8;
-        return LaunchPairKernel(msub, bn, g, epiWarps, half, oldc, grp.tm[0], tp, pairs, stream);
+        /* peer copies of C through TMA stores (NTB_PEER_TMA=0: per-lane stores, as the other kernels do) */
+        PeerMaps pm;
+        const bool peerTma = tp.nPeers > 0 && tp.cTma && Knob("NTB_PEER_TMA", 1) != 0;
+        if (peerTma) {
+            long long stC = 0;
+            int extC = 1, sel = 0;
+            BatchSelector(p.sCp, p.sCq, p.count / p.Q, p.Q, &sel, &stC, &extC);
+            for (int k = 0; k < tp.nPeers; k++) {
+                rc = EncodeOutput(&pm.m[k], p.dtC, p.peers[k], p.M, p.N, p.ldc, stC, extC);
+                if (rc != NTB_OK)
+                    return rc;
+            }
+            grp.p[0].peerTma = 1;
+        }
+        return LaunchPairKernel(msub, bn, g, epiWarps, half, oldc, grp.tm[0], grp.p[0], peerTma ? &pm : nullptr, pairs, stream);
     }
     return LaunchGroup(grp, mode, bn, p.dtC, ctx.smCount, stream);
 }

@@ -46,6 +46,7 @@ struct TcParams {
     int epiHint;            /* suspend-time hint (ns) of the epilogue warps' barrier probes */
     void * peers[NTB_MAX_PEERS];   /* further destinations of every result tile (peer GPUs' C), or none */
     int nPeers;
+    int peerTma;            /* CTA-pair kernel: the peers are written with TMA stores through their own tensor maps */
     int l2Hint;             /* pair kernel: L2 eviction policy of the A loads (bits 0-1) and B loads (bits 2-3): 0 none, 1 keep, 2 stream */
     int cPrefetch;          /* wide tiles with beta != 0: 0 no L2 prefetch of old C, 1 boxes through TMA, 2 one request per line */
     float alpha, beta;
@@ -60,9 +61,15 @@ struct TcParams {
 };
 
 
+/* tensor maps of the peer copies of C (same shape and pitch as C): the CTA-pair kernel sends
+   each finished box to them with TMA stores instead of per-lane stores */
+struct PeerMaps {
+    CUtensorMap m[NTB_MAX_PEERS];
+};
+
 /* launchers of the cluster kernels (ntb_tc_pair.cu, ntb_tc_split.cu); maps: A, B, C */
 int LaunchPairKernel(int msub, int bn, int g, int epiWarps, bool half, bool oldc, const CUtensorMap * maps, const TcParams & tp,
-                     int pairs, cudaStream_t stream);
+                     const PeerMaps * peerMaps, int pairs, cudaStream_t stream);
 int LaunchSplitKernel(int split, int g, bool half, bool oldc, const CUtensorMap * maps, const TcParams & tp,
                       int clusters, cudaStream_t stream);
 
@@ -263,6 +270,7 @@ struct TileWriter {
     uint32_t stage;          /* shared-memory address of this warp's two boxes */
     uint32_t boxes;          /* boxes handed to TMA so far */
     const CUtensorMap * map;
+    const CUtensorMap * peerMaps;   /* maps of the peer copies of C, or NULL: peers are then written with per-lane stores */
     uint32_t bars;           /* two mbarriers, one per box buffer, for the loads of old C values */
     uint32_t phase;          /* bit b: parity of the next wait on buffer b's barrier */
     volatile int * abortFlag;
@@ -278,6 +286,7 @@ struct TileWriter {
         stage = epiBase + sub * NBOX * EPI_BOX_BYTES;
         boxes = 0;
         map = m;
+        peerMaps = nullptr;
         bars = SmemAddr(barPair);
         phase = 0;
         abortFlag = abortPtr;
@@ -492,9 +501,16 @@ struct TileWriter {
             if (lane == 0 && row0 < p.M) {
                 asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
                              :: "l"(map), "r"(c0 - colInBox), "r"(row0), "r"(batch), "r"(box) : "memory");
+                if (OLDC && peerMaps != nullptr) {
+                    /* the same box to the same place of every peer's C: more stores of the same
+                       bulk group, so the wait before the box is refilled covers them too */
+                    for (int k = 0; k < p.nPeers; k++)
+                        asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
+                                     :: "l"(peerMaps + k), "r"(c0 - colInBox), "r"(row0), "r"(batch), "r"(box) : "memory");
+                }
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
-            if (OLDC && p.nPeers > 0 && live)
+            if (OLDC && p.nPeers > 0 && live && peerMaps == nullptr)
                 BoxToPeers(p, cRow - (long long)lane * p.ldc, box, row0, c0 - colInBox, lane);
             boxes++;
         }

@@ -32,7 +32,7 @@ namespace {
 template <int MSUB, int BN, int STAGES, int G, int EPIW, typename OutT, bool OLDC>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + 32 * EPIW, 1)
 GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmC, TcParams p)
+                 const __grid_constant__ CUtensorMap tmC, const __grid_constant__ PeerMaps peerMaps, TcParams p)
 {
     constexpr int ES = 2;
     constexpr int EPR = ROW_BYTES / ES;                 /* 64 halves of K per stage */
@@ -262,6 +262,8 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         bool ok = true;
         TileWriter<OutT, OLDC, NBOX> writer;
         writer.Init(smemBase + STAGES * STAGE_BYTES, ew, &tmC, &barOldC[ew * 2], abortPtr, p.status);
+        if (OLDC && p.nPeers > 0 && p.peerTma)
+            writer.peerMaps = peerMaps.m;
         for (int t = firstTile; ok && t < p.totalTiles; t += tileStep, ++it) {
             TileCoord tc = DecodeTile(t, p);
             const int n0 = tc.nBlk * BN;
@@ -345,15 +347,15 @@ GemmTcPairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 }
 
 template <int MSUB, int BN, int STAGES, int G, int EPIW, typename OutT, bool OLDC>
-int LaunchPair(const CUtensorMap & tmA, const CUtensorMap & tmB, const CUtensorMap & tmC, const TcParams & tp, int pairs,
-               cudaStream_t stream)
+int LaunchPair(const CUtensorMap & tmA, const CUtensorMap & tmB, const CUtensorMap & tmC, const PeerMaps & pm, const TcParams & tp,
+               int pairs, cudaStream_t stream)
 {
     constexpr int smem = (MSUB * A_TILE_BYTES + (BN / 2) * ROW_BYTES) * STAGES + EPI_BYTES + 1024;
     auto kern = GemmTcPairKernel<MSUB, BN, STAGES, G, EPIW, OutT, OLDC>;
     static SmemOptIn optIn;
     if (!optIn.Ensure((const void *)kern, smem))
         return NTB_ERR_CUDA;
-    const cudaError_t err = LaunchPdl(kern, 2 * pairs, 64 + 32 * EPIW, smem, stream, tmA, tmB, tmC, tp);
+    const cudaError_t err = LaunchPdl(kern, 2 * pairs, 64 + 32 * EPIW, smem, stream, tmA, tmB, tmC, pm, tp);
     CountLaunch();
     return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? NTB_OK : NTB_ERR_CUDA;
 }
@@ -361,10 +363,12 @@ int LaunchPair(const CUtensorMap & tmA, const CUtensorMap & tmB, const CUtensorM
 }
 
 int LaunchPairKernel(int msub, int bn, int g, int epiWarps, bool half, bool oldc, const CUtensorMap * maps, const TcParams & tp,
-                     int pairs, cudaStream_t stream)
+                     const PeerMaps * peerMaps, int pairs, cudaStream_t stream)
 {
-#define NTB_PAIR2(MS, W, ST, GG, EW, T) (oldc ? LaunchPair<MS, W, ST, GG, EW, T, true>(maps[0], maps[1], maps[2], tp, pairs, stream) \
-                                              : LaunchPair<MS, W, ST, GG, EW, T, false>(maps[0], maps[1], maps[2], tp, pairs, stream))
+    static const PeerMaps noPeers = {};
+    const PeerMaps & pm = peerMaps ? *peerMaps : noPeers;
+#define NTB_PAIR2(MS, W, ST, GG, EW, T) (oldc ? LaunchPair<MS, W, ST, GG, EW, T, true>(maps[0], maps[1], maps[2], pm, tp, pairs, stream) \
+                                              : LaunchPair<MS, W, ST, GG, EW, T, false>(maps[0], maps[1], maps[2], pm, tp, pairs, stream))
 #define NTB_PAIR(MS, W, ST, GG, EW) (half ? NTB_PAIR2(MS, W, ST, GG, EW, __half) : NTB_PAIR2(MS, W, ST, GG, EW, float))
     if (bn == 256) {
         if (msub == 2)

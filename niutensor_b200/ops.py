@@ -181,12 +181,15 @@ def MulAndShift(x, w, b, alpha=1.0, transposedX=X_NOTRANS, transposedW=X_NOTRANS
     return c
 
 
-def ScaledDotProductAttention(q, k, v, mask=None, scale=None):
+def ScaledDotProductAttention(q, k, v, mask=None, scale=None, keep=None, drop_prob=0.0):
     """softmax(scale * q k^T + mask) v over the last two dimensions, leading dimensions being
     (head, batch) blocks: the fused form of the chain in Attention::MakeAttention
-    (source/sample/transformer/submodel/Attention.cpp:206-238; inference, no dropout).
-    q [..., lenQ, 64], k, v [..., lenK, 64] half tensors; mask None or fp32 of shape
-    [lenQ, lenK] (shared) or [..., lenQ, lenK]; scale defaults to 1 / sqrt(64)."""
+    (source/sample/transformer/submodel/Attention.cpp:206-238). q [..., lenQ, d], k, v
+    [..., lenK, d] half tensors, d = 64 or 128, any lenK; mask None or fp32 of shape
+    [lenQ, lenK] (shared) or [..., lenQ, lenK]; scale defaults to 1 / sqrt(d). Training:
+    keep is a uint8 tensor [..., lenQ, lenK] (1 = keep) applied to the probabilities with the
+    factor 1 / (1 - drop_prob), the reference's Dropout with the caller's mask
+    (Attention.cpp:229-230, source/tensor/function/Dropout.cpp:148-158)."""
     _check(q.is_cuda and k.is_cuda and v.is_cuda, "this library has no CPU path: tensors must live on a CUDA device")
     _check(q.dtype == torch.float16 and k.dtype == q.dtype and v.dtype == q.dtype, "Unsupported data type!")
     _check(q.dim() >= 2 and q.shape[:-2] == k.shape[:-2] == v.shape[:-2], "Incorrect tensor sizes!")
@@ -207,11 +210,17 @@ def ScaledDotProductAttention(q, k, v, mask=None, scale=None):
             _check(tuple(mask.shape) == tuple(q.shape[:-2]) + (lenQ, lenK), "Incorrect tensor sizes!")
             stride = lenQ * lenK
         mptr = mask.data_ptr()
+    kptr, keep_scale = None, 1.0
+    if keep is not None:
+        _check(keep.is_cuda and keep.dtype == torch.uint8 and keep.is_contiguous(), "the keep-mask must be a packed uint8 CUDA tensor")
+        _check(tuple(keep.shape) == tuple(q.shape[:-2]) + (lenQ, lenK), "Incorrect tensor sizes!")
+        _check(0.0 <= drop_prob < 1.0, "The probability must be 0-1!")
+        kptr, keep_scale = keep.data_ptr(), 1.0 / (1.0 - drop_prob)
     out = torch.empty_like(q)
     if scale is None:
         scale = 1.0 / (d ** 0.5)
-    rc = capi.lib().ntb_attention(q.device.index, _stream(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), mptr,
-                                  out.data_ptr(), X_FLOAT16, blocks, lenQ, lenK, d, stride, scale)
+    rc = capi.lib().ntb_attention_dropout(q.device.index, _stream(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), mptr, kptr,
+                                          out.data_ptr(), X_FLOAT16, blocks, lenQ, lenK, d, stride, scale, keep_scale)
     _raise_rc(rc, "ScaledDotProductAttention")
     return out
 

@@ -235,8 +235,9 @@ void orc_mulandshift_f32(const float * x, int transX, const float * w, int trans
  * q: [blocks, lenQ, dim], k, v: [blocks, lenK, dim], mask: NULL or [.., lenQ, lenK] with
  * maskBlockStride elements between blocks (0 = one mask for all), out: [blocks, lenQ, dim].
  */
-void orc_attention_f32(const float * q, const float * k, const float * v, const float * mask, float * out,
-                       int blocks, int lenQ, int lenK, int dim, long long maskBlockStride, float scale)
+void orc_attention_dropout_f32(const float * q, const float * k, const float * v, const float * mask,
+                               const unsigned char * keep, float keepScale, float * out,
+                               int blocks, int lenQ, int lenK, int dim, long long maskBlockStride, float scale)
 {
     int b, i, j;
     float * qs = (float *)malloc(sizeof(float) * (size_t)lenQ * dim);
@@ -270,6 +271,10 @@ void orc_attention_f32(const float * q, const float * k, const float * v, const 
                     else if (r < 0)
                         r = 0;
                 }
+                /* training: Dropout on the probabilities (Attention.cpp:229-230), i.e. a product
+                   with a mask of zeros and 1 / (1 - p) (source/tensor/function/Dropout.cpp:148-158) */
+                if (keep)
+                    r = r * (keep[((size_t)b * lenQ + i) * lenK + j] ? keepScale : 0.0f);
                 row[j] = r;
             }
         }
@@ -278,6 +283,12 @@ void orc_attention_f32(const float * q, const float * k, const float * v, const 
     }
     free(qs);
     free(att);
+}
+
+void orc_attention_f32(const float * q, const float * k, const float * v, const float * mask, float * out,
+                       int blocks, int lenQ, int lenK, int dim, long long maskBlockStride, float scale)
+{
+    orc_attention_dropout_f32(q, k, v, mask, NULL, 1.0f, out, blocks, lenQ, lenK, dim, maskBlockStride, scale);
 }
 
 /*

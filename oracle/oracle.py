@@ -110,6 +110,27 @@ class Oracle:
         """log-probabilities of the output layer: LogSoftmax(h w^T), w stored [vocab, hidden]."""
         return self.logsoftmax(self.matmul2d(_as_f32(h), X_NOTRANS, _as_f32(w), X_TRANS))
 
+    def attention_dropout(self, q, k, v, keep, keep_scale, mask=None, scale=1.0):
+        """attention with Dropout on the probabilities: keep [blocks, lenQ, lenK] uint8 (1 = keep),
+        kept probabilities times keep_scale = 1 / (1 - p)."""
+        q, k, v = _as_f32(q), _as_f32(k), _as_f32(v)
+        blocks, lenQ, d = q.shape
+        lenK = k.shape[1]
+        keep = np.ascontiguousarray(keep, dtype=np.uint8)
+        assert keep.shape == (blocks, lenQ, lenK)
+        out = np.zeros((blocks, lenQ, d), np.float32)
+        mp, stride = None, 0
+        if mask is not None:
+            mask = _as_f32(mask)
+            mp = _fp(mask)
+            stride = lenQ * lenK if mask.ndim == 3 else 0
+        fn = self.lib.orc_attention_dropout_f32
+        fn.argtypes = [_F32P, _F32P, _F32P, _F32P, ctypes.c_void_p, ctypes.c_float, _F32P] + [ctypes.c_int] * 4 + \
+            [ctypes.c_longlong, ctypes.c_float]
+        fn.restype = None
+        fn(_fp(q), _fp(k), _fp(v), mp, keep.ctypes.data, keep_scale, _fp(out), blocks, lenQ, lenK, d, stride, scale)
+        return out
+
     def attention(self, q, k, v, mask=None, scale=1.0):
         """softmax(scale * q k^T + mask) v per block; q [blocks, lenQ, d], k, v [blocks, lenK, d],
         mask None, [lenQ, lenK] (shared) or [blocks, lenQ, lenK]."""
@@ -241,20 +262,26 @@ def ref_mulandshift(ref, x, w, b, alpha=1.0, tX=X_NOTRANS, tW=X_NOTRANS):
     return c
 
 
-def ref_attention(ref, q, k, v, mask=None, scale=1.0):
-    """The reference's own CPU operator chain for inference-time attention."""
+def ref_attention(ref, q, k, v, mask=None, scale=1.0, keep=None, keep_scale=1.0):
+    """The reference's own CPU operator chain for attention; with `keep`, the probabilities are
+    multiplied by the dropout mask (zeros and keep_scale) as the reference's Dropout does."""
     q, k, v = _as_f32(q), _as_f32(k), _as_f32(v)
     blocks, lenQ, d = q.shape
     lenK = k.shape[1]
     out = np.zeros((blocks, lenQ, d), np.float32)
-    ref.lib.ref_attention_f32.argtypes = [_F32P, _F32P, _F32P, _F32P, _F32P] + [ctypes.c_int] * 4 + [ctypes.c_float]
+    fn = ref.lib.ref_attention_dropout_f32
+    fn.argtypes = [_F32P, _F32P, _F32P, _F32P, _F32P, _F32P] + [ctypes.c_int] * 4 + [ctypes.c_float]
     mp = None
     if mask is not None:
         mask = _as_f32(np.broadcast_to(mask, (blocks, lenQ, lenK)))
         mp = _fp(mask)
-    rc = ref.lib.ref_attention_f32(_fp(q), _fp(k), _fp(v), mp, _fp(out), blocks, lenQ, lenK, d, scale)
+    dp = None
+    if keep is not None:
+        drop = _as_f32(np.where(np.asarray(keep) != 0, np.float32(keep_scale), np.float32(0)))
+        dp = _fp(drop)
+    rc = fn(_fp(q), _fp(k), _fp(v), mp, dp, _fp(out), blocks, lenQ, lenK, d, scale)
     if rc != 0:
-        raise RuntimeError("ref_attention_f32 failed")
+        raise RuntimeError("ref_attention_dropout_f32 failed")
     return out
 
 

@@ -103,8 +103,9 @@ int ref_mulandshift_f32(const float * x, int xOrder, const int * xDims, int tran
    206-238 with the reference's own CPU operators: scale q, BMMul(q, k^T), add the mask,
    Softmax over the last dimension, BMMul(att, v). mask may be NULL; otherwise it has the
    shape of the scores. */
-int ref_attention_f32(const float * q, const float * k, const float * v, const float * mask, float * out,
-                      int blocks, int lenQ, int lenK, int dim, float scale)
+int ref_attention_dropout_f32(const float * q, const float * k, const float * v, const float * mask,
+                              const float * dropMask, float * out,
+                              int blocks, int lenQ, int lenK, int dim, float scale)
 {
     int dq[3] = { blocks, lenQ, dim }, dk[3] = { blocks, lenK, dim }, ds[3] = { blocks, lenQ, lenK };
     XTensor tq, att, att2;
@@ -123,11 +124,24 @@ int ref_attention_f32(const float * q, const float * k, const float * v, const f
         Drop(tm);
     }
     _Softmax(&att, &att2, 2);
+    if (dropMask != NULL) {
+        /* Dropout as source/tensor/function/Dropout.cpp:148-158 applies it: a product with a mask
+           of zeros and 1 / (1 - p); the mask is the caller's instead of the operator's own draw */
+        XTensor * td = View((float*)dropMask, 3, ds);
+        _Multiply(&att2, td, &att2);
+        Drop(td);
+    }
     _MatrixMulBatched(&att2, X_NOTRANS, tv, X_NOTRANS, to);
     Drop(tk);
     Drop(tv);
     Drop(to);
     return 0;
+}
+
+int ref_attention_f32(const float * q, const float * k, const float * v, const float * mask, float * out,
+                      int blocks, int lenQ, int lenK, int dim, float scale)
+{
+    return ref_attention_dropout_f32(q, k, v, mask, NULL, out, blocks, lenQ, lenK, dim, scale);
 }
 
 /* The normalised output layer of source/sample/transformer/submodel/Output.cpp:86-101 with

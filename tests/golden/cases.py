@@ -89,6 +89,32 @@ def attention_cases():
     return out
 
 
+def attention_cases_wide():
+    """(q, k, v, mask, scale, keep, keep_scale): the transformer sample's default head size of
+    128, key sequences beyond one 256-key step, and training-time dropout with a given
+    keep-mask (None: inference)."""
+    rng = np.random.default_rng(20244)
+    out = []
+    for (blocks, lenQ, lenK, dim, kind, drop) in [(2, 40, 70, 128, "none", 0.0), (2, 130, 256, 128, "block", 0.0),
+                                                  (1, 33, 300, 64, "block", 0.0), (2, 140, 600, 128, "shared", 0.0),
+                                                  (2, 50, 90, 64, "none", 0.1), (1, 64, 520, 128, "block", 0.3)]:
+        q = rng.normal(size=(blocks, lenQ, dim)).astype(np.float32)
+        k = rng.normal(size=(blocks, lenK, dim)).astype(np.float32)
+        v = rng.normal(size=(blocks, lenK, dim)).astype(np.float32)
+        mask = None
+        if kind == "shared":
+            mask = np.where(np.arange(lenK)[None, :] > np.arange(lenQ)[:, None] + 300, -1e9, 0.0).astype(np.float32)
+        elif kind == "block":
+            mask = np.where(rng.uniform(size=(blocks, lenQ, lenK)) < 0.25, -1e9, 0.0).astype(np.float32)
+            mask[:, :, 0] = 0.0
+        keep, keep_scale = None, 1.0
+        if drop > 0:
+            keep = (rng.uniform(size=(blocks, lenQ, lenK)) >= drop).astype(np.uint8)
+            keep_scale = 1.0 / (1.0 - drop)
+        out.append((q, k, v, mask, 1.0 / np.sqrt(dim), keep, keep_scale))
+    return out
+
+
 def output_layer_cases():
     """(h, w): hidden states and a [vocab, hidden] matrix; the third case has logits spread
     wide enough for the -20 floor of the reference's LogSoftmax to act."""

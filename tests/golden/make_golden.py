@@ -19,7 +19,9 @@ without either.
 
   ref_attention.npz  outputs of the reference's CPU operator chain for inference-time
                    attention (scale, BMMul, Sum(mask), Softmax, BMMul) on the seeded inputs
-                   of tests/golden/cases.py::attention_cases.
+                   of tests/golden/cases.py::attention_cases; ref_attention_wide.npz: the same
+                   chain for head size 128, long key sequences and dropout with a given mask
+                   (attention_cases_wide).
 
   ref_output_layer.npz  outputs of the reference's CPU MMul(h, w^T) + LogSoftmax on
                    tests/golden/cases.py::output_layer_cases.
@@ -39,7 +41,8 @@ sys.path.insert(0, ROOT)
 REF = os.environ.get("REF", "/root/reference")
 
 from oracle.oracle import Reference, ref_mulandshift, ref_attention, ref_output_layer, X_TRANS, X_NOTRANS  # noqa: E402
-from tests.golden.cases import seeded_cases, mulandshift_cases, attention_cases, output_layer_cases  # noqa: E402
+from tests.golden.cases import (seeded_cases, mulandshift_cases, attention_cases, attention_cases_wide,  # noqa: E402
+                                output_layer_cases)
 
 TEST_FILES = ["TMatrixMul.cpp", "TMatrixMul2D.cpp", "TMatrixMul2DParallel.cpp",
               "TMatrixMulBatched.cpp"]
@@ -106,6 +109,12 @@ def main():
         arrays["o%d" % i] = ref_attention(ref, q, k, v, mask, scale)
     np.savez_compressed(os.path.join(HERE, "ref_attention.npz"), **arrays)
     print("ref_attention.npz: %d cases" % len(arrays))
+
+    arrays = {}
+    for i, (q, k, v, mask, scale, keep, keep_scale) in enumerate(attention_cases_wide()):
+        arrays["o%d" % i] = ref_attention(ref, q, k, v, mask, scale, keep, keep_scale)
+    np.savez_compressed(os.path.join(HERE, "ref_attention_wide.npz"), **arrays)
+    print("ref_attention_wide.npz: %d cases" % len(arrays))
 
     arrays = {}
     for i, (h, w) in enumerate(output_layer_cases()):

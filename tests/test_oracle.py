@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 
 from oracle.oracle import (Oracle, Reference, ref_available, rel_fro, X_TRANS, X_NOTRANS)
-from tests.golden.cases import (seeded_cases, mulandshift_cases, attention_cases, output_layer_cases, FORM_GENERAL, FORM_BATCHED,
+from tests.golden.cases import (seeded_cases, mulandshift_cases, attention_cases, attention_cases_wide, output_layer_cases, FORM_GENERAL, FORM_BATCHED,
                                 FORM_2D)
 
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
@@ -83,6 +83,17 @@ def test_attention_oracle_matches_stored_reference_outputs(oracle):
     assert len(cases) == len(z.files) == 5
     for i, (q, k, v, mask, scale) in enumerate(cases):
         got = oracle.attention(q, k, v, mask, scale)
+        assert got.shape == z["o%d" % i].shape
+        assert rel_fro(got, z["o%d" % i]) <= 1e-6, i
+
+
+def test_attention_oracle_head_128_long_keys_and_dropout(oracle):
+    z = np.load(os.path.join(GOLD, "ref_attention_wide.npz"))
+    cases = attention_cases_wide()
+    assert len(cases) == len(z.files) == 6
+    for i, (q, k, v, mask, scale, keep, keep_scale) in enumerate(cases):
+        got = oracle.attention(q, k, v, mask, scale) if keep is None else \
+            oracle.attention_dropout(q, k, v, keep, keep_scale, mask, scale)
         assert got.shape == z["o%d" % i].shape
         assert rel_fro(got, z["o%d" % i]) <= 1e-6, i
 
