@@ -56,7 +56,7 @@ NCU_TRAFFIC_BYTES = 1.075e9
 def config_dict(world):
     return {"workload": WORKLOAD, "M": N_DIM, "N": N_DIM, "K": N_DIM, "N_per_gpu": N_DIM // max(1, world),
             "l2": "operands (537 MB at N=1) exceed the 126 MB L2; no flush between steps",
-            "parallelism": "column shards of B and C; all-gather of C by peer stores from the epilogue"
+            "parallelism": "column shards of B and C; all-gather of C by stores from the epilogue (see gather.method)"
                            if world > 1 else "one GPU"}
 
 
@@ -288,13 +288,24 @@ def main_ours(args):
 
     if world > 1:
         # every rank's whole C in symmetric memory; this rank writes its block of each
-        c_all, peers = shard.symmetric_matrix(N_DIM, N_DIM, torch.float16, dev)
+        want_mc = args.gather != "peers"
+        c_all, peers, mc = shard.symmetric_matrix(N_DIM, N_DIM, torch.float16, dev, multicast=want_mc) if want_mc \
+            else shard.symmetric_matrix(N_DIM, N_DIM, torch.float16, dev) + (0,)
+        # every rank must take the same path
+        flag = torch.tensor([1 if mc else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        use_mc = bool(flag.item())
         c_all.zero_()
         c_all[:, lo:hi] = c0
         plist = [peers[r] for r in sorted(peers)]
 
-        def step():
+        def step_peers():
             ops.MatrixMul2DToPeers(a, capi.X_NOTRANS, b, capi.X_NOTRANS, c_all, lo, plist, ALPHA, BETA)
+
+        def step_mc():
+            ops.MatrixMul2DToMulticast(a, capi.X_NOTRANS, b, capi.X_NOTRANS, c_all, lo, mc, ALPHA, BETA)
+
+        step = step_mc if use_mc else step_peers
     else:
         def step():
             ops._MatrixMul(a, capi.X_NOTRANS, b, capi.X_NOTRANS, c_local, ALPHA, BETA)
@@ -383,8 +394,18 @@ def main_ours(args):
             step_nccl()
         nccl_step_ms, _, _ = timed(step_nccl, sub_steps)
         nccl_gather_ms, _, _ = timed(gather_only, sub_steps)
+        peers_ms = None
+        if use_mc:
+            for _ in range(3):
+                step_peers()
+            peers_ms, _, _ = timed(step_peers, sub_steps)
         recv = (world - 1) * N_DIM * w * 2
-        gather = {"bytes_received_per_gpu": recv,
+        gather = {"method": ("multimem.st to the NVLink multicast address of C: each block leaves its GPU once, "
+                             "the switch replicates it" if use_mc else
+                             "TMA stores of every finished box to each peer's C: each block leaves its GPU n_gpus - 1 times"),
+                  "bytes_sent_per_gpu": N_DIM * w * 2 * (1 if use_mc else world - 1),
+                  "peer_stores_ms_per_step": peers_ms,
+                  "bytes_received_per_gpu": recv,
                   "fused_ms_per_step": ms_per_step,
                   "fused_extra_ms": ms_per_step - so_ms,
                   "fused_gb_per_s_per_gpu": recv / (ms_per_step * 1e-3) / 1e9,
@@ -393,7 +414,8 @@ def main_ours(args):
                   "nccl_all_gather_ms": nccl_gather_ms,
                   "nccl_gb_per_s_per_gpu": recv / (nccl_gather_ms * 1e-3) / 1e9,
                   "product_then_nccl_ms_per_step": nccl_step_ms,
-                  "limited_by": ("NVLink egress of the epilogue's peer stores" if ms_per_step > 1.15 * so_ms
+                  "limited_by": (("NVLink ingress of the replicated blocks" if use_mc else
+                                  "NVLink egress of the epilogue's peer stores") if ms_per_step > 1.15 * so_ms
                                  else "the product itself"),
                   "note": "fused = product whose epilogue stores its block into every rank's C (value); nccl = "
                           "all_gather_into_tensor of the packed shards + one re-interleave kernel, after the product"}
@@ -484,6 +506,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--gather", default="auto", choices=["auto", "peers"],
+                    help="N > 1: auto = through the NVLink multicast object where there is one, else stores to each peer")
     ap.add_argument("--no-configs", action="store_true", help="skip the table of the other benchmark configurations")
     ap.add_argument("--kernel-only", action="store_true",
                     help="only the headline region (short runs under a profiler)")

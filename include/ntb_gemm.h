@@ -225,6 +225,22 @@ int ntb_gemm_list(int devID, void * stream,
                   float alpha, float beta);
 
 /*
+ * A list of `count` products whose shapes may all differ (host arrays of device pointers and
+ * of stored extents; packed matrices; one pair of transposition flags, one alpha and beta for
+ * the whole list, as in _CudaBLASMatrixMULList). Replaces the fallback loop of single cuBLAS
+ * calls the reference takes when the shapes of a list are not uniform
+ * (source/tensor/core/arithmetic/XTensorBLAS.cu:373-385): up to eight problems share one
+ * persistent launch whose tile walk covers them one after the other; longer lists take one
+ * launch per eight. Items TMA cannot address and items with an empty inner dimension are
+ * issued on their own on the same stream. Shapes are all checked before anything is launched.
+ */
+int ntb_gemm_grouped(int devID, void * stream, int count,
+                     const void * const * a, int transA, const void * const * b, int transB, void * const * c,
+                     int dtypeAB, int dtypeC,
+                     const int * na, const int * ma, const int * nb, const int * mb, const int * nc, const int * mc,
+                     float alpha, float beta);
+
+/*
  * One 2-D product whose result is also written, tile by tile from the epilogue, to the
  * same rows and columns of up to NTB_MAX_PEERS further buffers of the shape and pitch of c:
  * the copies of C that other GPUs hold (their memory mapped into this process) or other
@@ -301,6 +317,25 @@ void ntb_shard_range(int total, int shards, int shard, int multiple, int * lo, i
  */
 int ntb_unshard_columns(int devID, void * stream, const void * src, void * dst, int dtype,
                         long long rows, int shards, int colsPerShard, long long ldDst);
+
+/*
+ * ntb_gemm_peers with the NVLink switch doing the fan-out: mc is the MULTICAST address of the
+ * place of this product's block in the copies of C that all GPUs of a group hold (a multicast
+ * object bound to every GPU's buffer: cuMulticastCreate / cuMulticastBindMem, or the
+ * multicast pointer of a symmetric-memory allocation). The epilogue writes every finished
+ * 128-byte line once, with multimem.st; the switch delivers it to every GPU, this one included,
+ * so each GPU sends its block once instead of once per peer. c is this GPU's ordinary address
+ * of the same block (old values for beta != 0 are read there, and the block is also written
+ * there directly). The column count of the block must be a whole number of 16-byte units.
+ * Visibility on the other GPUs as for ntb_gemm_peers: synchronise the stream, then the ranks.
+ * The reference has no counterpart (source/tensor/XUtility.cpp:196-201 copies whole tensors).
+ */
+int ntb_gemm_multicast(int devID, void * stream,
+                       const void * a, int transA, const void * b, int transB, void * c, void * mc,
+                       int dtypeAB, int dtypeC,
+                       int na, int ma, int nb, int mb, int nc, int mc_cols,
+                       long long lda, long long ldb, long long ldc,
+                       float alpha, float beta);
 
 /*
  * Host-buffer form: a, b and c are HOST memory (pinned or pageable). Copies the

@@ -306,6 +306,37 @@ def sharded_table(dev, world, rank, timed):
     return table
 
 
+def run_accuracy(dev):
+    """fp32 products against the float64 product of the same fp32 inputs, for K from 256 to
+    16384, on both fp32 routes (three kind::tf32 passes with chains of 256 of K; two half pieces
+    per value with chains of 512) and for torch.matmul (cuBLAS SGEMM): relative Frobenius error
+    and mean signed relative error. Inputs U[-1, 1] ("sym") and U[0, 1] ("pos": partial sums
+    only grow, the worst case for a truncating accumulator)."""
+    g = torch.Generator(device=dev)
+    g.manual_seed(77)
+    L = capi.lib()
+    for (M, N, K) in ((512, 512, 256), (512, 512, 1024), (512, 512, 4096), (512, 512, 16384), (2048, 2048, 2048)):
+        for kind in ("sym", "pos"):
+            a = torch.rand(M, K, device=dev, generator=g)
+            b = torch.rand(K, N, device=dev, generator=g)
+            if kind == "sym":
+                a, b = a * 2 - 1, b * 2 - 1
+            truth = a.double() @ b.double()
+            row = {"M": M, "N": N, "K": K, "inputs": kind}
+            for name, env in (("tf32x3", "0"), ("f16x2", "1")):
+                os.environ["NTB_F32_SPLIT"] = env
+                c = torch.zeros(M, N, device=dev)
+                ops._MatrixMul2D(a, X_NOTRANS, b, X_NOTRANS, c, 1.0, 0.0)
+                torch.cuda.synchronize()
+                d = c.double() - truth
+                row[name] = {"route": L.ntb_last_route(), "rel_fro": float(d.norm() / truth.norm()),
+                             "signed": float((d / truth.abs().clamp_min(1e-30)).mean()) if kind == "pos" else None}
+            os.environ.pop("NTB_F32_SPLIT", None)
+            d = (a @ b).double() - truth
+            row["cublas_sgemm_rel_fro"] = float(d.norm() / truth.norm())
+            print(json.dumps(row), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--configs", default="1,2a,2b,3a,3b,3fused,4,4lsm,5,5f32")
@@ -314,11 +345,15 @@ def main():
     ap.add_argument("--cublas", action="store_true")
     ap.add_argument("--shapes", default="",
                     help="extra fp16 products M x N x K (a row-major, b stored N x K, beta 0), e.g. 4096x512x2048,2048x1024x4096")
+    ap.add_argument("--accuracy", action="store_true", help="fp32 routes against float64 instead of timings")
     args = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("no CUDA device; this path has no CPU implementation")
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
+    if args.accuracy:
+        run_accuracy(dev)
+        return 0
     names = [n for n in args.configs.split(",") if n]
     for shape in [x for x in args.shapes.split(",") if x]:
         M, N, K = (int(v) for v in shape.lower().split("x"))

@@ -36,12 +36,15 @@ PROTOTYPES = {
     "ntb_gemm_strided_batched": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _i, _i] + [_i] * 6 + [_ll] * 6 + [_i, _f, _f]),
     "ntb_gemm_broadcast": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _i, _i] + [_i] * 6 + [_i, _i, _f, _f]),
     "ntb_gemm_peers": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, ctypes.POINTER(_vp), _i, _i, _i] + [_i] * 6 + [_ll] * 3 + [_f, _f]),
+    "ntb_gemm_multicast": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i] + [_i] * 6 + [_ll] * 3 + [_f, _f]),
     "ntb_gemm_list": (_i, [_i, _vp, ctypes.POINTER(_vp), _i, ctypes.POINTER(_vp), _i, ctypes.POINTER(_vp),
                            _i, _i, _i] + [_i] * 6 + [_f, _f]),
     "ntb_gemm_sharded": (_i, [ctypes.POINTER(_i), _i, ctypes.POINTER(_vp), ctypes.POINTER(_vp), _i, ctypes.POINTER(_vp), _i,
                               ctypes.POINTER(_vp), _i, _i] + [_i] * 6 + [_i, _i, _i, _f, _f]),
     "ntb_shard_range": (None, [_i, _i, _i, _i, ctypes.POINTER(_i), ctypes.POINTER(_i)]),
     "ntb_unshard_columns": (_i, [_i, _vp, _vp, _vp, _i, _ll, _i, _i, _ll]),
+    "ntb_gemm_grouped": (_i, [_i, _vp, _i, ctypes.POINTER(_vp), _i, ctypes.POINTER(_vp), _i, ctypes.POINTER(_vp), _i, _i] +
+                         [ctypes.POINTER(_i)] * 6 + [_f, _f]),
     "ntb_gemm_host": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _i, _i] + [_i] * 6 + [_ll] * 3 + [_i, _f, _f]),
     "ntb_gemm_host_noalloc": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _i, _i] + [_i] * 6 + [_f, _f]),
     "ntb_last_route": (_i, []),

@@ -495,6 +495,37 @@ int ntb_gemm_peers(int devID, void * stream,
     return Dispatch(devID, (cudaStream_t)stream, p);
 }
 
+int ntb_gemm_multicast(int devID, void * stream,
+                       const void * a, int transA, const void * b, int transB, void * c, void * mc,
+                       int dtypeAB, int dtypeC,
+                       int na, int ma, int nb, int mb, int nc, int mc_cols,
+                       long long lda, long long ldb, long long ldc,
+                       float alpha, float beta)
+{
+    Problem p;
+    memset(&p, 0, sizeof(p));
+    int rc = CheckDtypes(dtypeAB, dtypeC);
+    if (rc != NTB_OK)
+        return rc;
+    rc = SetShape(p, transA, transB, na, ma, nb, mb, nc, mc_cols);
+    if (rc != NTB_OK)
+        return rc;
+    const long long ces = ElemSize(dtypeC);
+    if (lda < ma || ldb < mb || ldc < mc_cols || !mc || ((uintptr_t)mc & 15) || (ldc * ces) % 16 || (mc_cols * ces) % 16)
+        return NTB_ERR_ARG;
+    p.peers[0] = mc;
+    p.nPeers = 1;
+    p.peerMcast = 1;
+    p.a = a; p.b = b; p.c = c;
+    p.dtAB = dtypeAB; p.dtC = dtypeC;
+    p.lda = lda; p.ldb = ldb; p.ldc = ldc;
+    p.count = 1; p.Q = 1;
+    p.alpha = alpha; p.beta = beta;
+    if (p.K == 0 || !TcEligible(p))
+        return NTB_ERR_ARG;
+    return Dispatch(devID, (cudaStream_t)stream, p);
+}
+
 int ntb_gemm_broadcast(int devID, void * stream,
                        const void * a, int transA, const void * b, int transB, void * c,
                        int dtypeAB, int dtypeC,

@@ -36,6 +36,7 @@ struct Problem {
        mapped into this process, or other buffers of this GPU) */
     void * peers[NTB_MAX_PEERS];
     int nPeers;
+    int peerMcast;          /* peers[0] is an NVLink multicast address: one multimem store reaches every GPU bound to it */
 };
 
 struct DeviceCtx {

@@ -321,6 +321,7 @@ int Prepare(const DeviceCtx & ctx, const Problem & p, int mode, int bn, bool pai
     tp.bias = p.bias; tp.act = p.act;
     tp.nPeers = p.nPeers;
     tp.peerTma = 0;
+    tp.peerMcast = p.peerMcast;
     for (int i = 0; i < NTB_MAX_PEERS; i++)
         tp.peers[i] = i < p.nPeers ? p.peers[i] : nullptr;
     tp.status = ctx.status;
@@ -382,6 +383,11 @@ int Prepare(const DeviceCtx & ctx, const Problem & p, int mode, int bn, bool pai
 
 }
 
+int PrepareSingle(const DeviceCtx & ctx, const Problem & p, int bn, TcParams & tp, CUtensorMap * maps)
+{
+    return Prepare(ctx, p, p.dtAB == NTB_X_FLOAT16 ? 0 : 1, bn, false, 1, tp, maps, false);
+}
+
 bool LdgEligible(const Problem & p)
 {
     if (p.M <= 0 || p.N <= 0 || p.K <= 0 || p.count <= 0)
@@ -415,7 +421,8 @@ int LaunchLdg(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int
     grp.p[1] = grp.p[0];
     for (int i = 0; i < 3; i++)
         grp.tm[1][i] = grp.tm[0][i];
-    grp.split = grp.total = grp.p[0].totalTiles;
+    grp.first[0] = 0;
+    grp.first[1] = grp.first[2] = grp.total = grp.p[0].totalTiles;
     if (p.nPeers > 0 && !grp.p[0].cTma)
         return NTB_ERR_ARG;
     *route = mode == 0 ? NTB_ROUTE_TC_F16 : NTB_ROUTE_TC_3XTF32;
@@ -487,7 +494,8 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
     grp.p[1] = grp.p[0];
     for (int i = 0; i < 3; i++)
         grp.tm[1][i] = grp.tm[0][i];
-    grp.split = grp.total = grp.p[0].totalTiles;
+    grp.first[0] = 0;
+    grp.first[1] = grp.first[2] = grp.total = grp.p[0].totalTiles;
 
     if (p.nPeers > 0 && !grp.p[0].cTma)
         return NTB_ERR_ARG;                         /* peer copies are made from the staged boxes */
@@ -514,7 +522,7 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
         const int epiWarps = Knob("NTB_PAIR_EPIW", 8) == 4 ? 4 : 8;
         /* peer copies of C through TMA stores (NTB_PEER_TMA=0: per-lane stores, as the other kernels do) */
         PeerMaps pm;
-        const bool peerTma = tp.nPeers > 0 && tp.cTma && Knob("NTB_PEER_TMA", 1) != 0;
+        const bool peerTma = tp.nPeers > 0 && tp.cTma && !p.peerMcast && Knob("NTB_PEER_TMA", 1) != 0;
         if (peerTma) {
             long long stC = 0;
             int extC = 1, sel = 0;
@@ -571,8 +579,9 @@ int LaunchTcTwo(const DeviceCtx & ctx, const Problem & p0, const Problem & p1, c
     rc = Prepare(ctx, p1, mode, bn, false, 1, grp.p[1], grp.tm[1]);
     if (rc != NTB_OK)
         return rc;
-    grp.split = grp.p[0].totalTiles;
-    grp.total = grp.p[0].totalTiles + grp.p[1].totalTiles;
+    grp.first[0] = 0;
+    grp.first[1] = grp.p[0].totalTiles;
+    grp.first[2] = grp.total = grp.p[0].totalTiles + grp.p[1].totalTiles;
     return LaunchGroup(grp, mode, bn, p0.dtC, ctx.smCount, stream);
 }
 

@@ -46,6 +46,7 @@ struct TcParams {
     int epiHint;            /* suspend-time hint (ns) of the epilogue warps' barrier probes */
     void * peers[NTB_MAX_PEERS];   /* further destinations of every result tile (peer GPUs' C), or none */
     int nPeers;
+    int peerMcast;          /* peers[0] is a multicast address, written with multimem.st */
     int peerTma;            /* CTA-pair kernel: the peers are written with TMA stores through their own tensor maps */
     int l2Hint;             /* pair kernel: L2 eviction policy of the A loads (bits 0-1) and B loads (bits 2-3): 0 none, 1 keep, 2 stream */
     int cPrefetch;          /* wide tiles with beta != 0: 0 no L2 prefetch of old C, 1 boxes through TMA, 2 one request per line */
@@ -535,11 +536,20 @@ struct TileWriter {
                          : "r"(box + (uint32_t)rr * ROW_BYTES + (uint32_t)((chunk ^ (rr & 7)) << 4)) : "memory");
             if (row0 + rr < p.M && col + VN <= p.N) {
                 const long long off = base + (long long)rr * p.ldc + col;
-                for (int k = 0; k < p.nPeers; k++)
-                    *(uint4 *)((OutT *)p.peers[k] + off) = make_uint4(w0, w1, w2, w3);
+                if (p.peerMcast) {
+                    /* one store, replicated by the NVLink switch into every GPU's copy of C */
+                    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                                 :: "l"((OutT *)p.peers[0] + off), "f"(__uint_as_float(w0)), "f"(__uint_as_float(w1)),
+                                    "f"(__uint_as_float(w2)), "f"(__uint_as_float(w3)) : "memory");
+                }
+                else {
+                    for (int k = 0; k < p.nPeers; k++)
+                        *(uint4 *)((OutT *)p.peers[k] + off) = make_uint4(w0, w1, w2, w3);
+                }
             }
-            else if (row0 + rr < p.M) {
-                const uint32_t w[4] = { w0, w1, w2, w3 };          /* ragged right edge: element by element */
+            else if (row0 + rr < p.M && !p.peerMcast) {
+                const uint32_t w[4] = { w0, w1, w2, w3 };          /* ragged right edge: element by element (multicast destinations
+                                                                      are only accepted with whole 16-byte columns) */
                 const OutT * e = (const OutT *)w;
                 for (int j = 0; j < VN; j++)
                     if (col + j < p.N) {

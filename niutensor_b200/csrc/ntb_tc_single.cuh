@@ -10,16 +10,27 @@
 
 namespace ntb {
 
-/* Up to two problems of different shapes in one launch (the two gradient products of a
-   matrix multiplication): tiles [0, split) belong to problem 0, the rest to problem 1. */
-struct TcGroup {
-    CUtensorMap tm[2][3];      /* A, B, C maps of each problem */
-    TcParams p[2];
-    int n, split, total;
+/* Several problems of different shapes in one launch: tiles [first[i], first[i + 1]) belong to
+   problem i. NP = 2 serves the two gradient products of a matrix multiplication (and every
+   single product); NP = GROUP_MAX the grouped entry point for lists of unequal shapes. The
+   whole group travels as kernel parameters, so NP is kept small where it is not needed. */
+constexpr int GROUP_MAX = 8;
+template <int NP>
+struct TcGroupT {
+    CUtensorMap tm[NP][3];     /* A, B, C maps of each problem */
+    TcParams p[NP];
+    int n, total;
+    int first[NP + 1];
 };
+typedef TcGroupT<2> TcGroup;
+typedef TcGroupT<GROUP_MAX> TcGroupWide;
 
 /* launcher of the kernels whose operands are fetched by loader warps (ntb_tc_ldg.cu) */
 int LaunchLdgKernel(const TcGroup & grp, int mode, int dtC, bool oldc, int smCount, cudaStream_t stream);
+/* launcher of the kernels that walk up to GROUP_MAX problems of unequal shapes (ntb_grouped.cu) */
+int LaunchWideGroup(const TcGroupWide & grp, int mode, int dtC, bool oldc, int smCount, cudaStream_t stream);
+/* kernel parameters and tensor maps of one problem for the single-CTA kernel with tiles bn wide (ntb_tc.cu) */
+int PrepareSingle(const DeviceCtx & ctx, const Problem & p, int bn, TcParams & tp, CUtensorMap * maps);
 
 namespace {
 
@@ -27,13 +38,16 @@ namespace {
 
 /* per-tile view of the problem a tile belongs to; names match the single-problem code */
 #define NTB_SELECT_PROBLEM() \
-    const int gi = t >= grp.split ? 1 : 0; \
+    int gi = 0; \
+    _Pragma("unroll") \
+    for (int k_ = 1; k_ < NP; k_++) \
+        gi += (k_ < grp.n && t >= grp.first[k_]) ? 1 : 0; \
     const TcParams & p = grp.p[gi]; \
     const CUtensorMap & tmA = grp.tm[gi][0]; \
     const CUtensorMap & tmB = grp.tm[gi][1]; \
     const CUtensorMap & tmC = grp.tm[gi][2]; \
     (void)tmA; (void)tmB; (void)tmC; \
-    const int tl = t - gi * grp.split; \
+    const int tl = t - grp.first[gi]; \
     const int kBlocks = (p.K + EPR - 1) / EPR; \
     /* k-blocks accumulated in TMEM before the partial sum is handed to the epilogue */ \
     const int chunkBlocks = MODE == 0 ? kBlocks : FP32_CHUNK_BLOCKS; \
@@ -87,9 +101,9 @@ __device__ __forceinline__ uint4 RealignChunk(uint4 own, uint4 next, uint32_t s,
     return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
-template <int MODE, int BN, int STAGES, int G, typename OutT, bool OLDC, bool LDG = false>
+template <int MODE, int BN, int STAGES, int G, typename OutT, bool OLDC, bool LDG = false, int NP = 2>
 __global__ void __launch_bounds__((MODE == 0 ? 192 : 192 + CONV_THREADS) + (LDG ? LDG_THREADS : 0), 1)
-GemmTcKernel(const __grid_constant__ TcGroup grp)
+GemmTcKernel(const __grid_constant__ TcGroupT<NP> grp)
 {
     static_assert(!LDG || G == 1, "loader warps fill one k-block per hand-shake");
     /* G k-blocks share one full / empty barrier pair: the producer and the MMA thread each
@@ -140,7 +154,7 @@ GemmTcKernel(const __grid_constant__ TcGroup grp)
            the MMA warp: a constant load that misses stalls its warp for the whole miss,
            one line after the other, and the producer reads half a dozen lines before its
            first copy. */
-        int touch = grp.total + grp.split;
+        int touch = grp.total + grp.first[1];
         for (int gi = 0; gi < grp.n; gi++) {
             const TcParams & p = grp.p[gi];
             if (threadIdx.x == 128) {
@@ -683,12 +697,12 @@ GemmTcKernel(const __grid_constant__ TcGroup grp)
 #endif
 }
 
-template <int MODE, int BN, int STAGES, int G, typename OutT, bool OLDC, bool LDG = false>
-int LaunchOne(const TcGroup & grp, int smCount, cudaStream_t stream)
+template <int MODE, int BN, int STAGES, int G, typename OutT, bool OLDC, bool LDG = false, int NP = 2>
+int LaunchOne(const TcGroupT<NP> & grp, int smCount, cudaStream_t stream)
 {
     constexpr int stage = (A_TILE_BYTES + BN * ROW_BYTES) * (MODE == 0 ? 1 : 2);
     constexpr int smem = stage * STAGES + EPI_BYTES + 1024;
-    auto kern = GemmTcKernel<MODE, BN, STAGES, G, OutT, OLDC, LDG>;
+    auto kern = GemmTcKernel<MODE, BN, STAGES, G, OutT, OLDC, LDG, NP>;
     static SmemOptIn optIn;
     if (!optIn.Ensure((const void *)kern, smem))
         return NTB_ERR_CUDA;

@@ -265,15 +265,37 @@ void _CudaBLASMatrixMULList(cublasHandle_t * handle, const TensorList * a, MATRI
         Fatal(rc, "_CudaBLASMatrixMULList");
         return;
     }
-    for (int i = 0; i < count; i++) {
-        XTensor * ai = (XTensor *)a->GetItem(i);
-        XTensor * bi = (XTensor *)b->GetItem(i);
-        XTensor * ci = (XTensor *)c->GetItem(i);
-        Fatal(ntb_gemm(ai->devID, NULL, ai->data, (int)transposedA, bi->data, (int)transposedB, ci->data,
-                       (int)ai->dataType, (int)ci->dataType, ai->dimSize[0], ai->dimSize[1],
-                       bi->dimSize[0], bi->dimSize[1], ci->dimSize[0], ci->dimSize[1],
-                       ai->dimSize[1], bi->dimSize[1], ci->dimSize[1], alpha, beta),
-              "_CudaBLASMatrixMULList");
+    /* shapes differ: one grouped launch per eight items instead of the reference's loop of
+       single calls (XTensorBLAS.cu:373-385); items of another data type or device go out alone */
+    {
+        const void ** ha = new const void *[count];
+        const void ** hb = new const void *[count];
+        void ** hc = new void *[count];
+        int * dims = new int[6 * count];
+        int n = 0;
+        for (int i = 0; i < count; i++) {
+            XTensor * ai = (XTensor *)a->GetItem(i);
+            XTensor * bi = (XTensor *)b->GetItem(i);
+            XTensor * ci = (XTensor *)c->GetItem(i);
+            if (ai->dataType != a0->dataType || ci->dataType != c0->dataType || ai->devID != a0->devID) {
+                Fatal(ntb_gemm(ai->devID, NULL, ai->data, (int)transposedA, bi->data, (int)transposedB, ci->data,
+                               (int)ai->dataType, (int)ci->dataType, ai->dimSize[0], ai->dimSize[1],
+                               bi->dimSize[0], bi->dimSize[1], ci->dimSize[0], ci->dimSize[1],
+                               ai->dimSize[1], bi->dimSize[1], ci->dimSize[1], alpha, beta),
+                      "_CudaBLASMatrixMULList");
+                continue;
+            }
+            ha[n] = ai->data; hb[n] = bi->data; hc[n] = ci->data;
+            dims[0 * count + n] = ai->dimSize[0]; dims[1 * count + n] = ai->dimSize[1];
+            dims[2 * count + n] = bi->dimSize[0]; dims[3 * count + n] = bi->dimSize[1];
+            dims[4 * count + n] = ci->dimSize[0]; dims[5 * count + n] = ci->dimSize[1];
+            n++;
+        }
+        int rc = ntb_gemm_grouped(a0->devID, NULL, n, ha, (int)transposedA, hb, (int)transposedB, hc,
+                                  (int)a0->dataType, (int)c0->dataType, dims, dims + count, dims + 2 * count,
+                                  dims + 3 * count, dims + 4 * count, dims + 5 * count, alpha, beta);
+        delete[] ha; delete[] hb; delete[] hc; delete[] dims;
+        Fatal(rc, "_CudaBLASMatrixMULList");
     }
 }
 

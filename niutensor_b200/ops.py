@@ -302,3 +302,22 @@ def MatrixMul2DToPeers(a, transposedA, b, transposedB, c_full, col0, peer_bases,
                                    a.shape[0], a.shape[1], b.shape[0], b.shape[1], an, bm,
                                    a.shape[1], b.shape[1], c_full.shape[1], alpha, beta)
     _raise_rc(rc, "MatrixMul2DToPeers")
+
+
+def MatrixMul2DToMulticast(a, transposedA, b, transposedB, c_full, col0, mc_base, alpha=1.0, beta=0.0):
+    """As MatrixMul2DToPeers, with the NVLink switch replicating the block: mc_base is the
+    multicast address of c_full (symmetric memory bound to every rank's copy); each finished
+    line is written once with multimem.st and lands in every rank's C (ntb_gemm_multicast)."""
+    _common_checks(a, b, c_full)
+    _check(a.dim() == 2 and b.dim() == 2 and c_full.dim() == 2, "Input tensors must have a order = 2!")
+    an, am = (a.shape[1], a.shape[0]) if transposedA == X_TRANS else (a.shape[0], a.shape[1])
+    bn, bm = (b.shape[1], b.shape[0]) if transposedB == X_TRANS else (b.shape[0], b.shape[1])
+    _check(am == bn and an == c_full.shape[0] and 0 <= col0 and col0 + bm <= c_full.shape[1],
+           "Unmatched tensors in multiplication!")
+    es = c_full.element_size()
+    rc = capi.lib().ntb_gemm_multicast(a.device.index, _stream(a), a.data_ptr(), transposedA, b.data_ptr(), transposedB,
+                                       c_full.data_ptr() + col0 * es, int(mc_base) + col0 * es,
+                                       _dtype_code(a), _dtype_code(c_full),
+                                       a.shape[0], a.shape[1], b.shape[0], b.shape[1], an, bm,
+                                       a.shape[1], b.shape[1], c_full.shape[1], alpha, beta)
+    _raise_rc(rc, "MatrixMul2DToMulticast")

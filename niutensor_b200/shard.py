@@ -53,20 +53,33 @@ def matmul_column_shard(a, transposedA, b_local, transposedB, alpha=1.0, beta=0.
     return ops.MatrixMul(a, transposedA, b_local, transposedB, alpha, beta, c=c_local)
 
 
-def symmetric_matrix(rows, cols, dtype, device, group=None):
+def symmetric_matrix(rows, cols, dtype, device, group=None, multicast=False):
     """A [rows, cols] matrix allocated on every rank of the group in symmetric memory, and
     the device addresses under which this process can write the other ranks' copies (NVLink
-    peer mappings; plain stores, no multicast: TORCH_SYMM_MEM_DISABLE_MULTICAST is set unless
-    the caller chose otherwise). Returns (tensor, {rank: address})."""
+    peer mappings). Returns (tensor, {rank: address}) -- plain stores, no multicast object:
+    TORCH_SYMM_MEM_DISABLE_MULTICAST is set unless the caller chose otherwise -- or, with
+    multicast=True, (tensor, {rank: address}, multicast address or 0): the address under which
+    one multimem store reaches every rank's copy, 0 where the platform offers no NVLink
+    multicast. The first symmetric allocation of a process decides which of the two it gets."""
     import os
-    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+    if multicast:
+        os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "0"
+    else:
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
     import torch.distributed._symmetric_memory as symm
     group = group if group is not None else dist.group.WORLD
     t = symm.empty((rows, cols), dtype=dtype, device=device)
     hdl = symm.rendezvous(t, group)
     me = dist.get_rank(group)
     peers = {r: int(hdl.buffer_ptrs[r]) for r in range(dist.get_world_size(group)) if r != me}
-    return t, peers
+    if not multicast:
+        return t, peers
+    mc = 0
+    try:
+        mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
+    except Exception:
+        mc = 0
+    return t, peers, mc
 
 
 def matmul_column_shard_to_all(a, transposedA, b_local, transposedB, c_sym, peer_addrs, n_cols, group=None,

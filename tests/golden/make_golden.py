@@ -38,7 +38,7 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
-REF = os.environ.get("REF", "/root/reference")
+REF = os.environ.get("REF") or os.path.join(os.path.dirname(ROOT), "reference")
 
 from oracle.oracle import Reference, ref_mulandshift, ref_attention, ref_output_layer, X_TRANS, X_NOTRANS  # noqa: E402
 from tests.golden.cases import (seeded_cases, mulandshift_cases, attention_cases, attention_cases_wide,  # noqa: E402
