@@ -199,7 +199,11 @@ void _CudaBLASMatrixMULBatchedStrided(cublasHandle_t * handle,
 }
 
 /* a, b, c are DEVICE arrays of device pointers here, as in the reference; they are read
-   back once so that the planner can look for a stride pattern */
+   back once so that the planner can look for a stride pattern. The reference's own callers
+   never reach this function once _CudaBLASMatrixMULList is replaced (it builds the tables
+   itself); the symbol stays for code that linked to it. The tables must have been written by
+   work the device has already finished or that was queued on the legacy default stream
+   before this call, as cublasGemmBatchedEx on the handle's stream required. */
 void _CudaBLASMatrixMULBatched(cublasHandle_t * handle,
                                const void ** a, MATRIX_TRANS_TYPE transposedA, TENSOR_DATA_TYPE dataTypeA,
                                const void ** b, MATRIX_TRANS_TYPE transposedB, TENSOR_DATA_TYPE dataTypeB,
@@ -216,9 +220,11 @@ void _CudaBLASMatrixMULBatched(cublasHandle_t * handle,
     const void ** ha = new const void *[count];
     const void ** hb = new const void *[count];
     void ** hc = new void *[count];
-    cudaMemcpy(ha, a, sizeof(void *) * count, cudaMemcpyDeviceToHost);
-    cudaMemcpy(hb, b, sizeof(void *) * count, cudaMemcpyDeviceToHost);
-    cudaMemcpy(hc, c, sizeof(void *) * count, cudaMemcpyDeviceToHost);
+    /* three copies in flight on the calling thread's default stream, one wait for all */
+    cudaMemcpyAsync(ha, a, sizeof(void *) * count, cudaMemcpyDeviceToHost, cudaStreamPerThread);
+    cudaMemcpyAsync(hb, b, sizeof(void *) * count, cudaMemcpyDeviceToHost, cudaStreamPerThread);
+    cudaMemcpyAsync(hc, c, sizeof(void *) * count, cudaMemcpyDeviceToHost, cudaStreamPerThread);
+    cudaStreamSynchronize(cudaStreamPerThread);
     int rc = ntb_gemm_list(dev, NULL, ha, (int)transposedA, hb, (int)transposedB, hc,
                            (int)dataTypeA, (int)dataTypeC, count, na, ma, nb, mb, nc, mc, alpha, beta);
     delete[] ha; delete[] hb; delete[] hc;

@@ -94,6 +94,27 @@ def test_sharded_entry_checks_arguments_before_cuda():
     assert L.ntb_unshard_columns(0, None, 4096, 8192, f16, 0, 2, 8, 16) == capi.OK
 
 
+def test_grouped_and_multicast_entries_check_arguments_before_cuda():
+    L = capi.lib()
+    f16 = capi.X_FLOAT16
+    vp = ctypes.c_void_p
+    ptrs = (vp * 2)(4096, 4096)
+    ia = lambda *v: (ctypes.c_int * 2)(*v)
+    ok = (ia(8, 16), ia(8, 8), ia(8, 8), ia(8, 24), ia(8, 16), ia(8, 24))
+    assert L.ntb_gemm_grouped(0, None, 0, None, 1, None, 1, None, f16, f16, None, None, None, None, None, None, 1.0, 0.0) == capi.OK
+    assert L.ntb_gemm_grouped(0, None, -1, ptrs, 1, ptrs, 1, ptrs, f16, f16, *ok, 1.0, 0.0) == capi.ERR_ARG
+    assert L.ntb_gemm_grouped(0, None, 2, ptrs, 5, ptrs, 1, ptrs, f16, f16, *ok, 1.0, 0.0) == capi.ERR_ARG
+    assert L.ntb_gemm_grouped(0, None, 2, ptrs, 1, ptrs, 1, ptrs, capi.X_INT, capi.X_INT, *ok, 1.0, 0.0) == capi.ERR_DTYPE
+    bad = (ia(8, 16), ia(8, 9), ia(8, 8), ia(8, 24), ia(8, 16), ia(8, 24))     # second item: inner extents 9 and 8
+    assert L.ntb_gemm_grouped(0, None, 2, ptrs, 1, ptrs, 1, ptrs, f16, f16, *bad, 1.0, 0.0) == capi.ERR_SHAPE
+    # multicast destination: NULL, misaligned, or a column count that is not a whole number of 16-byte units
+    args = (0, None, 4096, 1, 4096, 1, 4096)
+    tail = (f16, f16, 8, 8, 8, 16, 8, 16, 8, 16, 16, 1.0, 0.0)
+    assert L.ntb_gemm_multicast(*args, None, *tail) == capi.ERR_ARG
+    assert L.ntb_gemm_multicast(*args, 4098, *tail) == capi.ERR_ARG
+    assert L.ntb_gemm_multicast(*args, 8192, f16, f16, 8, 8, 8, 12, 8, 12, 8, 12, 16, 1.0, 0.0) == capi.ERR_ARG
+
+
 def test_no_cpu_fallback_without_a_device():
     import torch
     if torch.cuda.is_available():

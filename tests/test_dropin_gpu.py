@@ -3,7 +3,14 @@ translation units replaced by niutensor_b200/host/nts_matmul_shim.cpp (built by
 `make -C oracle dropin` into oracle/_ref/, which exists only where the reference sources
 were available at build time). The reference's own unit tests for this path then run on
 the new kernels, and user-level calls the reference has no test for are compared with the
-CPU oracle."""
+CPU oracle.
+
+Only the GPU halves of the reference's unit tests are evidence here: for tensors on the CPU
+(devID < 0) the shim hands the product to the reference's untouched _MatrixMul2DParallel, so
+the CPU halves, and TestMatrixMul2DParallel as a whole, are the reference checking itself.
+The tensors of these unit tests are allocated without a memory pool (mem == NULL); tensors
+that live in XMem pools are covered by tests/test_samples_gpu.py (the transformer sample
+allocates from its pools) and by the loader-warp cases of tests/test_gemm_gpu.py."""
 import ctypes
 import os
 
