@@ -430,6 +430,9 @@ int ntb_plan(int dtypeAB, int M, int N, int K, int count, int smCount);
 /* Products issued so far in this process through the kernel family `route` (NTB_ROUTE_*): shows,
    for a whole program, how many products alignment pushed off the tensor cores. */
 long long ntb_route_count(int route);
+/* one more counter read through the same call: products whose operands were first copied
+   into 16-byte aligned rows because TMA could not address them where they lay */
+#define NTB_COUNT_REPACK   7
 
 /* Number of kernels this library has launched in the process so far. */
 long long ntb_launch_count(void);

@@ -345,6 +345,8 @@ def main():
     ap.add_argument("--cublas", action="store_true")
     ap.add_argument("--shapes", default="",
                     help="extra fp16 products M x N x K (a row-major, b stored N x K, beta 0), e.g. 4096x512x2048,2048x1024x4096")
+    ap.add_argument("--f32-shapes", default="",
+                    help="extra fp32 products M x N x K (a and b row-major, beta 0.5), e.g. 4096x4096x4096")
     ap.add_argument("--accuracy", action="store_true", help="fp32 routes against float64 instead of timings")
     args = ap.parse_args()
     if not torch.cuda.is_available():
@@ -359,6 +361,10 @@ def main():
         M, N, K = (int(v) for v in shape.lower().split("x"))
         CONFIGS[shape] = (torch.float16, 1, M, N, K, X_NOTRANS, X_TRANS, 1.0, 0.0, "tensor", "fp16 " + shape)
         names.append(shape)
+    for shape in [x for x in args.f32_shapes.split(",") if x]:
+        M, N, K = (int(v) for v in shape.lower().split("x"))
+        CONFIGS["f32 " + shape] = (torch.float32, 1, M, N, K, X_NOTRANS, X_NOTRANS, 1.0, 0.5, "tensor", "fp32 " + shape)
+        names.append("f32 " + shape)
     for name in names:
         if name == "4lsm":
             print(json.dumps(run_output_layer(args.iters, not args.no_graph, args.cublas, dev)), flush=True)

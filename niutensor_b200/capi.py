@@ -11,6 +11,7 @@ LIB_PATH = os.path.join(_HERE, "libntb_gemm.so")
 
 X_INT, X_INT8, X_FLOAT, X_FLOAT16, X_DOUBLE = 0, 1, 2, 3, 4
 X_TRANS, X_NOTRANS = 0, 1
+COUNT_REPACK = 7
 ROUTE_NONE, ROUTE_TC_F16, ROUTE_TC_3XTF32, ROUTE_SIMT, ROUTE_TC_F16_PAIR, ROUTE_TC_F16X2 = 0, 1, 2, 3, 4, 5
 OK, ERR_ARG, ERR_SHAPE, ERR_DTYPE, ERR_CUDA, ERR_DEVICE_WAIT, ERR_LIMIT = range(7)
 MAX_PEERS = 8

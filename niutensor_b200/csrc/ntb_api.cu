@@ -102,7 +102,8 @@ int Dispatch(int devID, cudaStream_t stream, Problem & p)
 {
     if (p.count == 0 || p.M == 0 || p.N == 0)
         return NTB_OK;
-    if (!p.a || !p.b || !p.c)
+    /* with K = 0 the operands are empty and never read: frameworks hand out NULL for them */
+    if (!p.c || (p.K > 0 && (!p.a || !p.b)))
         return NTB_ERR_ARG;
     DeviceGuard guard(devID);
     if (!guard.ok) {
@@ -257,6 +258,12 @@ void SetLastRoute(int route)
     tLastRoute = route;
     if (route >= 0 && route < 8)
         gRouteCount[route].fetch_add(1);
+}
+
+void CountVariant(int index)
+{
+    if (index >= 0 && index < 8)
+        gRouteCount[index].fetch_add(1);
 }
 
 int InjectedSkipKBlock()

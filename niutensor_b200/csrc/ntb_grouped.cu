@@ -50,8 +50,8 @@ extern "C" int ntb_gemm_grouped(int devID, void * stream, int count,
         const int bn = transB == NTB_X_TRANS ? mb[i] : nb[i], bm = transB == NTB_X_TRANS ? nb[i] : mb[i];
         if (am != bn || an != nc[i] || bm != mc[i])
             return NTB_ERR_SHAPE;
-        if (nc[i] > 0 && mc[i] > 0 && (!a[i] || !b[i] || !c[i]))
-            return NTB_ERR_ARG;
+        if (nc[i] > 0 && mc[i] > 0 && (!c[i] || (am > 0 && (!a[i] || !b[i]))))
+            return NTB_ERR_ARG;                     /* empty operands (K = 0) may be NULL */
     }
     int prev = -1;
     if (cudaGetDevice(&prev) != cudaSuccess || (prev != devID && cudaSetDevice(devID) != cudaSuccess)) {

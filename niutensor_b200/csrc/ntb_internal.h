@@ -73,6 +73,11 @@ int LaunchSimt(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream);
    loader warps fetch them with ordinary loads */
 bool LdgEligible(const Problem & p);
 int LaunchLdg(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int * route);
+/* realigning pre-pass (ntb_repack.cu): operands TMA cannot address are copied into 16-byte
+   aligned rows in scratch memory and the product runs on the TMA-fed kernels; LaunchRepacked
+   returns NTB_ERR_ARG, with nothing launched, when that does not apply */
+bool RepackWorthwhile(const DeviceCtx & ctx, const Problem & p);
+int LaunchRepacked(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int * route);
 /* NTB_PDL=0 in the environment turns programmatic stream serialisation off */
 inline bool PdlEnabled()
 {
@@ -126,6 +131,7 @@ int LaunchF32Split(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream
 void CountLaunch();
 int ForcedRoute();           /* value of the last ntb_set_route() */
 int InjectedSkipKBlock();    /* test hook (ntb_debug_inject): k-block whose loads the producers leave out, or -1 */
+void CountVariant(int index);  /* NTB_COUNT_*: variants of a route, read through ntb_route_count() */
 void SetLastRoute(int route); /* what ntb_last_route() reports for the calling thread */
 
 /* The opt-in to more than 48 KB of dynamic shared memory is per kernel and per device. One

@@ -413,6 +413,13 @@ int LaunchLdg(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int
             *route = NTB_ROUTE_TC_F16X2;
         return rc;
     }
+    /* large enough to pay for one more pass over the operands: copy them into aligned rows
+       once and use the TMA-fed kernels (NTB_REPACK=0 keeps the loader warps) */
+    if (Knob("NTB_REPACK", 1) != 0 && RepackWorthwhile(ctx, p)) {
+        const int rr = LaunchRepacked(ctx, p, stream, route);
+        if (rr != NTB_ERR_ARG)
+            return rr;
+    }
     TcGroup grp;
     grp.n = 1;
     int rc = Prepare(ctx, p, mode, 128, false, 1, grp.p[0], grp.tm[0], true);

@@ -2,6 +2,8 @@
 value distributions, CUDA path against the CPU oracle. The 8192^3 case is checked on a
 row sample by the oracle and, over the whole output, through row and column checksums
 and through agreement of column-sharded launches with the single launch."""
+import os
+
 import numpy as np
 import pytest
 import torch

@@ -775,11 +775,57 @@ def test_loader_warp_route_every_offset_and_pitch(dtype, tA, tB, oracle):
     status_ok()
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("tA", [X_TRANS, X_NOTRANS])
+@pytest.mark.parametrize("tB", [X_TRANS, X_NOTRANS])
+def test_realigning_prepass_for_larger_products(dtype, tA, tB, oracle):
+    """From 2e8 floating-point operations on, operands TMA cannot address are first copied
+    into 16-byte aligned rows in scratch memory (one pass of aligned loads, funnel shifts and
+    aligned stores) and the product runs on the TMA-fed kernels. Every element offset, odd
+    pitches, ragged extents, batches and a shared operand; guard values must not leak in.
+    With NTB_REPACK=0 the same calls take the loader-warp kernel and must agree."""
+    rng = np.random.default_rng(1900 + 2 * tA + tB)
+    per16 = 8 if dtype == torch.float16 else 4
+    L = capi.lib()
+    for case, (M, N, K, cnt) in enumerate([(520, 264, 777, 1), (300, 201, 455, 5), (1024, 136, 1030, 1)]):
+        offA, offB = (case * 3 + 1) % per16, (case * 5 + 2) % per16
+        a = stored(rng, (cnt,), M, K, tA)
+        b = stored(rng, (cnt,), K, N, tB)
+        c0 = rng.normal(size=(cnt, M, N)).astype(np.float32)
+        if dtype == torch.float16:
+            a, b, c0 = round_to_half(a), round_to_half(b), round_to_half(c0)
+
+        def place(x, off):
+            buf = torch.full((x.size + off + 16,), 3.0e4, device=DEV, dtype=dtype)
+            buf[off:off + x.size] = to_dev(x, dtype).reshape(-1)
+            return buf, buf[off:off + x.size].view(x.shape)
+
+        abuf, av = place(a, offA)
+        bbuf, bv = place(b, offB)
+        want = oracle.matmul_batched(a, tA, b, tB, 0.5, 0.25, c0)
+        results = []
+        for repack in ("1", "0"):
+            os.environ["NTB_REPACK"] = repack
+            counted = L.ntb_route_count(capi.COUNT_REPACK)
+            try:
+                c = to_dev(c0, dtype)
+                ops._MatrixMulBatched(av, tA, bv, tB, c, 0.5, 0.25)
+            finally:
+                del os.environ["NTB_REPACK"]
+            assert L.ntb_route_count(capi.COUNT_REPACK) == counted + (1 if repack == "1" else 0)
+            assert L.ntb_last_route() in (capi.ROUTE_TC_F16, capi.ROUTE_TC_F16_PAIR, capi.ROUTE_TC_3XTF32)
+            err = rel_fro(c.float().cpu().numpy(), want)
+            assert err <= TOL[dtype], (case, repack, M, N, K, cnt, offA, offB, err)
+            results.append(c)
+        assert rel_fro(results[0].float().cpu().numpy(), results[1].float().cpu().numpy()) <= TOL[dtype]
+    status_ok()
+
+
 def test_two_byte_offset_operands_run_close_to_aligned_ones():
     """4096 x 512 x 2048 in half precision from bases two bytes off a 16-byte boundary,
-    against the same product from aligned bases and on the FFMA kernel (CUDA events, best of
-    five rounds of ten). The loader warps keep the product on the tensor cores; they are
-    still several times slower than TMA."""
+    against the same product from aligned bases, with the loader-warp kernel alone
+    (NTB_REPACK=0) and on the FFMA kernel (CUDA events, best of five rounds of ten). With
+    the realigning pre-pass the misaligned product must stay within 1.75 times the aligned one."""
     M, N, K = 4096, 512, 2048
     g = torch.Generator(device=DEV)
     g.manual_seed(5)
@@ -803,6 +849,13 @@ def test_two_byte_offset_operands_run_close_to_aligned_ones():
         return min(times)
 
     t_off = best(abuf[1:1 + M * K].view(M, K), bbuf[1:1 + K * N].view(K, N), c)
+    assert capi.lib().ntb_last_route() in (capi.ROUTE_TC_F16, capi.ROUTE_TC_F16_PAIR)
+    c4 = torch.zeros(M, N, device=DEV, dtype=torch.float16)
+    os.environ["NTB_REPACK"] = "0"
+    try:
+        t_ldg = best(abuf[1:1 + M * K].view(M, K), bbuf[1:1 + K * N].view(K, N), c4)
+    finally:
+        del os.environ["NTB_REPACK"]
     assert capi.lib().ntb_last_route() == capi.ROUTE_TC_F16
     # the same values from aligned storage
     a_al = abuf[1:1 + M * K].clone().view(M, K)
@@ -816,8 +869,10 @@ def test_two_byte_offset_operands_run_close_to_aligned_ones():
         t_ffma = best(abuf[1:1 + M * K].view(M, K), bbuf[1:1 + K * N].view(K, N), c3)
     finally:
         capi.lib().ntb_set_route(0)
-    print("two-byte offset %.1f us, aligned %.1f us (ratio %.2f), FFMA kernel %.1f us" %
-          (t_off * 1e3, t_al * 1e3, t_off / t_al, t_ffma * 1e3))
-    assert t_off <= 0.5 * t_ffma
-    assert t_off <= 6.0 * t_al
+    print("two-byte offset %.1f us, aligned %.1f us (ratio %.2f), loader warps alone %.1f us, FFMA kernel %.1f us" %
+          (t_off * 1e3, t_al * 1e3, t_off / t_al, t_ldg * 1e3, t_ffma * 1e3))
+    assert t_ldg <= 0.5 * t_ffma
+    assert t_ldg <= 6.0 * t_al
+    assert t_off <= 1.75 * t_al
+    assert rel_fro(c4.float().cpu().numpy(), c2.float().cpu().numpy()) <= 2e-3
     status_ok()
