@@ -425,6 +425,8 @@ int ntb_debug_inject(int devID, int skipKBlock, int waitLimitKiloCycles);
 #define NTB_PLAN_SPLIT_K4      (-4)
 #define NTB_PLAN_PAIR_256X128  (-8)
 #define NTB_PLAN_PAIR_512X128  (-9)
+#define NTB_PLAN_PAIRSPLIT_K2 (-18)   /* two CTA pairs share a 256 x 256 tile, half of K each */
+#define NTB_PLAN_PAIRSPLIT_K4 (-20)   /* four pairs per tile, a quarter of K each */
 int ntb_plan(int dtypeAB, int M, int N, int K, int count, int smCount);
 
 /* Products issued so far in this process through the kernel family `route` (NTB_ROUTE_*): shows,

@@ -25,6 +25,7 @@ from .capi import X_TRANS, X_NOTRANS
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 L2_BYTES = 126 * 1024 * 1024
+OFFSET_ELEMS = 0        # --offset-elems: operands start this many elements past a 16-byte boundary
 
 # name: (dtype, batch, M, N, K, transposedA, transposedB, alpha, beta, bound, note)
 CONFIGS = {
@@ -99,6 +100,15 @@ def make_set(cfg, dev, seed):
     a = torch.randn(a_shape, device=dev, generator=g).to(dtype)
     b = (torch.randn(b_shape, device=dev, generator=g) / math.sqrt(K)).to(dtype)
     c = torch.randn(lead + (M, N), device=dev, generator=g).to(dtype)
+    if OFFSET_ELEMS:
+        # the operands as a memory pool would hand them out: the same values, starting
+        # OFFSET_ELEMS elements past a 16-byte boundary (no tensor map can address them)
+        def shifted(x):
+            buf = torch.empty(x.numel() + 16, device=dev, dtype=dtype)
+            view = buf[OFFSET_ELEMS:OFFSET_ELEMS + x.numel()].view(x.shape)
+            view.copy_(x)
+            return view
+        a, b = shifted(a), shifted(b)
     return a, b, c
 
 
@@ -347,6 +357,9 @@ def main():
                     help="extra fp16 products M x N x K (a row-major, b stored N x K, beta 0), e.g. 4096x512x2048,2048x1024x4096")
     ap.add_argument("--f32-shapes", default="",
                     help="extra fp32 products M x N x K (a and b row-major, beta 0.5), e.g. 4096x4096x4096")
+    ap.add_argument("--offset-elems", type=int, default=0,
+                    help="place a and b this many elements past a 16-byte boundary, as a memory pool may "
+                         "(NTB_REPACK=0 then times the loader-warp kernel instead of the realigning pre-pass)")
     ap.add_argument("--accuracy", action="store_true", help="fp32 routes against float64 instead of timings")
     args = ap.parse_args()
     if not torch.cuda.is_available():
@@ -356,6 +369,8 @@ def main():
     if args.accuracy:
         run_accuracy(dev)
         return 0
+    global OFFSET_ELEMS
+    OFFSET_ELEMS = max(0, min(15, args.offset_elems))
     names = [n for n in args.configs.split(",") if n]
     for shape in [x for x in args.shapes.split(",") if x]:
         M, N, K = (int(v) for v in shape.lower().split("x"))

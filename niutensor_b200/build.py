@@ -17,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ_DIR = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libntb_gemm.so")
-SOURCES = ["ntb_api.cu", "ntb_tc.cu", "ntb_tc_pair.cu", "ntb_tc_split.cu", "ntb_tc_f32pair.cu", "ntb_tc_ldg.cu", "ntb_repack.cu",
+SOURCES = ["ntb_api.cu", "ntb_tc.cu", "ntb_tc_pair.cu", "ntb_tc_split.cu", "ntb_tc_pairsplit.cu", "ntb_tc_f32pair.cu", "ntb_tc_ldg.cu", "ntb_repack.cu",
            "ntb_simt.cu", "ntb_noalloc.cu", "ntb_attn.cu", "ntb_logsoftmax.cu", "ntb_sharded.cu", "ntb_grouped.cu"]
 HEADERS = [os.path.join(CSRC, "ntb_internal.h"), os.path.join(CSRC, "ntb_ptx.cuh"),
            os.path.join(CSRC, "ntb_tc_common.cuh"), os.path.join(CSRC, "ntb_tc_single.cuh"),

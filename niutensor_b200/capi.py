@@ -16,6 +16,7 @@ ROUTE_NONE, ROUTE_TC_F16, ROUTE_TC_3XTF32, ROUTE_SIMT, ROUTE_TC_F16_PAIR, ROUTE_
 OK, ERR_ARG, ERR_SHAPE, ERR_DTYPE, ERR_CUDA, ERR_DEVICE_WAIT, ERR_LIMIT = range(7)
 MAX_PEERS = 8
 PLAN_PAIR_256X256, PLAN_PAIR_512X256, PLAN_SPLIT_K2, PLAN_SPLIT_K4, PLAN_PAIR_256X128, PLAN_PAIR_512X128 = 0, -1, -2, -4, -8, -9
+PLAN_PAIRSPLIT_K2, PLAN_PAIRSPLIT_K4 = -18, -20
 NOALLOC_MAX_BYTES = 16 << 20
 ACT_NONE, ACT_RECTIFY = 0, 1
 SHARD_COLUMNS, SHARD_BATCH = 0, 1

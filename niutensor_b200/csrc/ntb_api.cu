@@ -181,7 +181,7 @@ DeviceCtx * CtxFor(int dev)
 int EnsureScratch(const DeviceCtx & ctx, int slot, size_t bytes, void ** out)
 {
     DeviceCtx * c = ctx.mayAllocate ? GetCtx(ctx.devID) : nullptr;
-    if (!c || slot < 0 || slot >= 3)
+    if (!c || slot < 0 || slot >= 4)
         return NTB_ERR_CUDA;
     std::lock_guard<std::mutex> g(gLock);
     if (c->scratchBytes[slot] < bytes) {
@@ -203,6 +203,32 @@ int EnsureScratch(const DeviceCtx & ctx, int slot, size_t bytes, void ** out)
         c->scratchBytes[slot] = want;
     }
     *out = c->scratch[slot];
+    return NTB_OK;
+}
+
+int EnsureCounted(const DeviceCtx & ctx, size_t workBytes, size_t flagBytes, cudaStream_t stream, float ** work, int ** flags)
+{
+    /* the counter area has one fixed size, so that its end does not move with the problem */
+    const size_t flagArea = 64 * 1024;
+    if (flagBytes > flagArea)
+        return NTB_ERR_LIMIT;
+    void * base = nullptr;
+    const int rc = EnsureScratch(ctx, 3, flagArea + workBytes, &base);
+    if (rc != NTB_OK)
+        return rc;
+    DeviceCtx * c = GetCtx(ctx.devID);
+    {
+        std::lock_guard<std::mutex> g(gLock);
+        if (c->countersCleared != base) {
+            if (cudaMemsetAsync(base, 0, flagArea, stream) != cudaSuccess) {
+                cudaGetLastError();
+                return NTB_ERR_CUDA;
+            }
+            c->countersCleared = base;
+        }
+    }
+    *flags = (int *)base;
+    *work = (float *)((char *)base + flagArea);
     return NTB_OK;
 }
 
@@ -790,8 +816,11 @@ int ntb_device_status(int devID)
         cudaGetLastError();
         return NTB_ERR_CUDA;
     }
-    if (v != 0)
+    if (v != 0) {
         cudaMemset(ctx->status, 0, sizeof(int));
+        std::lock_guard<std::mutex> g(gLock);
+        ctx->countersCleared = nullptr;     /* counters of an abandoned launch may be left non-zero */
+    }
     return v;
 }
 
@@ -843,7 +872,7 @@ void ntb_release(void)
                     cudaEventDestroy(c->evOut[i]);
                 }
             }
-            for (int s = 0; s < 3; s++)
+            for (int s = 0; s < 4; s++)
                 if (c->scratch[s])
                     cudaFree(c->scratch[s]);
             if (c->haveScratchEvent)

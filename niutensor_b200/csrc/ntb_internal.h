@@ -52,8 +52,9 @@ struct DeviceCtx {
     /* fp32-as-two-halves route: planes of a and b, scale vectors; shared by the calls on this
        device, which are ordered on the device through scratchEvent */
     bool mayAllocate;       /* false for the context of the entry point that must not allocate */
-    void * scratch[3];
-    size_t scratchBytes[3];
+    void * scratch[4];         /* 0-2: operand planes and vectors of the pre-passes; 3: partial sums of the split on CTA pairs */
+    size_t scratchBytes[4];
+    void * countersCleared;    /* the slot-3 buffer whose counters have been zeroed */
     cudaEvent_t scratchEvent;
     bool haveScratchEvent;
 };
@@ -117,6 +118,10 @@ DeviceCtx * CtxFor(int dev);
    needed, after the device has finished with the old one); the device is current */
 int EnsureScratch(const DeviceCtx & ctx, int slot, size_t bytes, void ** out);
 /* orders this stream behind the last use of the device's scratch / marks a new last use */
+/* scratch slot 3 as flagBytes of zeroed counters followed by workBytes of workspace; the counters
+   are cleared on the stream when the buffer is new or after a device wait ran out (kernels
+   leave them at zero otherwise) */
+int EnsureCounted(const DeviceCtx & ctx, size_t workBytes, size_t flagBytes, cudaStream_t stream, float ** work, int ** flags);
 int ScratchAcquire(const DeviceCtx & ctx, cudaStream_t stream);
 int ScratchRelease(const DeviceCtx & ctx, cudaStream_t stream);
 /* tensor maps of an operand and of the output (ntb_tc.cu) */

@@ -170,7 +170,8 @@ int EncodeOutput(CUtensorMap * map, int dtC, void * base, int rows, int cols, lo
  *     bound by this at half the MMA rate).
  * Returns the tile width of the single-CTA kernel; 0 / -1 for the CTA-pair kernel with
  * 256 x 256 / 512 x 256 tiles, -8 / -9 for pair tiles of 256 x 128 / 512 x 128; -2 / -4 for
- * the split-K kernel with clusters of 2 / 4 CTAs. Constants were fitted to timings of the
+ * the split-K kernel with clusters of 2 / 4 CTAs; -18 / -20 for split-K on CTA pairs (2 / 4
+ * pairs per 256 x 256 tile). Constants were fitted to timings of the
  * benchmark configurations and of mid-size products on a B200.
  */
 struct KbCost {
@@ -187,7 +188,7 @@ double PerKBlock(const KbCost & c, long long activeCtas)
     return fmax(fmax(c.math, smem), fmax(c.bytes / ingest, thread));
 }
 
-int PickBN(const Problem & p, int smCount, int mode)
+int PickBN(const Problem & p, int smCount, int mode, bool allowPairSplit = true)
 {
     const int es = mode == 0 ? 2 : 4;
     const int kElems = ROW_BYTES / es;
@@ -254,6 +255,30 @@ int PickBN(const Problem & p, int smCount, int mode)
             const double perK = PerKBlock(c, sp * (tiles < clusters ? tiles : clusters));
             const double cost = (double)waves * (ceil(kBlocks / sp) * perK + 2012.0 + 2500.0) + 2000.0;
             if (cost < bestCost) { bestCost = cost; best = -sp; }
+        }
+    }
+    if (mode == 0 && smCount >= 8 && allowPairSplit) {
+        /* split-K on CTA pairs: S pairs share a 256 x 256 tile and a 1/S part of K each; the
+           pair tile moves half the operand bytes per flop of the 128 x 128 split above */
+        for (int sp = 2; sp <= 4; sp *= 2) {
+            if (kBlocks < 8.0 * sp || smCount < 2 * sp)
+                continue;
+            const long long tiles = (long long)((p.M + 255) / 256) * ((p.N + 255) / 256) * p.count;
+            /* the pairs of a tile wait for one another: one wave only */
+            const long long clusters = (long long)(smCount / 2) / sp;
+            if (clusters < 1 || tiles > clusters)
+                continue;
+            const long long waves = 1;
+            KbCost c;
+            c.math = 512.0;
+            c.bytes = (double)(BM + 128) * ROW_BYTES;
+            c.reads = c.bytes;
+            c.mmas = 4.0;
+            c.shake = 500.0;
+            c.g = 1;
+            const double perK = PerKBlock(c, 2 * sp * (tiles < clusters ? tiles : clusters));
+            const double cost = (double)waves * (ceil(kBlocks / sp) * perK + 2524.0 + 1500.0 + 6.0 * (256 / sp)) + 2500.0;
+            if (cost < bestCost) { bestCost = cost; best = -16 - sp; }
         }
     }
     return best;
@@ -326,6 +351,8 @@ int Prepare(const DeviceCtx & ctx, const Problem & p, int mode, int bn, bool pai
         tp.peers[i] = i < p.nPeers ? p.peers[i] : nullptr;
     tp.status = ctx.status;
     tp.skipKBlock = InjectedSkipKBlock();
+    tp.psWork = nullptr;
+    tp.psFlags = nullptr;
     tp.pfDist = Tune().pfDist;
     tp.group = Tune().group;
     if (tp.group < 1)
@@ -452,7 +479,12 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
             *route = NTB_ROUTE_TC_F16X2;
         return rc;
     }
-    int bn = PickBN(p, ctx.smCount, mode);
+    /* split-K on CTA pairs is chosen by the model only when nothing restricts the choice
+       (NTB_PAIR_SPLIT: 0 never, 2 / 4 force that many pairs per tile) */
+    const int knobPS = Knob("NTB_PAIR_SPLIT", -1);
+    const bool modelMayPairSplit = forced == 0 && knobPS != 0 && Knob("NTB_BN", 0) == 0 && Knob("NTB_SPLIT_K", -1) < 0 &&
+                                   Knob("NTB_PAIR_BN", 0) == 0 && Knob("NTB_PAIR_MSUB", 0) == 0;
+    int bn = PickBN(p, ctx.smCount, mode, modelMayPairSplit);
     const int knobBN = Knob("NTB_BN", 0);           /* tuning: force the single-CTA tile width */
     if (knobBN == 64 || knobBN == 128 || (knobBN == 256 && mode == 0))
         bn = knobBN;
@@ -475,6 +507,39 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
         bn -= 8;
     if (knobPairBN == 256 && (bn == -8 || bn == -9))
         bn += 8;
+    {
+        int pairSplit = bn == -18 ? 2 : bn == -20 ? 4 : 0;
+        const long long tiles256 = (long long)((p.M + 255) / 256) * ((p.N + 255) / 256) * p.count;
+        if (mode == 0 && (knobPS == 2 || knobPS == 4) && (p.K + 63) / 64 >= 2 * knobPS && tiles256 * knobPS <= ctx.smCount / 2 &&
+            ctx.mayAllocate && (forced == 0 || forced == NTB_ROUTE_TC_F16_PAIR))
+            pairSplit = knobPS;
+        if (pairSplit) {
+            TcParams tp;
+            CUtensorMap maps[3];
+            int rc = Prepare(ctx, p, mode, 256, true, 1, tp, maps);
+            if (rc != NTB_OK)
+                return rc;
+            if (p.nPeers > 0 && !tp.cTma)
+                return NTB_ERR_ARG;
+            /* every pair of a tile waits for the others: all of them must be resident at once */
+            if ((long long)tp.totalTiles * pairSplit > ctx.smCount / 2 || !ctx.mayAllocate)
+                return NTB_ERR_ARG;
+            const size_t workBytes = (size_t)tp.totalTiles * pairSplit * (pairSplit - 1) * 2 * 128 * (256 / pairSplit) * sizeof(float);
+            const size_t flagBytes = (size_t)tp.totalTiles * pairSplit * 2 * 4 * sizeof(int);
+            rc = ScratchAcquire(ctx, stream);
+            if (rc == NTB_OK)
+                rc = EnsureCounted(ctx, workBytes, flagBytes, stream, &tp.psWork, &tp.psFlags);
+            if (rc != NTB_OK)
+                return rc;
+            *route = NTB_ROUTE_TC_F16_PAIR;
+            if (Tune().debugChoice)
+                fprintf(stderr, "ntb: M %d N %d K %d count %d -> %d pairs per 256 x 256 tile, split along K\n",
+                        p.M, p.N, p.K, p.count, pairSplit);
+            rc = LaunchPairSplitKernel(pairSplit, p.dtC == NTB_X_FLOAT16, tp.beta != 0.f || tp.nPeers > 0, maps, tp, stream);
+            const int rel = ScratchRelease(ctx, stream);
+            return rc != NTB_OK ? rc : rel;
+        }
+    }
     int split = (bn == -2 || bn == -4) ? -bn : 0;
     if (split == 4 && p.nPeers > 0 && p.dtC == NTB_X_FLOAT16)
         split = 2;                                  /* the 4-way split of a half tile stores directly */

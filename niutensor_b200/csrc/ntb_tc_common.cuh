@@ -59,6 +59,9 @@ struct TcParams {
     const void * b;
     long long lda, ldb, sAp, sAq, sBp, sBq;   /* elements */
     int skipKBlock;         /* test hook: the producer arms this k-block of its first tile but never loads it; -1 off */
+    /* split-K on CTA pairs: workspace for the partial sums and its arrival counters */
+    float * psWork;
+    int * psFlags;
 };
 
 
@@ -73,6 +76,8 @@ int LaunchPairKernel(int msub, int bn, int g, int epiWarps, bool half, bool oldc
                      const PeerMaps * peerMaps, int pairs, cudaStream_t stream);
 int LaunchSplitKernel(int split, int g, bool half, bool oldc, const CUtensorMap * maps, const TcParams & tp,
                       int clusters, cudaStream_t stream);
+/* split-K on CTA pairs (ntb_tc_pairsplit.cu): tp and maps as for the pair kernel's 256 x 256 tile */
+int LaunchPairSplitKernel(int split, bool half, bool oldc, const CUtensorMap * maps, const TcParams & tp, cudaStream_t stream);
 
 namespace {
 

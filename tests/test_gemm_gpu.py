@@ -286,6 +286,73 @@ def test_single_cta_tile_widths_and_hand_shake_groups(bn, group, oracle):
     status_ok()
 
 
+@pytest.mark.parametrize("pairs", ["2", "4"])
+def test_split_k_on_cta_pairs(pairs, oracle):
+    """Clusters of 2 / 4 CTA pairs share one 256 x 256 tile, every pair running the pair
+    kernel's main loop over its part of K; partial sums are exchanged through distributed
+    shared memory and every pair finishes a column slice. Forced here on shapes with ragged
+    edges, a K that does not divide evenly, several tiles, batches, every transposition,
+    alpha/beta and fp32 output; results must not depend on the run."""
+    rng = np.random.default_rng(640 + int(pairs))
+    L = capi.lib()
+    os.environ["NTB_PAIR_SPLIT"] = pairs
+    try:
+        shapes = [(256, 256, 1024), (200, 136, 1032), (72, 520, 576), (512, 256, 4096), (304, 296, 2112)]
+        n = 0
+        for tA in (X_TRANS, X_NOTRANS):
+            for tB in (X_TRANS, X_NOTRANS):
+                for (M, N, K) in shapes:
+                    alpha, beta = AB[n % len(AB)]
+                    n += 1
+                    cnt = 1 + n % 2
+                    a = round_to_half(stored(rng, (cnt,), M, K, tA))
+                    b = round_to_half(stored(rng, (cnt,), K, N, tB))
+                    c0 = round_to_half(rng.normal(size=(cnt, M, N)).astype(np.float32))
+                    out_dtype = torch.float32 if n % 3 == 0 else torch.float16
+                    c = to_dev(c0, out_dtype)
+                    before = L.ntb_launch_count()
+                    ops._MatrixMulBatched(to_dev(a, torch.float16), tA, to_dev(b, torch.float16), tB, c, alpha, beta)
+                    assert L.ntb_launch_count() == before + 1
+                    assert L.ntb_last_route() == capi.ROUTE_TC_F16_PAIR
+                    err = rel_fro(c.float().cpu().numpy(), oracle.matmul_batched(a, tA, b, tB, alpha, beta, c0))
+                    assert err <= 2e-3, (M, N, K, tA, tB, alpha, beta, err)
+                    again = to_dev(c0, out_dtype)
+                    ops._MatrixMulBatched(to_dev(a, torch.float16), tA, to_dev(b, torch.float16), tB, again, alpha, beta)
+                    assert torch.equal(again, c)
+    finally:
+        os.environ.pop("NTB_PAIR_SPLIT", None)
+    status_ok()
+
+
+def test_pair_split_is_chosen_for_few_tiles_with_long_k(oracle):
+    """The second FFN product (4096 x 512 x 2048) and a weight-gradient shape: the cost model
+    takes the split on CTA pairs by itself; sampled rows against the oracle, checksums over
+    every tile."""
+    L = capi.lib()
+    g = torch.Generator(device=DEV)
+    g.manual_seed(31)
+    for (M, N, K, tA) in [(4096, 512, 2048, X_NOTRANS), (1024, 512, 4096, X_TRANS), (1024, 1024, 8192, X_NOTRANS)]:
+        assert L.ntb_plan(capi.X_FLOAT16, M, N, K, 1, 148) in (capi.PLAN_PAIRSPLIT_K2, capi.PLAN_PAIRSPLIT_K4)
+        a = (torch.rand((K, M) if tA == X_TRANS else (M, K), device=DEV, generator=g) * 2 - 1).half()
+        b = (torch.rand(K, N, device=DEV, generator=g) * 2 - 1).half()
+        c0 = torch.randn(M, N, device=DEV, generator=g).half()
+        c = c0.clone()
+        ops._MatrixMul2D(a, tA, b, X_NOTRANS, c, 0.125, 0.5)
+        assert L.ntb_last_route() == capi.ROUTE_TC_F16_PAIR
+        rows = np.arange(0, M, max(1, M // 30))[:32]
+        a_rows = a[:, rows] if tA == X_TRANS else a[rows]
+        want = oracle.matmul2d(np.ascontiguousarray(a_rows.float().cpu().numpy()), tA, b.float().cpu().numpy(), X_NOTRANS,
+                               0.125, 0.5, c0[rows].float().cpu().numpy())
+        assert rel_fro(c[rows].float().cpu().numpy(), want) <= 2e-3
+        ad = (a.t() if tA == X_TRANS else a).double()
+        bd, c0d, cd = b.double(), c0.double(), c.double()
+        row_want = 0.125 * (ad @ bd.sum(1)) + 0.5 * c0d.sum(1)
+        col_want = 0.125 * (ad.sum(0) @ bd) + 0.5 * c0d.sum(0)
+        assert float((cd.sum(1) - row_want).norm() / row_want.norm()) <= 5e-4
+        assert float((cd.sum(0) - col_want).norm() / col_want.norm()) <= 5e-4
+    status_ok()
+
+
 @pytest.mark.parametrize("split", ["2", "2/1", "4"])
 def test_split_k_cluster_route(split, oracle):
     """Clusters of 2 / 4 CTAs share a tile and a part of K each and exchange partial sums
