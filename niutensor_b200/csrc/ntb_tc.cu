@@ -261,7 +261,10 @@ int PickBN(const Problem & p, int smCount, int mode, bool allowPairSplit = true)
         /* split-K on CTA pairs: S pairs share a 256 x 256 tile and a 1/S part of K each; the
            pair tile moves half the operand bytes per flop of the 128 x 128 split above */
         for (int sp = 2; sp <= 4; sp *= 2) {
-            if (kBlocks < 8.0 * sp || smCount < 2 * sp)
+            /* measured: the exchange of the partial sums costs 7 (two pairs) to 11 us (four),
+               which pays from K = 4096 on (4096 x 512 x 8192: 44 -> 35 us, 1024 x 1024 x 8192:
+               30 -> 26, 512 x 2048 x 4096: 19.4 -> 16.5) and not at K = 2048 (14.2 -> 15.3) */
+            if (kBlocks < 64.0 || kBlocks < 8.0 * sp || smCount < 2 * sp)
                 continue;
             const long long tiles = (long long)((p.M + 255) / 256) * ((p.N + 255) / 256) * p.count;
             /* the pairs of a tile wait for one another: one wave only */
@@ -277,7 +280,7 @@ int PickBN(const Problem & p, int smCount, int mode, bool allowPairSplit = true)
             c.shake = 500.0;
             c.g = 1;
             const double perK = PerKBlock(c, 2 * sp * (tiles < clusters ? tiles : clusters));
-            const double cost = (double)waves * (ceil(kBlocks / sp) * perK + 2524.0 + 1500.0 + 6.0 * (256 / sp)) + 2500.0;
+            const double cost = (double)waves * (ceil(kBlocks / sp) * perK * 1.25 + (sp == 2 ? 5000.0 : 9000.0)) + 2500.0;
             if (cost < bestCost) { bestCost = cost; best = -16 - sp; }
         }
     }
@@ -535,7 +538,8 @@ int LaunchTc(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream, int 
             if (Tune().debugChoice)
                 fprintf(stderr, "ntb: M %d N %d K %d count %d -> %d pairs per 256 x 256 tile, split along K\n",
                         p.M, p.N, p.K, p.count, pairSplit);
-            rc = LaunchPairSplitKernel(pairSplit, p.dtC == NTB_X_FLOAT16, tp.beta != 0.f || tp.nPeers > 0, maps, tp, stream);
+            rc = LaunchPairSplitKernel(pairSplit, Knob("NTB_PAIR_SPLIT_G", 2) == 1 ? 1 : 2, p.dtC == NTB_X_FLOAT16, tp.beta != 0.f || tp.nPeers > 0, maps, tp,
+                                       stream);
             const int rel = ScratchRelease(ctx, stream);
             return rc != NTB_OK ? rc : rel;
         }

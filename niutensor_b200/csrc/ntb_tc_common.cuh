@@ -77,7 +77,7 @@ int LaunchPairKernel(int msub, int bn, int g, int epiWarps, bool half, bool oldc
 int LaunchSplitKernel(int split, int g, bool half, bool oldc, const CUtensorMap * maps, const TcParams & tp,
                       int clusters, cudaStream_t stream);
 /* split-K on CTA pairs (ntb_tc_pairsplit.cu): tp and maps as for the pair kernel's 256 x 256 tile */
-int LaunchPairSplitKernel(int split, bool half, bool oldc, const CUtensorMap * maps, const TcParams & tp, cudaStream_t stream);
+int LaunchPairSplitKernel(int split, int g, bool half, bool oldc, const CUtensorMap * maps, const TcParams & tp, cudaStream_t stream);
 
 namespace {
 

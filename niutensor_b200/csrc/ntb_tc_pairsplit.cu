@@ -66,7 +66,7 @@ __device__ __forceinline__ void BulkLoad(uint32_t dst, const void * src, uint32_
  * idle (every load that was issued has been consumed): its first 32 KB become the epilogue's
  * staging boxes, the next 4 x (S - 1) x 32 x W x 4 bytes the landing area of the pieces.
  */
-template <int S, int STAGES, typename OutT, bool OLDC>
+template <int S, int STAGES, int G, typename OutT, bool OLDC>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 GemmTcPairSplitKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const __grid_constant__ CUtensorMap tmC, TcParams p)
@@ -80,7 +80,9 @@ GemmTcPairSplitKernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     constexpr int KSTEPS = ROW_BYTES / UMMA_K_BYTES;
     constexpr int PIECE_BYTES = 32 * W * 4;             /* one warp's rows of one sender's slice */
     constexpr int PIECE_V4 = PIECE_BYTES / 16;
+    constexpr int NSTG = STAGES / G;                    /* barrier pairs: G k-blocks share a hand-shake */
     static_assert(S == 2 || S == 4, "pairs per tile");
+    static_assert(STAGES % G == 0, "k-blocks per hand-shake");
     static_assert(STAGES * STAGE_BYTES >= EPI_BYTES + 4 * (S - 1) * PIECE_BYTES, "staging boxes and landing area live in the idle ring");
 
     extern __shared__ uint8_t smemRaw[];
@@ -117,7 +119,7 @@ GemmTcPairSplitKernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         asm volatile("" :: "r"(touch));
     }
     if (warp == 0) {
-        if (lane < STAGES) {
+        if (lane < NSTG) {
             MbarInit(SmemAddr(&barFull[lane]), 1);
             MbarInit(SmemAddr(&barEmpty[lane]), 1);
         }
@@ -158,32 +160,38 @@ GemmTcPairSplitKernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             const int ba = BatchCoord(p.aSel, tc.prob, p);
             const int bb = BatchCoord(p.bSel, tc.prob, p);
             const bool aMN = p.aMN != 0, bMN = p.bMN != 0;
-            for (int kb = kbLo; kb < kbHi; kb++) {
+            for (int kb = kbLo; kb < kbHi; kb += G) {
                 if (!MbarWait(SmemAddr(&barEmpty[s]), ph ^ 1u, abortPtr, p.status))
                     break;
                 const uint32_t fullLeader = MapToCta(SmemAddr(&barFull[s]), 0);
+                const int nb = kbHi - kb < G ? kbHi - kb : G;
                 if (rank == 0)
-                    MbarExpectTx(SmemAddr(&barFull[s]), 2u * STAGE_BYTES);
-                const uint32_t aDst = smemBase + (uint32_t)s * STAGE_BYTES;
-                const uint32_t bDst = aDst + A_TILE_BYTES;
-                const int k0 = kb * EPR;
-                if (!aMN) {
-                    TmaLoad3DPair(aDst, &tmA, fullLeader, k0, m0, ba);
-                }
-                else {
+                    MbarExpectTx(SmemAddr(&barFull[s]), (uint32_t)nb * 2u * STAGE_BYTES);
 #pragma unroll
-                    for (int i = 0; i < BM / EPR; i++)
-                        TmaLoad3DPair(aDst + i * EPR * ROW_BYTES, &tmA, fullLeader, m0 + i * EPR, k0, ba);
-                }
-                if (!bMN) {
-                    TmaLoad3DPair(bDst, &tmB, fullLeader, k0, n0, bb);
-                }
-                else {
+                for (int j = 0; j < G; j++) {
+                    if (j < nb) {
+                        const uint32_t aDst = smemBase + (uint32_t)(s * G + j) * STAGE_BYTES;
+                        const uint32_t bDst = aDst + A_TILE_BYTES;
+                        const int k0 = (kb + j) * EPR;
+                        if (!aMN) {
+                            TmaLoad3DPair(aDst, &tmA, fullLeader, k0, m0, ba);
+                        }
+                        else {
 #pragma unroll
-                    for (int i = 0; i < BNH / EPR; i++)
-                        TmaLoad3DPair(bDst + i * EPR * ROW_BYTES, &tmB, fullLeader, n0 + i * EPR, k0, bb);
+                            for (int i = 0; i < BM / EPR; i++)
+                                TmaLoad3DPair(aDst + i * EPR * ROW_BYTES, &tmA, fullLeader, m0 + i * EPR, k0, ba);
+                        }
+                        if (!bMN) {
+                            TmaLoad3DPair(bDst, &tmB, fullLeader, k0, n0, bb);
+                        }
+                        else {
+#pragma unroll
+                            for (int i = 0; i < BNH / EPR; i++)
+                                TmaLoad3DPair(bDst + i * EPR * ROW_BYTES, &tmB, fullLeader, n0 + i * EPR, k0, bb);
+                        }
+                    }
                 }
-                if (++s == STAGES) { s = 0; ph ^= 1u; }
+                if (++s == NSTG) { s = 0; ph ^= 1u; }
             }
         }
     }
@@ -201,22 +209,28 @@ GemmTcPairSplitKernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             int s = 0;
             uint32_t ph = 0, acc = 0u;
             bool ok = true;
-            for (int kb = kbLo; kb < kbHi; kb++) {
+            for (int kb = kbLo; kb < kbHi; kb += G) {
                 ok = MbarWait(SmemAddr(&barFull[s]), ph, abortPtr, p.status);
                 if (!ok)
                     break;
                 TcFenceAfter();
-                uint32_t aLo = aLo0 + (uint32_t)s * (STAGE_BYTES >> 4);
-                uint32_t bLo = bLo0 + (uint32_t)s * (STAGE_BYTES >> 4);
+                const int nb = kbHi - kb < G ? kbHi - kb : G;
 #pragma unroll
-                for (int k = 0; k < KSTEPS; k++) {
-                    TcMmaPairLH(tmemBase, aLo, aHiW, bLo, bHiW, iDesc, acc);
-                    acc = 1u;
-                    aLo += aStep4;
-                    bLo += bStep4;
+                for (int j = 0; j < G; j++) {
+                    if (j < nb) {
+                        uint32_t aLo = aLo0 + (uint32_t)(s * G + j) * (STAGE_BYTES >> 4);
+                        uint32_t bLo = bLo0 + (uint32_t)(s * G + j) * (STAGE_BYTES >> 4);
+#pragma unroll
+                        for (int k = 0; k < KSTEPS; k++) {
+                            TcMmaPairLH(tmemBase, aLo, aHiW, bLo, bHiW, iDesc, acc);
+                            acc = 1u;
+                            aLo += aStep4;
+                            bLo += bStep4;
+                        }
+                    }
                 }
                 TcCommitPair(SmemAddr(&barEmpty[s]));
-                if (++s == STAGES) { s = 0; ph ^= 1u; }
+                if (++s == NSTG) { s = 0; ph ^= 1u; }
             }
             if (ok)
                 TcCommitPair(SmemAddr(&barTFull));
@@ -324,11 +338,11 @@ GemmTcPairSplitKernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     }
 }
 
-template <int S, int STAGES, typename OutT, bool OLDC>
+template <int S, int STAGES, int G, typename OutT, bool OLDC>
 int LaunchPairSplit(const CUtensorMap & tmA, const CUtensorMap & tmB, const CUtensorMap & tmC, const TcParams & tp, cudaStream_t stream)
 {
     constexpr int smem = (A_TILE_BYTES + 128 * ROW_BYTES) * STAGES + 1024;
-    auto kern = GemmTcPairSplitKernel<S, STAGES, OutT, OLDC>;
+    auto kern = GemmTcPairSplitKernel<S, STAGES, G, OutT, OLDC>;
     static SmemOptIn optIn;
     if (!optIn.Ensure((const void *)kern, smem))
         return NTB_ERR_CUDA;
@@ -341,12 +355,14 @@ int LaunchPairSplit(const CUtensorMap & tmA, const CUtensorMap & tmB, const CUte
 
 /* tp and maps as for the CTA-pair kernel with a 256 x 256 tile (one 128-row sub-tile per CTA);
    tp.psWork / tp.psFlags: workspace of PairSplitWorkBytes / cleared counters of PairSplitFlagBytes */
-int LaunchPairSplitKernel(int split, bool half, bool oldc, const CUtensorMap * maps, const TcParams & tp, cudaStream_t stream)
+int LaunchPairSplitKernel(int split, int g, bool half, bool oldc, const CUtensorMap * maps, const TcParams & tp, cudaStream_t stream)
 {
     if (tp.totalTiles <= 0 || tp.totalTiles > (1 << 20))
         return NTB_ERR_LIMIT;
-#define NTB_PSPLIT(SS, ST, T) (oldc ? LaunchPairSplit<SS, ST, T, true>(maps[0], maps[1], maps[2], tp, stream) \
-                                    : LaunchPairSplit<SS, ST, T, false>(maps[0], maps[1], maps[2], tp, stream))
+#define NTB_PSPLIT(SS, ST, T) (g == 1 ? (oldc ? LaunchPairSplit<SS, ST, 1, T, true>(maps[0], maps[1], maps[2], tp, stream)   \
+                                             : LaunchPairSplit<SS, ST, 1, T, false>(maps[0], maps[1], maps[2], tp, stream)) \
+                                     : (oldc ? LaunchPairSplit<SS, ST, 2, T, true>(maps[0], maps[1], maps[2], tp, stream)   \
+                                             : LaunchPairSplit<SS, ST, 2, T, false>(maps[0], maps[1], maps[2], tp, stream)))
     if (!tp.psWork || !tp.psFlags)
         return NTB_ERR_ARG;
     if (split == 2)

@@ -152,12 +152,13 @@ def test_tile_cost_model_choices_for_the_benchmark_configurations():
     f16, f32 = capi.X_FLOAT16, capi.X_FLOAT
     assert L.ntb_plan(f16, 8192, 8192, 8192, 1, 148) == capi.PLAN_PAIR_512X256     # config 5
     assert L.ntb_plan(f16, 4096, 2048, 512, 1, 148) == capi.PLAN_PAIR_256X256      # config 2a
-    assert L.ntb_plan(f16, 4096, 512, 2048, 1, 148) == capi.PLAN_PAIRSPLIT_K2      # config 2b: 32 tiles of 256 x 256, two pairs each
+    assert L.ntb_plan(f16, 4096, 512, 2048, 1, 148) == capi.PLAN_PAIR_256X128      # config 2b: 128 CTAs, less B traffic
     assert L.ntb_plan(f16, 256, 65536, 512, 1, 148) in (capi.PLAN_PAIR_256X256, capi.PLAN_PAIR_512X256)   # config 4
     assert L.ntb_plan(f16, 256, 64, 256, 64, 148) == 64                            # config 3b: one tile per m-block
     assert L.ntb_plan(f16, 256, 256, 64, 64, 148) in (128, 256)                    # config 3a
-    assert L.ntb_plan(f16, 1024, 512, 4096, 1, 148) in (capi.PLAN_PAIRSPLIT_K2, capi.PLAN_PAIRSPLIT_K4)   # weight gradient
-    assert L.ntb_plan(f16, 256, 256, 4096, 1, 148) in (capi.PLAN_SPLIT_K2, capi.PLAN_SPLIT_K4)   # one 256 x 256 tile: the 128 x 128 split uses more SMs
+    assert L.ntb_plan(f16, 1024, 512, 4096, 1, 148) in (capi.PLAN_SPLIT_K2, capi.PLAN_SPLIT_K4)   # weight gradient
+    assert L.ntb_plan(f16, 4096, 512, 8192, 1, 148) == capi.PLAN_PAIRSPLIT_K2      # 32 tiles of 256 x 256 with a long K: two pairs each
+    assert L.ntb_plan(f16, 1024, 1024, 8192, 1, 148) == capi.PLAN_PAIRSPLIT_K4     # weight gradient over 8192 tokens: four pairs per tile
     assert L.ntb_plan(f32, 512, 512, 512, 1, 148) in (64, 128)                     # config 1: no cluster kernel for fp32
     assert L.ntb_plan(f32, 8192, 8192, 8192, 1, 148) == 128
     assert L.ntb_plan(f16, 8192, 8192, 8192, 1, 1) > 0                             # one SM: no pairs, no clusters

@@ -325,13 +325,13 @@ def test_split_k_on_cta_pairs(pairs, oracle):
 
 
 def test_pair_split_is_chosen_for_few_tiles_with_long_k(oracle):
-    """The second FFN product (4096 x 512 x 2048) and a weight-gradient shape: the cost model
-    takes the split on CTA pairs by itself; sampled rows against the oracle, checksums over
-    every tile."""
+    """Few 256 x 256 tiles with K of 4096 and more (an FFN product over a long inner size, weight
+    gradients over 8192 tokens): the cost model takes the split on CTA pairs by itself;
+    sampled rows against the oracle, checksums over every tile."""
     L = capi.lib()
     g = torch.Generator(device=DEV)
     g.manual_seed(31)
-    for (M, N, K, tA) in [(4096, 512, 2048, X_NOTRANS), (1024, 512, 4096, X_TRANS), (1024, 1024, 8192, X_NOTRANS)]:
+    for (M, N, K, tA) in [(4096, 512, 8192, X_NOTRANS), (1024, 1024, 8192, X_TRANS), (512, 2048, 4096, X_NOTRANS)]:
         assert L.ntb_plan(capi.X_FLOAT16, M, N, K, 1, 148) in (capi.PLAN_PAIRSPLIT_K2, capi.PLAN_PAIRSPLIT_K4)
         a = (torch.rand((K, M) if tA == X_TRANS else (M, K), device=DEV, generator=g) * 2 - 1).half()
         b = (torch.rand(K, N, device=DEV, generator=g) * 2 - 1).half()
