@@ -9,7 +9,9 @@ no transposition -- ONE product of fixed size at every N ("strong" scaling). Wit
 is N-sharded: A is replicated, rank r owns columns [r * 8192 / N, (r + 1) * 8192 / N) of B,
 C0 and C, and the whole C is gathered onto every rank inside the timed region: the
 epilogue of each rank's product writes its tiles into every rank's copy of C over NVLink
-(symmetric memory; `ntb_gemm_peers`). One step = that product; `value` = 2 * 8192^3 flop
+(symmetric memory): with one multicast store per 128-byte line where an NVLink multicast
+object can be bound (`ntb_gemm_multicast`), else, or with `--gather peers`, with one TMA store
+per peer and box (`ntb_gemm_peers`). One step = that product; `value` = 2 * 8192^3 flop
 divided by the time until every rank holds the whole C. Beside it the line reports
 `sharded_only` (C left distributed, no exchange) and `gather` (what the exchange costs, and
 the NCCL all-gather + re-interleave kernel as the comparison). Inputs are seeded synthetic
