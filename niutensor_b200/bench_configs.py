@@ -37,6 +37,9 @@ CONFIGS = {
     "4":    (torch.float16, 1, 256, 65536, 512, X_NOTRANS, X_TRANS, 1.0, 0.0, "hbm", "output layer H*W^T"),
     "5":    (torch.float16, 1, 8192, 8192, 8192, X_NOTRANS, X_NOTRANS, 1.0, 0.5, "tensor", "8192^3 fp16"),
     "5f32": (torch.float32, 1, 8192, 8192, 8192, X_NOTRANS, X_NOTRANS, 1.0, 0.5, "tensor", "8192^3 fp32"),
+    # not in the benchmark list: a weight gradient as XBackwardMath forms it (a^T * dE/dc accumulated
+    # into dE/db, 8192 tokens), the shape class the split on CTA pairs serves
+    "wgrad": (torch.float16, 1, 1024, 1024, 8192, X_TRANS, X_NOTRANS, 1.0, 1.0, "tensor", "weight gradient a^T * dE/dc, 8192 tokens"),
 }
 
 
@@ -252,7 +255,7 @@ def driver_table(dev, iters=60):
     GPU (CUDA-graph replay over an operand ring larger than twice the L2), each beside
     cuBLAS / torch on the same operands."""
     table = {}
-    for name in ("1", "2a", "2b", "3a", "3b", "3fused", "4", "4lsm", "5f32"):
+    for name in ("1", "2a", "2b", "3a", "3b", "3fused", "4", "4lsm", "5f32", "wgrad"):
         try:
             if name == "3fused":
                 line = run_attention(iters, True, True, dev)
