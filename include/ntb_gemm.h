@@ -356,6 +356,21 @@ int ntb_gemm_host(int devID, void * stream,
                   int count, float alpha, float beta);
 
 /*
+ * The same with `aDevice` already in DEVICE memory (b and c are host buffers as above): for
+ * a product sharded over several GPUs, where every rank needs the whole of a but the host's
+ * copy should cross PCIe once, not once per GPU -- each rank copies a slice in, the ranks
+ * all-gather it over NVLink, then each calls this with its shards of b and c. aDevice must be
+ * ready on `stream`. The reference's counterpart is a tensor that SetDevice moved earlier
+ * (source/tensor/XTensor.cpp:533-539) multiplied with ones that still live on the host.
+ */
+int ntb_gemm_host_resident_a(int devID, void * stream,
+                             const void * aDevice, int transA, const void * b, int transB, void * c,
+                             int dtypeAB, int dtypeC,
+                             int na, int ma, int nb, int mb, int nc, int mc,
+                             long long strideA, long long strideB, long long strideC,
+                             int count, float alpha, float beta);
+
+/*
  * Host-buffer form of one product that allocates nothing. It has no counterpart in the
  * reference, whose wrappers borrow scratch from XMem or cudaMalloc (XTensorBLAS.cu:
  * 329-343); it exists for callers that cannot allocate device memory at call time: a

@@ -48,6 +48,7 @@ PROTOTYPES = {
     "ntb_gemm_grouped": (_i, [_i, _vp, _i, ctypes.POINTER(_vp), _i, ctypes.POINTER(_vp), _i, ctypes.POINTER(_vp), _i, _i] +
                          [ctypes.POINTER(_i)] * 6 + [_f, _f]),
     "ntb_gemm_host": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _i, _i] + [_i] * 6 + [_ll] * 3 + [_i, _f, _f]),
+    "ntb_gemm_host_resident_a": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _i, _i] + [_i] * 6 + [_ll] * 3 + [_i, _f, _f]),
     "ntb_gemm_host_noalloc": (_i, [_i, _vp, _vp, _i, _vp, _i, _vp, _i, _i] + [_i] * 6 + [_f, _f]),
     "ntb_last_route": (_i, []),
     "ntb_set_route": (_i, [_i]),
