@@ -21,7 +21,7 @@ namespace ntb {
 namespace {
 
 constexpr int REPACK_THREADS = 256;
-constexpr int REPACK_PER_THREAD = 4;
+constexpr int REPACK_PER_THREAD = 8;
 
 struct RepackJob {
     const char * src;
@@ -51,34 +51,40 @@ __global__ void __launch_bounds__(REPACK_THREADS) RepackKernel(const RepackJobs 
     const bool second = blockIdx.x >= jobs.blocks0;
     const RepackJob & j = jobs.job[second ? 1 : 0];
     const long long base = ((long long)(blockIdx.x - (second ? jobs.blocks0 : 0u)) * REPACK_PER_THREAD) * REPACK_THREADS + threadIdx.x;
+    /* one 64-bit division per thread; the chunks after the first are reached by stepping
+       (column, row) with 32-bit arithmetic */
+    const uint32_t cpr = (uint32_t)j.chunksPerRow;
+    uint32_t col = (uint32_t)(base % cpr);
+    uint32_t rowAll = (uint32_t)(base / cpr);           /* row counted through all matrices (< 2^31, checked by the host) */
     asm volatile("griddepcontrol.wait;" ::: "memory");
     uint4 own[REPACK_PER_THREAD], nxt[REPACK_PER_THREAD];
     uint32_t shift[REPACK_PER_THREAD];
     int valid[REPACK_PER_THREAD];
-    /* all loads first, so that each thread has up to eight 16-byte requests in flight */
+    /* all loads first, so that each thread has up to 2 x REPACK_PER_THREAD 16-byte requests in flight */
 #pragma unroll
     for (int i = 0; i < REPACK_PER_THREAD; i++) {
         const long long idx = base + (long long)i * REPACK_THREADS;
         own[i] = nxt[i] = make_uint4(0u, 0u, 0u, 0u);
         shift[i] = 0u;
         valid[i] = 0;
-        if (idx >= j.total)
-            continue;
-        const int c = (int)(idx % j.chunksPerRow);
-        const long long rowAll = idx / j.chunksPerRow;
-        const int row = (int)(rowAll % j.rows);
-        const long long mat = rowAll / j.rows;
-        const long long q = mat % j.nQ, p = mat / j.nQ;
-        const int left = (j.cols - c * PER16) * ES;             /* bytes of the row from this chunk on */
-        valid[i] = left < 0 ? 0 : (left > 16 ? 16 : left);
-        if (valid[i] == 0)
-            continue;
-        const uintptr_t g = (uintptr_t)j.src + (uintptr_t)((p * j.sP + q * j.sQ + (long long)row * j.ld + (long long)c * PER16) * ES);
-        shift[i] = (uint32_t)(g & 15);
-        const uint4 * v = reinterpret_cast<const uint4 *>(g - shift[i]);
-        own[i] = __ldg(v);                                      /* holds the byte at g, which is inside the matrix */
-        if ((int)shift[i] + valid[i] > 16)
-            nxt[i] = __ldg(v + 1);                              /* holds the byte at g + 16 - shift, inside as well */
+        if (idx < j.total) {
+            const uint32_t row = rowAll % (uint32_t)j.rows, mat = rowAll / (uint32_t)j.rows;
+            const uint32_t q = mat % (uint32_t)j.nQ, p = mat / (uint32_t)j.nQ;
+            const int left = (j.cols - (int)col * PER16) * ES;     /* bytes of the row from this chunk on */
+            valid[i] = left < 0 ? 0 : (left > 16 ? 16 : left);
+            if (valid[i] != 0) {
+                const uintptr_t g = (uintptr_t)j.src
+                                  + (uintptr_t)(((long long)p * j.sP + (long long)q * j.sQ + (long long)row * j.ld + (long long)col * PER16) * ES);
+                shift[i] = (uint32_t)(g & 15);
+                const uint4 * v = reinterpret_cast<const uint4 *>(g - shift[i]);
+                own[i] = __ldg(v);                                  /* holds the byte at g, which is inside the matrix */
+                if ((int)shift[i] + valid[i] > 16)
+                    nxt[i] = __ldg(v + 1);                          /* holds the byte at g + 16 - shift, inside as well */
+            }
+        }
+        col += REPACK_THREADS;
+        rowAll += col / cpr;
+        col %= cpr;
     }
 #pragma unroll
     for (int i = 0; i < REPACK_PER_THREAD; i++) {
@@ -106,7 +112,7 @@ size_t PlanOperand(const void * src, int rows, int cols, long long ld, long long
     job.nP = sP ? P : 1;
     job.nQ = sQ ? Q : 1;
     job.sP = sP; job.sQ = sQ;
-    job.total = (long long)job.chunksPerRow * rows * job.nP * job.nQ;
+    job.total = (long long)job.chunksPerRow * rows * job.nP * job.nQ;   /* LaunchRepacked refuses more than 2^31 rows in all */
     *ldOut = (long long)job.chunksPerRow * per16;
     const long long mat = *ldOut * rows;
     *sQOut = sQ ? mat : 0;
@@ -165,6 +171,9 @@ int LaunchRepacked(const DeviceCtx & ctx, const Problem & p, cudaStream_t stream
     if (doB)
         bytesB = PlanOperand(p.b, p.bRows, p.bCols, p.ldb, p.sBp, p.sBq, P, p.Q, es, jobB, &q.ldb, &q.sBp, &q.sBq);
     if ((!doA && !doB) || bytesA + bytesB > ((size_t)4 << 30))
+        return NTB_ERR_ARG;
+    /* the copy kernel counts rows through all matrices of an operand in 32 bits */
+    if ((doA && (long long)p.aRows * jobA.nP * jobA.nQ >= (1LL << 31)) || (doB && (long long)p.bRows * jobB.nP * jobB.nQ >= (1LL << 31)))
         return NTB_ERR_ARG;
     int rc = ScratchAcquire(ctx, stream);
     if (rc != NTB_OK)
