@@ -56,7 +56,7 @@ FLOPS_TOTAL = 2.0 * N_DIM * N_DIM * N_DIM
 MAT_BYTES = N_DIM * N_DIM * 2
 # DRAM traffic of one full 8192^3 launch measured by ncu (dram__bytes_read.sum +
 # dram__bytes_write.sum) on the CTA-pair kernel with 512 x 256 tiles
-NCU_TRAFFIC_BYTES = 1.075e9
+NCU_TRAFFIC_BYTES = 1.106e9
 
 
 def config_dict(world):
