@@ -699,7 +699,11 @@ int HostProduct(int devID, void * stream, bool aResident,
        (Row chunks of a and c, whose copies are single contiguous blocks, measured 4-5 % slower
        on one and on two GPUs.) */
     const long long N = transB == NTB_X_TRANS ? nb : mb;
-    const int chunks = N >= 2048 ? 8 : (int)(N / 256);
+    /* tuning: fewest columns a chunk may have (a chunk of a row-major matrix is copied in pieces
+       of that many elements) */
+    const char * minColsKnob = getenv("NTB_HOST_CHUNK_COLS");
+    const long long minCols = minColsKnob && atoi(minColsKnob) >= 64 ? atoi(minColsKnob) : 256;
+    const int chunks = N >= 8 * minCols ? 8 : (int)(N / minCols);
     if (count == 1 && chunks >= 2 && (aResident ? 0 : aBytes) + bBytes + cBytes >= ((size_t)16 << 20) && EnsurePipe(ctx)) {
         const long long step = ((N + chunks - 1) / chunks + 63) / 64 * 64;      /* columns per chunk */
         rc = NTB_ERR_CUDA;
