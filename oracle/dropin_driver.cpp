@@ -5,8 +5,9 @@
  * niutensor_b200/host/nts_matmul_shim.cpp + libntb_gemm.so. The functions below run the
  * reference's OWN unit tests for this path (source/tensor/test/TMatrixMul.cpp,
  * TMatrixMul2D.cpp, TMatrixMul2DParallel.cpp, TMatrixMulBatched.cpp -- compiled from where
- * they lie), whose GPU halves now execute on the new kernels, and a half-precision
- * user-level call the reference has no test for.
+ * they lie), whose GPU halves now execute on the new kernels, a half-precision
+ * user-level call the reference has no test for, and the two list forms of the cuBLAS
+ * wrapper layer that none of the reference's tests reaches.
  */
 #include <cstdio>
 #include <cstring>
@@ -17,6 +18,7 @@
 #include "tensor/core/arithmetic/MatrixMul.h"
 #include "tensor/core/arithmetic/MatrixMulBatched.h"
 #include "tensor/core/arithmetic/MulAndShift.h"
+#include "tensor/core/arithmetic/XTensorBLAS.h"
 #include "tensor/test/TMatrixMul.h"
 #include "tensor/test/TMatrixMul2D.h"
 #include "tensor/test/TMatrixMul2DParallel.h"
@@ -74,6 +76,78 @@ int dropin_mulandshift_f32(int dev, int rows, int in, int out, const float * x, 
         return 1;
     cudaMemcpy(y, ty.data, sizeof(float) * ty.unitNum, cudaMemcpyDeviceToHost);
     return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+/* _CudaBLASMatrixMULList (XTensorBLAS.cu:252-387) on a list of fp32 GPU tensors whose shapes
+   differ from item to item (m[i] x k[i] times k[i] x n[i]): the reference loops over single
+   cuBLAS calls there, the shim hands the whole list to one grouped launch. Operands and
+   results are packed one item after the other in the host arrays. */
+int dropin_list_unequal_f32(int dev, int count, const int * m, const int * n, const int * k,
+                            const float * a, const float * b, float * c, float alpha, float beta)
+{
+    std::vector<XTensor *> keep;
+    TensorList la, lb, lc;
+    size_t oa = 0, ob = 0, oc = 0;
+    for (int i = 0; i < count; i++) {
+        int da[2] = { m[i], k[i] }, db[2] = { k[i], n[i] }, dc[2] = { m[i], n[i] };
+        XTensor * ta = new XTensor(), * tb = new XTensor(), * tc = new XTensor();
+        InitTensorV2(ta, 2, da, X_FLOAT, 1.0F, dev);
+        InitTensorV2(tb, 2, db, X_FLOAT, 1.0F, dev);
+        InitTensorV2(tc, 2, dc, X_FLOAT, 1.0F, dev);
+        ta->SetData(a + oa, ta->unitNum);
+        tb->SetData(b + ob, tb->unitNum);
+        tc->SetData(c + oc, tc->unitNum);
+        oa += (size_t)ta->unitNum; ob += (size_t)tb->unitNum; oc += (size_t)tc->unitNum;
+        la.Add(ta); lb.Add(tb); lc.Add(tc);
+        keep.push_back(ta); keep.push_back(tb); keep.push_back(tc);
+    }
+    _CudaBLASMatrixMULList(NULL, &la, X_NOTRANS, &lb, X_NOTRANS, &lc, count, alpha, beta);
+    oc = 0;
+    for (int i = 0; i < count; i++) {
+        XTensor * tc = keep[3 * i + 2];
+        cudaMemcpy(c + oc, tc->data, sizeof(float) * tc->unitNum, cudaMemcpyDeviceToHost);
+        oc += (size_t)tc->unitNum;
+    }
+    const int rc = cudaGetLastError() == cudaSuccess ? 0 : 2;
+    for (size_t i = 0; i < keep.size(); i++)
+        delete keep[i];
+    return rc;
+}
+
+/* _CudaBLASMatrixMULBatched (XTensorBLAS.cu:109-178): DEVICE tables of device pointers to
+   `count` fp32 matrices of one shape, as cublasGemmBatchedEx took them */
+int dropin_batched_pointer_tables_f32(int dev, int count, int m, int n, int k,
+                                      const float * a, const float * b, float * c, float alpha, float beta)
+{
+    int prev = 0;
+    cudaGetDevice(&prev);
+    cudaSetDevice(dev);
+    float * da = NULL, * db = NULL, * dc = NULL;
+    void ** tables = NULL;
+    const size_t sa = (size_t)m * k, sb = (size_t)k * n, sc = (size_t)m * n;
+    int rc = 2;
+    if (cudaMalloc(&da, sizeof(float) * sa * count) == cudaSuccess && cudaMalloc(&db, sizeof(float) * sb * count) == cudaSuccess &&
+        cudaMalloc(&dc, sizeof(float) * sc * count) == cudaSuccess && cudaMalloc(&tables, sizeof(void *) * 3 * count) == cudaSuccess) {
+        cudaMemcpy(da, a, sizeof(float) * sa * count, cudaMemcpyHostToDevice);
+        cudaMemcpy(db, b, sizeof(float) * sb * count, cudaMemcpyHostToDevice);
+        cudaMemcpy(dc, c, sizeof(float) * sc * count, cudaMemcpyHostToDevice);
+        std::vector<void *> host(3 * count);
+        /* an irregular order of the items, so that no stride pattern describes the tables */
+        for (int i = 0; i < count; i++) {
+            const int j = (i * 5 + 3) % count;
+            host[i] = da + sa * j;
+            host[count + i] = db + sb * j;
+            host[2 * count + i] = dc + sc * j;
+        }
+        cudaMemcpy(tables, host.data(), sizeof(void *) * 3 * count, cudaMemcpyHostToDevice);
+        _CudaBLASMatrixMULBatched(NULL, (const void **)tables, X_NOTRANS, X_FLOAT, (const void **)(tables + count), X_NOTRANS, X_FLOAT,
+                                  tables + 2 * count, X_FLOAT, count, m, k, k, n, m, n, alpha, beta);
+        cudaMemcpy(c, dc, sizeof(float) * sc * count, cudaMemcpyDeviceToHost);
+        rc = cudaGetLastError() == cudaSuccess ? 0 : 2;
+    }
+    cudaFree(da); cudaFree(db); cudaFree(dc); cudaFree(tables);
+    cudaSetDevice(prev);
+    return rc;
 }
 
 }

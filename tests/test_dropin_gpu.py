@@ -68,3 +68,45 @@ def test_reference_mulandshift_runs_on_the_shim(dropin, oracle):
     assert rc == 0
     want = oracle.matmul2d(x, X_NOTRANS, w, X_NOTRANS) + b[None, :]
     assert rel_fro(y, want) <= 1e-5
+
+
+def test_wrapper_list_of_unequal_shapes(dropin, oracle):
+    """_CudaBLASMatrixMULList with items of different shapes (the reference loops over single
+    cuBLAS calls, XTensorBLAS.cu:373-385; the shim passes the list to one grouped launch),
+    called through the reference's own signature with TensorLists of GPU tensors."""
+    from niutensor_b200 import capi
+    rng = np.random.default_rng(33)
+    shapes = [(64, 72, 40), (128, 256, 96), (8, 8, 8), (200, 136, 64), (32, 520, 128)]
+    a = [rng.normal(size=(m, k)).astype(np.float32) for m, n, k in shapes]
+    b = [rng.normal(size=(k, n)).astype(np.float32) for m, n, k in shapes]
+    c0 = [rng.normal(size=(m, n)).astype(np.float32) for m, n, k in shapes]
+    pack = lambda xs: np.ascontiguousarray(np.concatenate([x.reshape(-1) for x in xs]))
+    pa, pb, pc = pack(a), pack(b), pack(c0)
+    ia = lambda col: (ctypes.c_int * len(shapes))(*[s[col] for s in shapes])
+    fp = ctypes.POINTER(ctypes.c_float)
+    before = capi.lib().ntb_launch_count()
+    rc = dropin.dropin_list_unequal_f32(0, len(shapes), ia(0), ia(1), ia(2), pa.ctypes.data_as(fp), pb.ctypes.data_as(fp),
+                                        pc.ctypes.data_as(fp), ctypes.c_float(0.5), ctypes.c_float(0.25))
+    assert rc == 0
+    assert capi.lib().ntb_launch_count() == before + 1          # one grouped launch, not five
+    off = 0
+    for (m, n, k), x, y, z in zip(shapes, a, b, c0):
+        got = pc[off:off + m * n].reshape(m, n)
+        off += m * n
+        assert rel_fro(got, oracle.matmul2d(x, X_NOTRANS, y, X_NOTRANS, 0.5, 0.25, z)) <= 1e-5, (m, n, k)
+
+
+def test_wrapper_device_pointer_tables(dropin, oracle):
+    """_CudaBLASMatrixMULBatched as cublasGemmBatchedEx took it: device arrays of device pointers,
+    here in an order no stride pattern describes."""
+    rng = np.random.default_rng(34)
+    count, m, n, k = 7, 72, 136, 48
+    a = rng.normal(size=(count, m, k)).astype(np.float32)
+    b = rng.normal(size=(count, k, n)).astype(np.float32)
+    c0 = rng.normal(size=(count, m, n)).astype(np.float32)
+    c = c0.copy()
+    fp = ctypes.POINTER(ctypes.c_float)
+    rc = dropin.dropin_batched_pointer_tables_f32(0, count, m, n, k, a.ctypes.data_as(fp), b.ctypes.data_as(fp),
+                                                  c.ctypes.data_as(fp), ctypes.c_float(1.0), ctypes.c_float(0.5))
+    assert rc == 0
+    assert rel_fro(c, oracle.matmul_batched(a, X_NOTRANS, b, X_NOTRANS, 1.0, 0.5, c0)) <= 1e-5
