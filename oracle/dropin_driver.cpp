@@ -114,6 +114,35 @@ int dropin_list_unequal_f32(int dev, int count, const int * m, const int * n, co
     return rc;
 }
 
+/* MatrixMul(a, tA, b, tB, c, alpha, beta) -- the overload with an existing c and beta != 0
+   (MatrixMul.cpp:317) -- on fp32 tensors that live in an XMem pool of GPU `dev`. An int
+   tensor of `pad` elements is allocated from the pool first, so the matrices that follow
+   start wherever the pool's cursor stands (XMem.cpp:668-686), 16-byte aligned or not.
+   Returns 0 on success; *aligned receives 1 when a's address is a multiple of 16. */
+int dropin_matmul_beta_in_pool_f32(int dev, int pad, int m, int n, int k, const float * a, const float * b, float * c,
+                                   float alpha, float beta, int * aligned)
+{
+    XMem * mem = new XMem(dev, UNI_FREE, (MTYPE)64 * 1024 * 1024, 1, 0);
+    int rc = 0;
+    {
+        int dp[1] = { pad }, da[2] = { m, k }, db[2] = { k, n }, dc[2] = { m, n };
+        XTensor tp, ta, tb, tc;
+        InitTensorV2(&tp, 1, dp, X_INT, 1.0F, dev, mem);
+        InitTensorV2(&ta, 2, da, X_FLOAT, 1.0F, dev, mem);
+        InitTensorV2(&tb, 2, db, X_FLOAT, 1.0F, dev, mem);
+        InitTensorV2(&tc, 2, dc, X_FLOAT, 1.0F, dev, mem);
+        ta.SetData(a, ta.unitNum);
+        tb.SetData(b, tb.unitNum);
+        tc.SetData(c, tc.unitNum);
+        *aligned = ((size_t)ta.data % 16) == 0 ? 1 : 0;
+        MatrixMul(ta, X_NOTRANS, tb, X_NOTRANS, tc, alpha, beta);
+        cudaMemcpy(c, tc.data, sizeof(float) * tc.unitNum, cudaMemcpyDeviceToHost);
+        rc = cudaGetLastError() == cudaSuccess ? 0 : 2;
+    }
+    delete mem;
+    return rc;
+}
+
 /* _CudaBLASMatrixMULBatched (XTensorBLAS.cu:109-178): DEVICE tables of device pointers to
    `count` fp32 matrices of one shape, as cublasGemmBatchedEx took them */
 int dropin_batched_pointer_tables_f32(int dev, int count, int m, int n, int k,

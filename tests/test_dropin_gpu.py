@@ -8,9 +8,10 @@ CPU oracle.
 Only the GPU halves of the reference's unit tests are evidence here: for tensors on the CPU
 (devID < 0) the shim hands the product to the reference's untouched _MatrixMul2DParallel, so
 the CPU halves, and TestMatrixMul2DParallel as a whole, are the reference checking itself.
-The tensors of these unit tests are allocated without a memory pool (mem == NULL); tensors
-that live in XMem pools are covered by tests/test_samples_gpu.py (the transformer sample
-allocates from its pools) and by the loader-warp cases of tests/test_gemm_gpu.py."""
+The tensors of the reference's unit tests are allocated without a memory pool (mem == NULL);
+tensors that live in XMem pools are covered by the pool test at the end of this file, by
+tests/test_samples_gpu.py (the transformer sample allocates from its pools) and by the
+misaligned-operand cases of tests/test_gemm_gpu.py."""
 import ctypes
 import os
 
@@ -110,3 +111,26 @@ def test_wrapper_device_pointer_tables(dropin, oracle):
                                                   c.ctypes.data_as(fp), ctypes.c_float(1.0), ctypes.c_float(0.5))
     assert rc == 0
     assert rel_fro(c, oracle.matmul_batched(a, X_NOTRANS, b, X_NOTRANS, 1.0, 0.5, c0)) <= 1e-5
+
+
+@pytest.mark.parametrize("pad", [64, 3])
+def test_matmul_with_beta_on_tensors_from_a_memory_pool(dropin, oracle, pad):
+    """The C++ overload MatrixMul(a, tA, b, tB, c, alpha, beta) with beta != 0 on tensors
+    allocated from an XMem pool; with an odd-sized tensor ahead of them in the pool the
+    matrices need not start on a 16-byte boundary, and the product stays on the tensor cores."""
+    from niutensor_b200 import capi
+    rng = np.random.default_rng(35 + pad)
+    m, n, k = 200, 136, 72
+    a = rng.normal(size=(m, k)).astype(np.float32)
+    b = rng.normal(size=(k, n)).astype(np.float32)
+    c0 = rng.normal(size=(m, n)).astype(np.float32)
+    c = c0.copy()
+    fp = ctypes.POINTER(ctypes.c_float)
+    aligned = ctypes.c_int(-1)
+    simt_before = capi.lib().ntb_route_count(capi.ROUTE_SIMT)
+    rc = dropin.dropin_matmul_beta_in_pool_f32(0, pad, m, n, k, a.ctypes.data_as(fp), b.ctypes.data_as(fp), c.ctypes.data_as(fp),
+                                               ctypes.c_float(0.5), ctypes.c_float(0.25), ctypes.byref(aligned))
+    assert rc == 0
+    assert aligned.value in (0, 1)
+    assert capi.lib().ntb_route_count(capi.ROUTE_SIMT) == simt_before       # no product fell back to FFMA
+    assert rel_fro(c, oracle.matmul2d(a, X_NOTRANS, b, X_NOTRANS, 0.5, 0.25, c0)) <= 1e-5
