@@ -100,6 +100,28 @@ def matmul_column_shard_to_all(a, transposedA, b_local, transposedB, c_sym, peer
     return c_sym
 
 
+class RankLost(RuntimeError):
+    """A collective of the sharded path did not complete: a rank left, never joined, or the
+    group's timeout ran out. The caller's step is void; nothing was left half-launched on this
+    rank (the error surfaces on the host, between launches)."""
+
+
+def guarded(collective, *args, **kwargs):
+    """Runs one collective-bearing call of this module (gather_columns, vocab_parallel_output,
+    ...) and turns the backend's own errors -- a closed connection, the process group's
+    timeout -- into RankLost, so that a trainer can tell "a peer is gone" from a bug. The
+    reference has no counterpart: its workers share one process (source/train/XWorkerJob.cpp)
+    and cannot lose one another. Give the process group a short timeout
+    (init_process_group(..., timeout=...)) for this to answer quickly."""
+    try:
+        out = collective(*args, **kwargs)
+        if torch.cuda.is_available() and any(isinstance(a, torch.Tensor) and a.is_cuda for a in args):
+            torch.cuda.current_stream().synchronize()     # NCCL reports a lost peer when the work is waited for
+        return out
+    except (RuntimeError, dist.DistBackendError, dist.DistNetworkError) as exc:
+        raise RankLost("collective failed: %s" % (str(exc).splitlines()[0] if str(exc) else type(exc).__name__)) from exc
+
+
 def gather_columns(c_local, n_cols, group=None):
     """All ranks receive the full [..., M, n_cols] matrix from the per-rank column shards.
 

@@ -889,6 +889,36 @@ def test_realigning_prepass_for_larger_products(dtype, tA, tB, oracle):
     status_ok()
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_every_extent_from_1_to_130(dtype, oracle):
+    """Every value from 1 to 130 appears as M, as N and as K (in different products), across
+    the four transpositions and the alpha / beta combinations: tile edges, K tails, pitches of
+    every residue. Guard values around C must survive."""
+    rng = np.random.default_rng(130)
+    L = capi.lib()
+    simt_before = L.ntb_route_count(capi.ROUTE_SIMT)
+    for d in range(1, 131):
+        M, N, K = d, 131 - d, (d * 37) % 130 + 1
+        tA = X_TRANS if d & 1 else X_NOTRANS
+        tB = X_TRANS if d & 2 else X_NOTRANS
+        alpha, beta = AB[d % len(AB)]
+        a = stored(rng, (), M, K, tA)
+        b = stored(rng, (), K, N, tB)
+        c0 = rng.normal(size=(M, N)).astype(np.float32)
+        if dtype == torch.float16:
+            a, b, c0 = round_to_half(a), round_to_half(b), round_to_half(c0)
+        cbuf = torch.full((M + 2, N), 7.0, device=DEV, dtype=dtype)
+        cbuf[1:M + 1] = to_dev(c0, dtype)
+        c = cbuf[1:M + 1]
+        ops._MatrixMul2D(to_dev(a, dtype), tA, to_dev(b, dtype), tB, c, alpha, beta)
+        err = rel_fro(c.float().cpu().numpy(), oracle.matmul2d(a, tA, b, tB, alpha, beta, c0))
+        assert err <= TOL[dtype], (M, N, K, tA, tB, alpha, beta, err)
+        assert float(cbuf[0].min()) == 7.0 and float(cbuf[0].max()) == 7.0
+        assert float(cbuf[M + 1].min()) == 7.0 and float(cbuf[M + 1].max()) == 7.0
+    assert L.ntb_route_count(capi.ROUTE_SIMT) == simt_before      # all of them on the tensor cores
+    status_ok()
+
+
 def test_host_product_with_a_resident_on_the_device(oracle):
     """ntb_gemm_host_resident_a: b and c are host buffers, a is device memory already (a rank of
     a sharded product after the all-gather of a). Small shapes take the plain path, a wide one

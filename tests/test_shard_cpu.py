@@ -79,3 +79,34 @@ def test_sharded_products_gather_to_the_full_result(world):
         out = mgr.dict()
         mp.spawn(_worker, args=(world, port, out), nprocs=world, join=True)
         assert dict(out) == {r: 7 for r in range(world)}
+
+
+def _leaver(rank, world, port, out):
+    import datetime
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    piece = torch.full((4, 8), float(rank))
+    full = shard.gather_columns(piece, 16)                  # a step in which every rank takes part
+    out["first_%d" % rank] = full.tolist()
+    if rank == 1:
+        # this rank leaves between two steps, with nothing of its own in flight
+        dist.destroy_process_group()
+        return
+    try:
+        shard.guarded(shard.gather_columns, piece, 16)
+        out["second"] = "completed"
+    except shard.RankLost as exc:
+        out["second"] = "lost: " + str(exc)[:60]
+
+
+def test_a_rank_that_leaves_between_steps_is_reported_on_the_host():
+    """Failure detection without any device fault: rank 1 leaves after a complete step; rank 0's
+    next collective ends with shard.RankLost (closed connection or the group's 8 s timeout)
+    instead of hanging."""
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_leaver, args=(2, _free_port(), out), nprocs=2, join=True)
+    assert out["first_0"] == out["first_1"]
+    assert out["first_0"][0] == [0.0] * 8 + [1.0] * 8
+    assert out["second"].startswith("lost: "), out["second"]
