@@ -246,9 +246,8 @@ def main_reference(args):
     world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
     steps, warm = max(1, args.steps), max(1, args.warmup)
     r = time_cpu(steps, warm)
-    cfg = config_dict(world)
-    cfg["device"] = "host CPU"
-    line = {"impl": "reference", "metric": "MatrixMul TFLOP/s", "value": r["value"], "unit": "TFLOP/s",
+    cfg = config_dict(world)                        # the same dictionary as the GPU arm prints
+    line = {"impl": "reference", "device": "host CPU", "metric": "MatrixMul TFLOP/s", "value": r["value"], "unit": "TFLOP/s",
             "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": r["ms_per_step"],
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
             "data": "synthetic", "config": cfg,
