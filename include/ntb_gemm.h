@@ -378,8 +378,9 @@ int ntb_gemm_host_resident_a(int devID, void * stream,
  * may fail, and worker threads sharing a device, which cudaMalloc / cudaFree would stall.
  * a, b and c are HOST buffers, packed (pitch = columns). All device scratch -- staging for
  * a, b, c and the status word -- is a fixed array inside the library, so the staged
- * operands (each rounded up to 256 bytes) must fit in NTB_NOALLOC_MAX_BYTES; a larger
- * problem returns NTB_ERR_LIMIT. Calls on one device share that array: do not overlap
+ * operands (rows padded to a multiple of 16 bytes, so that TMA can address every shape; each
+ * operand rounded up to 256 bytes) must fit in NTB_NOALLOC_MAX_BYTES; a larger problem
+ * returns NTB_ERR_LIMIT. Calls on one device share that array: do not overlap
  * them. The first call on a device looks up the array's address, and with CUDA's default
  * lazy module loading that look-up is also when the runtime reserves the array's 16 MiB on
  * the device: make that first call (any tiny product) early -- before the host's pools take

@@ -103,9 +103,13 @@ extern "C" int ntb_gemm_host_noalloc(int devID, void * stream,
     if (nc == 0 || mc == 0)
         return NTB_OK;
 
-    const size_t aBytes = (size_t)na * ma * ElemSize(dtypeAB);
-    const size_t bBytes = (size_t)nb * mb * ElemSize(dtypeAB);
-    const size_t cBytes = (size_t)nc * mc * ElemSize(dtypeC);
+    /* The staged copies get row pitches that are multiples of 16 bytes (the host buffers are
+       packed), so that every staged operand can be described to TMA whatever its extents. */
+    const size_t rowA = (size_t)ma * ElemSize(dtypeAB), rowB = (size_t)mb * ElemSize(dtypeAB), rowC = (size_t)mc * ElemSize(dtypeC);
+    const size_t pitchA = (rowA + 15) & ~(size_t)15, pitchB = (rowB + 15) & ~(size_t)15, pitchC = (rowC + 15) & ~(size_t)15;
+    const size_t aBytes = (size_t)na * pitchA;
+    const size_t bBytes = (size_t)nb * pitchB;
+    const size_t cBytes = (size_t)nc * pitchC;
     if (RoundUp256(aBytes) + RoundUp256(bBytes) + RoundUp256(cBytes) > (size_t)NTB_NOALLOC_MAX_BYTES)
         return NTB_ERR_LIMIT;      /* the fixed scratch array cannot hold this problem */
 
@@ -136,11 +140,11 @@ extern "C" int ntb_gemm_host_noalloc(int devID, void * stream,
         if (cudaMemsetAsync(scratch, 0, HEADER_BYTES, st) != cudaSuccess)
             break;
         queued = true;
-        if (aBytes && cudaMemcpyAsync(dA, a, aBytes, cudaMemcpyHostToDevice, st) != cudaSuccess)
+        if (aBytes && cudaMemcpy2DAsync(dA, pitchA, a, rowA, rowA, (size_t)na, cudaMemcpyHostToDevice, st) != cudaSuccess)
             break;
-        if (bBytes && cudaMemcpyAsync(dB, b, bBytes, cudaMemcpyHostToDevice, st) != cudaSuccess)
+        if (bBytes && cudaMemcpy2DAsync(dB, pitchB, b, rowB, rowB, (size_t)nb, cudaMemcpyHostToDevice, st) != cudaSuccess)
             break;
-        if (beta != 0.f && cudaMemcpyAsync(dC, c, cBytes, cudaMemcpyHostToDevice, st) != cudaSuccess)
+        if (beta != 0.f && cudaMemcpy2DAsync(dC, pitchC, c, rowC, rowC, (size_t)nc, cudaMemcpyHostToDevice, st) != cudaSuccess)
             break;
 
         Problem p;
@@ -151,7 +155,8 @@ extern "C" int ntb_gemm_host_noalloc(int devID, void * stream,
         p.bMN = transB == NTB_X_NOTRANS;
         p.M = an; p.N = bm; p.K = am;
         p.aRows = na; p.aCols = ma; p.bRows = nb; p.bCols = mb;
-        p.lda = ma; p.ldb = mb; p.ldc = mc;
+        p.lda = (long long)(pitchA / ElemSize(dtypeAB)); p.ldb = (long long)(pitchB / ElemSize(dtypeAB));
+        p.ldc = (long long)(pitchC / ElemSize(dtypeC));
         p.count = 1; p.Q = 1;
         p.alpha = alpha; p.beta = beta;
         int route = NTB_ROUTE_NONE;
@@ -160,7 +165,7 @@ extern "C" int ntb_gemm_host_noalloc(int devID, void * stream,
             rc = LaunchTc(ctx, p, st, &route);
         }
         else if (forced != NTB_ROUTE_SIMT && forced != NTB_ROUTE_TC_F16_PAIR && LdgEligible(p)) {
-            rc = LaunchLdg(ctx, p, st, &route);         /* pitches TMA cannot address: loader warps, as everywhere else */
+            rc = LaunchLdg(ctx, p, st, &route);         /* not reached with the padded staging pitches; kept for safety */
         }
         else if (forced == NTB_ROUTE_TC_F16 || forced == NTB_ROUTE_TC_3XTF32 || forced == NTB_ROUTE_TC_F16_PAIR) {
             rc = NTB_ERR_ARG;                       /* a tensor-core route was demanded and cannot address this */
@@ -173,7 +178,7 @@ extern "C" int ntb_gemm_host_noalloc(int devID, void * stream,
             break;
         SetLastRoute(route);
         rc = NTB_ERR_CUDA;
-        if (cudaMemcpyAsync(c, dC, cBytes, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+        if (cudaMemcpy2DAsync(c, rowC, dC, pitchC, rowC, (size_t)nc, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
             cudaMemcpyAsync(&hostStatus, scratch, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess ||
             cudaStreamSynchronize(st) != cudaSuccess)
             break;

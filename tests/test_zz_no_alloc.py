@@ -56,8 +56,8 @@ def test_two_calls_in_a_row_match_the_allocating_entry_point(oracle):
     assert np.isfinite(got.astype(np.float32)).all() and np.abs(got.astype(np.float32)).max() > 0
     ref = oracle.matmul2d(a.astype(np.float32), X_NOTRANS, b.astype(np.float32), X_TRANS, 0.5, 0.5, c0.astype(np.float32))
     assert rel_fro(got.astype(np.float32), ref) <= 2e-3
-    # call 2, straight after: fp32, smaller, ragged (pitches TMA cannot address), beta == 0 -- the scratch
-    # still holds call 1's operands and result
+    # call 2, straight after: fp32, smaller, ragged (packed pitches TMA could not address: the staged
+    # copies get padded rows), beta == 0 -- the scratch still holds call 1's operands and result
     a = rng.uniform(-1, 1, (53, 37)).astype(np.float32)             # stored K x M, used transposed
     b = rng.uniform(-1, 1, (53, 29)).astype(np.float32)
     c0 = np.full((37, 29), np.nan, np.float32)
