@@ -339,7 +339,8 @@ int ntb_gemm_multicast(int devID, void * stream,
 
 /*
  * Host-buffer form: a, b and c are HOST memory (pinned or pageable). Copies the
- * operands (and c when beta != 0) to staging buffers owned by the device context, runs
+ * operands (and c when beta != 0) to staging buffers owned by the device context (a single
+ * product with rows padded to a multiple of 16 bytes, so that TMA can address any extents), runs
  * the strided-batched GEMM, copies c back and synchronises the stream. This is what a
  * caller holding CPU tensors does through the reference with SetDevice/FlushToDevice
  * (source/tensor/XTensor.cpp:533-539, 1992-1999) around MatrixMul. Staging buffers grow

@@ -682,10 +682,17 @@ int HostProduct(int devID, void * stream, bool aResident,
         return NTB_ERR_CUDA;
     cudaStream_t st = (cudaStream_t)stream;
     const size_t esAB = ElemSize(dtypeAB), esC = ElemSize(dtypeC);
+    /* A single product is staged with row pitches that are multiples of 16 bytes (the host
+       buffers are packed), so that TMA can address the staged copies whatever the extents;
+       batches keep the caller's packed layout and strides. */
+    const bool pad = count == 1;
+    const long long ldaS = pad && !aResident ? (long long)((((size_t)ma * esAB + 15) & ~(size_t)15) / esAB) : ma;
+    const long long ldbS = pad ? (long long)((((size_t)mb * esAB + 15) & ~(size_t)15) / esAB) : mb;
+    const long long ldcS = pad ? (long long)((((size_t)mc * esC + 15) & ~(size_t)15) / esC) : mc;
     /* a stride of 0 shares one matrix; otherwise `count` matrices at the given stride */
-    const size_t aBytes = ((size_t)(strideA ? strideA * (count - 1) : 0) + (size_t)na * ma) * esAB;
-    const size_t bBytes = ((size_t)(strideB ? strideB * (count - 1) : 0) + (size_t)nb * mb) * esAB;
-    const size_t cBytes = ((size_t)(strideC ? strideC * (count - 1) : 0) + (size_t)nc * mc) * esC;
+    const size_t aBytes = pad ? (size_t)na * ldaS * esAB : ((size_t)(strideA ? strideA * (count - 1) : 0) + (size_t)na * ma) * esAB;
+    const size_t bBytes = pad ? (size_t)nb * ldbS * esAB : ((size_t)(strideB ? strideB * (count - 1) : 0) + (size_t)nb * mb) * esAB;
+    const size_t cBytes = pad ? (size_t)nc * ldcS * esC : ((size_t)(strideC ? strideC * (count - 1) : 0) + (size_t)nc * mc) * esC;
     {
         std::lock_guard<std::mutex> g(gLock);
         if ((!aResident && GrowStage(ctx, 0, aBytes) != NTB_OK) || GrowStage(ctx, 1, bBytes) != NTB_OK ||
@@ -712,7 +719,8 @@ int HostProduct(int devID, void * stream, bool aResident,
                 cudaStreamWaitEvent(ctx->copyIn, ctx->evStart, 0) != cudaSuccess ||
                 cudaStreamWaitEvent(ctx->copyOut, ctx->evStart, 0) != cudaSuccess)
                 break;
-            if (!aResident && cudaMemcpyAsync(ctx->stage[0], a, aBytes, cudaMemcpyHostToDevice, ctx->copyIn) != cudaSuccess)
+            if (!aResident && cudaMemcpy2DAsync(ctx->stage[0], (size_t)ldaS * esAB, a, (size_t)ma * esAB, (size_t)ma * esAB, (size_t)na,
+                                                cudaMemcpyHostToDevice, ctx->copyIn) != cudaSuccess)
                 break;
             bool fail = false;
             int used = 0;
@@ -720,13 +728,14 @@ int HostProduct(int devID, void * stream, bool aResident,
                 const long long w = N - n0 < step ? N - n0 : step;
                 /* B: columns [n0, n0+w) of a stored k x N matrix, or rows of a stored N x k one */
                 if (transB == NTB_X_TRANS)
-                    fail |= cudaMemcpyAsync((char *)ctx->stage[1] + (size_t)n0 * mb * esAB, (const char *)b + (size_t)n0 * mb * esAB,
-                                            (size_t)w * mb * esAB, cudaMemcpyHostToDevice, ctx->copyIn) != cudaSuccess;
+                    fail |= cudaMemcpy2DAsync((char *)ctx->stage[1] + (size_t)n0 * ldbS * esAB, (size_t)ldbS * esAB,
+                                              (const char *)b + (size_t)n0 * mb * esAB, (size_t)mb * esAB, (size_t)mb * esAB, (size_t)w,
+                                              cudaMemcpyHostToDevice, ctx->copyIn) != cudaSuccess;
                 else
-                    fail |= cudaMemcpy2DAsync((char *)ctx->stage[1] + n0 * esAB, (size_t)mb * esAB, (const char *)b + n0 * esAB,
+                    fail |= cudaMemcpy2DAsync((char *)ctx->stage[1] + n0 * esAB, (size_t)ldbS * esAB, (const char *)b + n0 * esAB,
                                               (size_t)mb * esAB, (size_t)w * esAB, nb, cudaMemcpyHostToDevice, ctx->copyIn) != cudaSuccess;
                 if (beta != 0.f)
-                    fail |= cudaMemcpy2DAsync((char *)ctx->stage[2] + n0 * esC, (size_t)mc * esC, (const char *)c + n0 * esC,
+                    fail |= cudaMemcpy2DAsync((char *)ctx->stage[2] + n0 * esC, (size_t)ldcS * esC, (const char *)c + n0 * esC,
                                               (size_t)mc * esC, (size_t)w * esC, nc, cudaMemcpyHostToDevice, ctx->copyIn) != cudaSuccess;
                 fail |= cudaEventRecord(ctx->evIn[used], ctx->copyIn) != cudaSuccess;
                 fail |= cudaStreamWaitEvent(st, ctx->evIn[used], 0) != cudaSuccess;
@@ -734,18 +743,18 @@ int HostProduct(int devID, void * stream, bool aResident,
                     break;
                 int r2;
                 if (transB == NTB_X_TRANS)
-                    r2 = ntb_gemm(devID, stream, aDev, transA, (char *)ctx->stage[1] + (size_t)n0 * mb * esAB, transB,
+                    r2 = ntb_gemm(devID, stream, aDev, transA, (char *)ctx->stage[1] + (size_t)n0 * ldbS * esAB, transB,
                                   (char *)ctx->stage[2] + n0 * esC, dtypeAB, dtypeC, na, ma, (int)w, mb, nc, (int)w,
-                                  ma, mb, mc, alpha, beta);
+                                  ldaS, ldbS, ldcS, alpha, beta);
                 else
                     r2 = ntb_gemm(devID, stream, aDev, transA, (char *)ctx->stage[1] + n0 * esAB, transB,
                                   (char *)ctx->stage[2] + n0 * esC, dtypeAB, dtypeC, na, ma, nb, (int)w, nc, (int)w,
-                                  ma, mb, mc, alpha, beta);
+                                  ldaS, ldbS, ldcS, alpha, beta);
                 if (r2 != NTB_OK) { rc = r2; fail = true; break; }
                 fail |= cudaEventRecord(ctx->evOut[used], st) != cudaSuccess;
                 fail |= cudaStreamWaitEvent(ctx->copyOut, ctx->evOut[used], 0) != cudaSuccess;
                 fail |= cudaMemcpy2DAsync((char *)c + n0 * esC, (size_t)mc * esC, (char *)ctx->stage[2] + n0 * esC,
-                                          (size_t)mc * esC, (size_t)w * esC, nc, cudaMemcpyDeviceToHost, ctx->copyOut) != cudaSuccess;
+                                          (size_t)ldcS * esC, (size_t)w * esC, nc, cudaMemcpyDeviceToHost, ctx->copyOut) != cudaSuccess;
             }
             /* even after a failure, let everything issued so far drain before returning */
             const bool s1 = cudaStreamSynchronize(ctx->copyIn) == cudaSuccess;
@@ -759,6 +768,31 @@ int HostProduct(int devID, void * stream, bool aResident,
         return rc;
     }
 
+    if (pad) {
+        /* packed host rows to padded device rows and back */
+        if ((!aResident && na && ma &&
+             cudaMemcpy2DAsync(ctx->stage[0], (size_t)ldaS * esAB, a, (size_t)ma * esAB, (size_t)ma * esAB, (size_t)na,
+                               cudaMemcpyHostToDevice, st) != cudaSuccess) ||
+            (nb && mb &&
+             cudaMemcpy2DAsync(ctx->stage[1], (size_t)ldbS * esAB, b, (size_t)mb * esAB, (size_t)mb * esAB, (size_t)nb,
+                               cudaMemcpyHostToDevice, st) != cudaSuccess))
+            return NTB_ERR_CUDA;
+        if (beta != 0.f && nc && mc &&
+            cudaMemcpy2DAsync(ctx->stage[2], (size_t)ldcS * esC, c, (size_t)mc * esC, (size_t)mc * esC, (size_t)nc,
+                              cudaMemcpyHostToDevice, st) != cudaSuccess)
+            return NTB_ERR_CUDA;
+        rc = ntb_gemm(devID, stream, aDev, transA, ctx->stage[1], transB, ctx->stage[2], dtypeAB, dtypeC,
+                      na, ma, nb, mb, nc, mc, ldaS, ldbS, ldcS, alpha, beta);
+        if (rc != NTB_OK)
+            return rc;
+        if ((nc && mc && cudaMemcpy2DAsync(c, (size_t)mc * esC, ctx->stage[2], (size_t)ldcS * esC, (size_t)mc * esC, (size_t)nc,
+                                           cudaMemcpyDeviceToHost, st) != cudaSuccess) ||
+            cudaStreamSynchronize(st) != cudaSuccess) {
+            cudaGetLastError();
+            return NTB_ERR_CUDA;
+        }
+        return NTB_OK;
+    }
     if ((!aResident && cudaMemcpyAsync(ctx->stage[0], a, aBytes, cudaMemcpyHostToDevice, st) != cudaSuccess) ||
         cudaMemcpyAsync(ctx->stage[1], b, bBytes, cudaMemcpyHostToDevice, st) != cudaSuccess)
         return NTB_ERR_CUDA;
