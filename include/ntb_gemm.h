@@ -63,10 +63,12 @@ extern "C" {
 
 /* kernel routes, as reported by ntb_last_route() */
 #define NTB_ROUTE_NONE      0
-#define NTB_ROUTE_TC_F16    1   /* tcgen05 kind::f16, TMA-fed, TMEM accumulators */
-#define NTB_ROUTE_TC_3XTF32 2   /* tcgen05 kind::tf32, three passes on hi/lo split fp32 */
-#define NTB_ROUTE_SIMT      3   /* FFMA kernel for operands TMA cannot address */
-#define NTB_ROUTE_TC_F16_PAIR 4 /* kind::f16 on CTA pairs (cta_group::2), 256 x 256 tiles */
+#define NTB_ROUTE_TC_F16    1   /* tcgen05 kind::f16, TMEM accumulators; operands by TMA (after a realigning copy where
+                                   TMA could not address them) or, for the tiniest such products, by loader warps */
+#define NTB_ROUTE_TC_3XTF32 2   /* tcgen05 kind::tf32, three passes on hi/lo split fp32; operands as above */
+#define NTB_ROUTE_SIMT      3   /* FFMA kernel: K = 0, operands not aligned to their element size, or forced */
+#define NTB_ROUTE_TC_F16_PAIR 4 /* kind::f16 on CTA pairs (cta_group::2): 512 x 256 to 256 x 128 tiles, or several
+                                   pairs sharing a 256 x 256 tile along K */
 #define NTB_ROUTE_TC_F16X2  5   /* large fp32 products: every value as two scaled half pieces, three
                                    kind::f16 products on CTA pairs (needs scratch for the pieces) */
 
